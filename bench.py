@@ -1,0 +1,228 @@
+"""Benchmark of the B200 W4A16 decode hot path.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Workloads (``config.workload``):
+  gemm      W4A16 GEMM over the four Llama-2-7B projections at ``--tokens`` tokens; a step is one
+            pass over the four linears of a layer.  Inputs larger than L2: the weights of every
+            projection are replicated until they exceed twice the L2 size and each launch takes
+            the next replica.
+
+The timed region is bracketed by a barrier + ``torch.cuda.synchronize()``; device time comes from
+CUDA events on the launching stream; SM clocks and throttle reasons are sampled with nvidia-smi
+during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LLAMA7B_PROJ = [("qkv", 12288, 4096, False), ("o", 4096, 4096, False), ("gate_up", 22016, 4096, True),
+                ("down", 4096, 11008, False)]
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def gemm_bytes(n, k, t, fused):
+    """algorithmic bytes of one W4A16 GEMM: int4 weight + {zero, scale} + activations in + out."""
+    n_out = n // 2 if fused else n
+    return k * n // 2 + (k // 128) * n * 4 + t * k * 2 + t * n_out * 2
+
+
+def build_gemm_case(name, n, k, fused, tokens, l2_bytes, device, seed):
+    """Random packed weights (any nibble pattern is a valid int4 weight) replicated beyond 2x L2."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    per = k * n // 2 + (k // 128) * n * 4
+    reps = max(2, int(2 * l2_bytes // per) + 1)
+    A = torch.randint(-2 ** 31, 2 ** 31 - 1, (reps, k, n // 8), dtype=torch.int32, device=device, generator=g)
+    z = torch.randint(64, 80, (reps, k // 128, n, 1), device=device, generator=g).half()
+    s = (torch.rand(reps, k // 128, n, 1, device=device, generator=g) * 0.01 + 0.002).half()
+    Q = torch.cat([z, s], dim=-1).contiguous()
+    X = torch.randn(reps, tokens, k, device=device, generator=g).half()
+    Y = torch.empty(reps, tokens, n // 2 if fused else n, dtype=torch.float16, device=device)
+    return dict(name=name, n=n, k=k, fused=fused, A=A, Q=Q, X=X, Y=Y, reps=reps)
+
+
+def run_gemm_workload(args, rank, world, device):
+    from lmdeploy_b200 import turbomind as tm
+    from lmdeploy_b200 import lib as l
+    torch.cuda.set_device(device)
+    h = l.default_handle(device)
+    l2 = torch.cuda.get_device_properties(device).L2_cache_size
+    T = args.tokens
+    cases = [build_gemm_case(nm, n, k, fz, T, l2, device, 1000 + i) for i, (nm, n, k, fz) in enumerate(LLAMA7B_PROJ)]
+    op = tm.LlamaLinear(device)
+    weights = [[tm.LlamaDenseWeight(c["k"], c["n"], c["A"][r], tm.WeightType.kINT4, None, c["Q"][r], 128)
+                for r in range(c["reps"])] for c in cases]
+
+    def step(i):
+        for c, ws in zip(cases, weights):
+            r = i % c["reps"]
+            op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
+
+    for i in range(args.warmup):
+        step(i)
+    h.check_device_status(torch.cuda.current_stream().cuda_stream)
+    barrier(world)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device)
+    sampler.start()
+    launches0 = h.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev[1].record()
+    torch.cuda.synchronize()
+    barrier(world)
+    ms = ev[0].elapsed_time(ev[1])
+    clocks = sampler.stop()
+    launches = h.launch_count() - launches0
+    h.check_device_status(torch.cuda.current_stream().cuda_stream)
+
+    # per-kernel timing of the dominant projection (gate_up): events around a run of launches
+    per = {}
+    for c, ws in zip(cases, weights):
+        n_it = max(20, args.steps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(n_it):
+            r = i % c["reps"]
+            op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n_it
+        b = gemm_bytes(c["n"], c["k"], T, c["fused"])
+        per[c["name"]] = dict(us=round(us, 3), gbs=round(b / us * 1e-3, 1), bytes=b)
+
+    bytes_step = sum(gemm_bytes(c["n"], c["k"], T, c["fused"]) for c in cases)
+    ms_step = max_over_ranks(ms / args.steps, world)
+    peaks = measured_peaks()
+    gbs = bytes_step / (ms_step * 1e-3) * 1e-9 * world
+    dom = per["gate_up"]
+    out = {
+        "metric": "W4 GEMM HBM GB/s vs peak (Llama-2-7B projections)", "value": round(gbs, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 x int4 -> f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "gemm", "tokens": T, "shapes": [c["name"] for c in cases],
+                   "l2": "inputs larger than L2: weights replicated beyond 2x L2, next replica each launch",
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "kernel": "gemm_s4_f16_small_kernel (gate_up)", "achieved": dom["gbs"],
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4),
+                     "peak_source": peaks["source"], "traffic": None},
+        "per_kernel": per, "clocks": clocks, "gpu_launches": int(launches),
+    }
+    return out
+
+
+def barrier(world):
+    if world > 1:
+        torch.distributed.barrier()
+
+
+def max_over_ranks(v, world):
+    if world == 1:
+        return v
+    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="gemm")
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--impl", default="b200")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    if args.workload == "gemm":
+        out = run_gemm_workload(args, rank, world, local)
+    else:
+        raise SystemExit(f"unknown workload {args.workload}")
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,93 @@
+/*
+ * tm_b200 — C ABI of a B200 (sm_100a) implementation of TurboMind's quantized decode path.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers are caller-owned,
+ * 16-byte aligned CUDA allocations of the device the handle was created on; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  All work is asynchronous
+ * on `stream`.  Functions return TM_OK (0) or a negative tm_status; they never throw, abort or
+ * exit.  Citations name the interface of lmdeploy v0.0.9 (TurboMind) that each entry replaces,
+ * by the file's path inside that project.
+ *
+ * Naming trap kept from the reference GEMM: `m` is the number of OUTPUT FEATURES, `n` the
+ * number of TOKENS (batch), `k` the number of input features.
+ */
+#ifndef TM_B200_H_
+#define TM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TM_API __attribute__((visibility("default")))
+#else
+#define TM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tm_status {
+    TM_OK                 = 0,
+    TM_ERR_INVALID_ARG    = -1, /* null pointer, misaligned pointer, negative size            */
+    TM_ERR_UNSUPPORTED    = -2, /* group_size != 128, k % 128, m % 32, head_dim != 128 ...    */
+    TM_ERR_WORKSPACE      = -3, /* caller workspace too small                                 */
+    TM_ERR_CUDA           = -4, /* a CUDA runtime call failed (see tm_last_cuda_error)        */
+    TM_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (status word non-zero)  */
+    TM_ERR_NCCL           = -6,
+    TM_ERR_NOT_BUILT      = -7  /* feature compiled out (e.g. NCCL missing)                   */
+} tm_status;
+
+typedef struct tm_handle tm_handle;
+
+/* Per-device state: SM count, split-K scratch, split-KV scratch, device status word.
+ * One handle is used by one host thread at a time (the reference runs one engine thread per
+ * GPU: src/turbomind/models/llama/LlamaV2.cc:435-438); handles of different devices may be
+ * used concurrently.  No process-global mutable state. */
+TM_API int tm_create(tm_handle** out, int device);
+TM_API int tm_destroy(tm_handle* h);
+TM_API const char* tm_status_string(int status);
+/* cudaError_t of the most recent failing CUDA call made through this handle (0 if none). */
+TM_API int tm_last_cuda_error(const tm_handle* h);
+/* Synchronises `stream`, then reads and clears the device status word written by bounded
+ * waits inside the kernels.  *word == 0 means no kernel gave up. */
+TM_API int tm_check_device_status(tm_handle* h, void* stream, unsigned* word);
+/* Number of kernel launches issued through this handle since creation. */
+TM_API unsigned long long tm_launch_count(const tm_handle* h);
+
+/* ------------------------------------------------------------------------------------------
+ * AWQ W4A16 GEMM.  Replaces GemmS4F16::Run
+ *   (src/turbomind/kernels/gemm_s_f16/gemm_s4_f16.h:41-51), called by
+ *   LlamaLinear<half>::forwardInt4 (src/turbomind/models/llama/LlamaLinear.h:62-81).
+ *
+ *   C  half  [n, m]        (type 0)  or  [n, m/2]  (type 1: silu(C[:,2j]) * C[:,2j+1])
+ *   A  uint  [k/32][m/32][32] uint4  — the runtime int4 layout written by tm_convert_s4_k_m8
+ *   B  half  [n, k]        activations, row major
+ *   Q  half2 [k/128, m]    {64 + zero, scale}
+ * Requirements: group_size == 128, k % 128 == 0, m % 32 == 0 (type 1: m % 64 == 0), n >= 1.
+ * `workspace` may be NULL (the handle's own scratch is used); otherwise it must hold
+ * tm_gemm_s4_f16_workspace_bytes(m, n, k) bytes, zero-filled once before first use.
+ */
+enum { TM_GEMM_PLAIN = 0, TM_GEMM_FUSED_SILU_FFN = 1 };
+TM_API size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k);
+TM_API int tm_gemm_s4_f16(tm_handle* h, void* C, const void* A, const void* B, const void* Q, int m, int n, int k,
+                   int group_size, int type, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * int4 format helpers.  Replace the functions of
+ *   src/turbomind/kernels/gemm_s_f16/format.h:11-30 that src/turbomind/python/bind.cpp:414-465
+ *   exports to lmdeploy/serve/turbomind/deploy.py.  Same argument order.  `dst` is fully
+ *   overwritten and must not alias `src`.
+ */
+TM_API int tm_reformat_s4_k_m8(uint32_t* dst, const uint32_t* src, int m, int k, void* stream);
+TM_API int tm_convert_s4_k_m8(uint32_t* A_dst, void* Q_dst, void* workspace, const uint32_t* A_src, const void* scales,
+                       const uint32_t* qzeros, int m, int k, int group_size, void* stream);
+TM_API int tm_transpose_qk_s4_k_m8_hf(uint32_t* dst, const uint32_t* src, int m, int k, int size_per_head, void* stream);
+TM_API int tm_fuse_w1_w3_s4_k_m8(uint32_t* dst, const uint32_t* src, int m, int k, void* stream);
+/* dst: 8 halves per source word, nibble order [0,4,1,5,2,6,3,7], plain values 0..15. */
+TM_API int tm_dequantize_s4(void* dst, const uint32_t* src, size_t count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TM_B200_H_ */

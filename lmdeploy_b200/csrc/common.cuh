@@ -1,0 +1,160 @@
+// Shared device helpers for the sm_100a kernels: mbarrier + bulk-copy (TMA) wrappers with
+// bounded waits, warp-level MMA, and the device status word.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tmb {
+
+// Bits of the device status word (one unsigned per handle).  A kernel that gives up on a
+// bounded wait ORs its bit in and finishes without touching its output any further.
+enum : unsigned {
+    kStatusGemvFullWait  = 1u << 0,
+    kStatusGemvEmptyWait = 1u << 1,
+    kStatusGemmPipeWait  = 1u << 2,
+    kStatusGemmTmemWait  = 1u << 3,
+    kStatusMmhaPipeWait  = 1u << 4,
+};
+
+// Upper bound on polls of one mbarrier wait.  Each poll is an mbarrier.try_wait, which itself
+// blocks for a hardware-defined slice, so the bound is comfortably above any legitimate wait
+// (microseconds) and far below the host-side watchdog.
+constexpr uint32_t kMaxBarrierPolls = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the poll budget ran out (caller records the status bit).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kMaxBarrierPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src),
+                 "r"(bytes),
+                 "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Same, with an L2 eviction-priority hint created by createpolicy.
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(smem_u32(dst)),
+        "l"(src),
+        "r"(bytes),
+        "r"(smem_u32(bar)),
+        "l"(pol)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t policy_evict_first()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ uint64_t policy_evict_last()
+{
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One packed word of the runtime int4 layout -> the four half2 registers of an m16n8k16 A
+// fragment holding the exact integers (nibble - zero):
+//   out[0] = nibbles {0,4} (row r,   k pair low)     out[1] = nibbles {1,5} (row r+8, k pair low)
+//   out[2] = nibbles {2,6} (row r,   k pair high)    out[3] = nibbles {3,7} (row r+8, k pair high)
+// `z1024_lo` = half2{1024 + z(row r)} ; `nz64_hi` = half2{-(64 + z(row r+8))}.
+// 1024 + nib and (1024 + 16 nib) / 16 - (64 + z) are exact in fp16, so the result equals the
+// reference's (64 + nib) - (64 + z) (kernels/gemm_s_f16/common.h:115-156, 218-235) bit for bit.
+__device__ __forceinline__ void unpack_s4_minus_zero(uint32_t w, uint32_t z1024_lo, uint32_t nz64_hi, uint32_t (&out)[4])
+{
+    constexpr uint32_t kLut   = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
+    constexpr uint32_t kBot   = 0x000f000f;
+    constexpr uint32_t kTop   = 0x00f000f0;
+    constexpr uint32_t kMagic = 0x64006400;  // half2{1024, 1024}
+    constexpr uint32_t kSixteenth = 0x2c002c00;  // half2{1/16, 1/16}
+    const uint32_t     hi     = w >> 8;
+    uint32_t           t0, t1, t2, t3;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(t0) : "r"(w), "n"(kBot), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(t1) : "r"(w), "n"(kTop), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(t2) : "r"(hi), "n"(kBot), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(t3) : "r"(hi), "n"(kTop), "n"(kMagic), "n"(kLut));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out[0]) : "r"(t0), "r"(z1024_lo));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[1]) : "r"(t1), "r"(kSixteenth), "r"(nz64_hi));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out[2]) : "r"(t2), "r"(z1024_lo));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[3]) : "r"(t3), "r"(kSixteenth), "r"(nz64_hi));
+}
+
+}  // namespace tmb

@@ -1,0 +1,20 @@
+// Per-device state behind the opaque tm_handle of the C ABI.
+#pragma once
+
+#include "gemm_s4_f16.h"
+
+struct tm_handle {
+    int                device          = 0;
+    int                sm_count        = 0;
+    int                max_smem        = 0;
+    int                l2_bytes        = 0;
+    void*              scratch         = nullptr;  // split-K / split-KV partials
+    size_t             scratch_bytes   = 0;
+    int*               counters        = nullptr;  // self-resetting arrival tickets
+    size_t             counter_ints    = 0;
+    unsigned*          status          = nullptr;  // device status word (bounded waits)
+    int                last_cuda_error = 0;
+    unsigned long long launches        = 0;
+    int                gemv_stages     = 0;  // 0 = automatic; TM_B200_GEMV_STAGES overrides
+    int                gemv_groups     = 0;  // 0 = automatic; TM_B200_GEMV_GROUPS overrides
+};

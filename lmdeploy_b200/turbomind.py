@@ -1,0 +1,121 @@
+"""Host-side mirror of the TurboMind operator surface on the quantized decode path.
+
+Same names, argument order and meaning as lmdeploy v0.0.9:
+
+* ``GemmS4F16.Run``            src/turbomind/kernels/gemm_s_f16/gemm_s4_f16.h:41-51
+* ``LlamaDenseWeight`` / ``WeightType``   src/turbomind/models/llama/LlamaDenseWeight.h:28-63
+* ``LlamaLinear.forward``      src/turbomind/models/llama/LlamaLinear.h:28-42
+* ``transpose_qk_s4_k_m8`` / ``fuse_w1_w3_s4_k_m8`` / ``convert_s4_k_m8`` / ``dequantize_s4``
+                               the ``_turbomind`` helpers of src/turbomind/python/bind.cpp:414-465
+
+Tensors are torch CUDA tensors (device memory + streams are torch's job, nothing else);
+every call goes through the C ABI of ``libtm_b200.so`` on the current torch stream.
+Errors that the reference reports by throwing ``std::runtime_error`` / ``FT_CHECK`` surface
+as :class:`lmdeploy_b200.lib.TmError`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import lib as _l
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("tm_b200 operators take CUDA tensors only (there is no CPU path)")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("tm_b200 operators take contiguous tensors")
+
+
+class WeightType(enum.IntEnum):
+    kFP32 = 0
+    kFP16 = 1
+    kFP8 = 2
+    kINT8 = 3
+    kINT4 = 4
+
+
+@dataclass
+class LlamaDenseWeight:
+    input_dims: int
+    output_dims: int
+    kernel: torch.Tensor                     # int4: int32 [K, N/8] in the runtime layout
+    type: WeightType
+    bias: Optional[torch.Tensor] = None
+    scales_and_zeros: Optional[torch.Tensor] = None   # half [K/g, N, 2] = {64 + z, s}
+    group_size: int = 128
+
+
+class GemmS4F16:
+    kGemm = 0
+    kFusedSiluFfn = 1
+
+    def __init__(self, device: Optional[int] = None):
+        self.device = torch.cuda.current_device() if device is None else device
+        self.handle = _l.default_handle(self.device)
+
+    def Run(self, C_out, A, B, Q, m, n, k, group_size, type, algo_id=-1, stream=None):
+        """C[n, m] = B[n, k] . dequant(A, Q)^T  (m = output features, n = tokens)."""
+        _need_cuda(C_out, A, B, Q)
+        st = _stream() if stream is None else C.c_void_p(stream)
+        s = _l.lib.tm_gemm_s4_f16(self.handle.ptr, _ptr(C_out), _ptr(A), _ptr(B), _ptr(Q), int(m), int(n), int(k),
+                                  int(group_size), int(type), None, 0, st)
+        _l.check(s, "GemmS4F16.Run")
+
+
+class LlamaLinear:
+    kGemm = 0
+    kFusedSiluFfn = 1
+
+    def __init__(self, device: Optional[int] = None):
+        self.gemm_s4_f16_ = GemmS4F16(device)
+
+    def forward(self, output_data, input_data, batch_size, weight: LlamaDenseWeight, type=0):
+        if weight.type == WeightType.kINT4:
+            if input_data.dtype != torch.float16:
+                raise NotImplementedError("int4 weights need half activations")  # LlamaLinear.h:64,78-80
+            self.gemm_s4_f16_.Run(output_data, weight.kernel, input_data, weight.scales_and_zeros, weight.output_dims,
+                                  batch_size, weight.input_dims, weight.group_size,
+                                  GemmS4F16.kFusedSiluFfn if type == self.kFusedSiluFfn else GemmS4F16.kGemm, -1)
+        else:
+            raise NotImplementedError("only the int4 (W4A16) path is built; fp16 linears are out of scope")
+
+
+# ---- `_turbomind` format helpers (bind.cpp:414-465): (src, dst, ...) argument order kept ----
+
+def transpose_qk_s4_k_m8(src, dst, m, k, size_per_head):
+    _need_cuda(src, dst)
+    _l.check(_l.lib.tm_transpose_qk_s4_k_m8_hf(_ptr(dst), _ptr(src), m, k, size_per_head, _stream()),
+             "transpose_qk_s4_k_m8")
+
+
+def fuse_w1_w3_s4_k_m8(src, dst, m, k):
+    _need_cuda(src, dst)
+    _l.check(_l.lib.tm_fuse_w1_w3_s4_k_m8(_ptr(dst), _ptr(src), m, k, _stream()), "fuse_w1_w3_s4_k_m8")
+
+
+def convert_s4_k_m8(A_dst, Q_dst, ws, A_src, scales, qzeros, m, k, group_size):
+    _need_cuda(A_dst, Q_dst, ws, A_src, scales, qzeros)
+    _l.check(_l.lib.tm_convert_s4_k_m8(_ptr(A_dst), _ptr(Q_dst), _ptr(ws), _ptr(A_src), _ptr(scales), _ptr(qzeros),
+                                       m, k, group_size, _stream()), "convert_s4_k_m8")
+
+
+def dequantize_s4(src, dst):
+    _need_cuda(src, dst)
+    if src.numel() * 8 != dst.numel():
+        raise ValueError("dst must hold 8 halves per source word")  # bind.cpp:462
+    _l.check(_l.lib.tm_dequantize_s4(_ptr(dst), _ptr(src), src.numel(), _stream()), "dequantize_s4")
