@@ -127,41 +127,65 @@ def run_gemm_workload(args, rank, world, device):
             r = i % c["reps"]
             op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
 
-    for i in range(args.warmup):
-        step(i)
-    h.check_device_status(torch.cuda.current_stream().cuda_stream)
-    barrier(world)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(device)
-    sampler.start()
-    launches0 = h.launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    ev[1].record()
-    torch.cuda.synchronize()
-    barrier(world)
-    ms = ev[0].elapsed_time(ev[1])
-    clocks = sampler.stop()
-    launches = h.launch_count() - launches0
-    h.check_device_status(torch.cuda.current_stream().cuda_stream)
+    def one(c, ws, i):
+        r = i % c["reps"]
+        op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
 
-    # per-kernel timing of the dominant projection (gate_up): events around a run of launches
-    per = {}
-    for c, ws in zip(cases, weights):
-        n_it = max(20, args.steps)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The launches are replayed from CUDA graphs so that the device, not the Python caller,
+    # sets the pace.  One graph = `ring` consecutive steps (every step takes the next replica).
+    ring = max(c["reps"] for c in cases)
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            step(i)
+        h.check_device_status(stream.cuda_stream)
+        g_step = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_step, stream=stream):
+            for i in range(ring):
+                step(i)
+        g_one = {}
+        for c, ws in zip(cases, weights):
+            g_one[c["name"]] = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_one[c["name"]], stream=stream):
+                for i in range(c["reps"]):
+                    one(c, ws, i)
+        n_replay = max(1, (args.steps + ring - 1) // ring)
+        steps_done = n_replay * ring
+        g_step.replay()
+        barrier(world)
         torch.cuda.synchronize()
-        e0.record()
-        for i in range(n_it):
-            r = i % c["reps"]
-            op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
-        e1.record()
+        sampler = ClockSampler(device)
+        sampler.start()
+        launches0 = h.launch_count()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record(stream)
+        for _ in range(n_replay):
+            g_step.replay()
+        ev[1].record(stream)
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / n_it
-        b = gemm_bytes(c["n"], c["k"], T, c["fused"])
-        per[c["name"]] = dict(us=round(us, 3), gbs=round(b / us * 1e-3, 1), bytes=b)
+        barrier(world)
+        ms = ev[0].elapsed_time(ev[1])
+        launches = n_replay * ring * len(cases)
+        h.check_device_status(stream.cuda_stream)
+
+        # per-kernel device time: a graph of `reps` launches of one projection, replayed
+        per = {}
+        for c in cases:
+            g = g_one[c["name"]]
+            n_rep = max(3, 200 // c["reps"])
+            g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(n_rep):
+                g.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (n_rep * c["reps"])
+            b = gemm_bytes(c["n"], c["k"], T, c["fused"])
+            per[c["name"]] = dict(us=round(us, 3), gbs=round(b / us * 1e-3, 1), bytes=b)
+        clocks = sampler.stop()
+    args.steps = steps_done
 
     bytes_step = sum(gemm_bytes(c["n"], c["k"], T, c["fused"]) for c in cases)
     ms_step = max_over_ranks(ms / args.steps, world)

@@ -87,6 +87,77 @@ TM_API int tm_fuse_w1_w3_s4_k_m8(uint32_t* dst, const uint32_t* src, int m, int 
 /* dst: 8 halves per source word, nibble order [0,4,1,5,2,6,3,7], plain values 0..15. */
 TM_API int tm_dequantize_s4(void* dst, const uint32_t* src, size_t count, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Decode-step masked multi-head attention with fused RoPE, KV append and (optionally) an int8
+ * KV cache.  Replaces masked_multihead_attention(const Masked_multihead_attention_params<
+ * uint16_t>&, const cudaStream_t&)
+ *   (src/turbomind/kernels/decoder_masked_multihead_attention.h:50-133) as LLaMA drives it
+ *   (fusedQKV_masked_attention_dispatch, src/turbomind/models/llama/
+ *   LlamaDecoderSelfAttentionLayer.cc:44-166).  The struct mirrors the fields that call site
+ *   sets, with the reference's names and meaning; zero-initialise it and fill what you use.
+ *
+ *   q/k/v              one fused buffer half [batch, stride]; q heads | k heads | v heads
+ *   out                half [batch, num_heads * 128]
+ *   k/v_cache_per_sample  device array [batch] of base pointers; sequence b's cache for this
+ *                      layer starts kv_cache_per_sample_offset ELEMENTS in and is laid out
+ *                      [num_kv_heads][memory_max_len][128] (element = half, or int8 when
+ *                      int8_mode & 4)
+ *   length_per_sample  device int [batch]: tokens already cached; the new token is written to
+ *                      slot length % memory_max_len and attends to the last
+ *                      min(length, memory_max_len - 1) cached tokens plus itself
+ *   timestep           >= every length_per_sample[b]; RoPE position of sequence b is
+ *                      timestep - total_padding_tokens[b] (0 padding if the pointer is NULL)
+ *   finished           device bool [batch] or NULL: finished sequences are skipped entirely
+ * Only hidden_size_per_head == 128 is supported (as in the reference build).
+ */
+typedef struct tm_mmha_params {
+    void*       out;
+    const void* q;
+    const void* q_bias;
+    const void* k;
+    const void* k_bias;
+    const void* v;
+    const void* v_bias;
+    int         stride;
+    int         batch_size;
+    int         memory_max_len;
+    int         num_heads;
+    int         num_kv_heads;
+    int         hidden_size_per_head;
+    int         rotary_embedding_dim;
+    int         timestep;
+    float       inv_sqrt_dh;
+    const int*  total_padding_tokens;
+    int         int8_mode; /* bit 2 (value 4, QuantPolicy::kCacheKVInt8): int8 KV cache */
+    float       attention_k_scale;
+    float       attention_k_zp;
+    float       attention_v_scale;
+    float       attention_v_zp;
+    const unsigned char* finished;
+    const int*  length_per_sample;
+    void**      k_cache_per_sample;
+    void**      v_cache_per_sample;
+    size_t      kv_cache_per_sample_offset;
+    int         max_position_embeddings;
+    int         use_dynamic_ntk;
+    int         use_logn_attn;
+    float       rotary_embedding_base;
+} tm_mmha_params;
+
+TM_API int tm_mmha_decode(tm_handle* h, const tm_mmha_params* params, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * RMSNorm of the decoder loop (half data, fp32 math).  Replace
+ *   invokeRootMeanSquareNorm            (src/turbomind/models/llama/llama_kernels.cu:69-79)
+ *   invokeFusedAddBiasResidualRMSNorm   (src/turbomind/models/llama/llama_decoder_kernels.cu:147-160)
+ * tm_rmsnorm: out[m, n] = in * rsqrt(mean(in^2) + eps) * scale   (out may alias in).
+ * tm_add_residual_rmsnorm: residual += in_out (+ bias); in_out = RMSNorm(residual) * scale.
+ * n % 8 == 0, n <= 16384.
+ */
+TM_API int tm_rmsnorm(void* out, const void* in, const void* scale, float eps, int m, int n, void* stream);
+TM_API int tm_add_residual_rmsnorm(void* residual, void* in_out, const void* bias, const void* scale, float eps, int m,
+                            int n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

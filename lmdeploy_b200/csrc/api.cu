@@ -56,12 +56,18 @@ extern "C" int tm_create(tm_handle** out, int device)
     }
     if (e == cudaSuccess) e = cudaMalloc(&h->counters, h->counter_ints * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(h->counters, 0, h->counter_ints * sizeof(int));
+    h->attn_scratch_bytes = 128u << 20;
+    h->attn_counter_ints  = 1u << 18;
+    if (e == cudaSuccess) e = cudaMalloc(&h->attn_scratch, h->attn_scratch_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&h->attn_counters, h->attn_counter_ints * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(h->attn_counters, 0, h->attn_counter_ints * sizeof(int));
+    if (e == cudaSuccess) e = mmha_prepare();
     if (e == cudaSuccess) e = cudaMalloc(&h->status, 256);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);
     if (e == cudaSuccess) e = gemm_small_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->gemv_stages = env_int("TM_B200_GEMV_STAGES", 0);
-    h->gemv_groups = env_int("TM_B200_GEMV_GROUPS", 0);
+    h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -80,6 +86,8 @@ extern "C" int tm_destroy(tm_handle* h)
     cudaSetDevice(h->device);
     if (h->scratch) cudaFree(h->scratch);
     if (h->counters) cudaFree(h->counters);
+    if (h->attn_scratch) cudaFree(h->attn_scratch);
+    if (h->attn_counters) cudaFree(h->attn_counters);
     if (h->status) cudaFree(h->status);
     cudaSetDevice(prev);
     delete h;
@@ -116,7 +124,7 @@ extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
 {
     if (m <= 0 || n <= 0 || k <= 0 || k % 128 || m % 32) return 0;
     // device independent: the slot count grows with the grid, so plan for a grid no part exceeds
-    GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024, 0, 0);
+    GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024, 0);
     return pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
 }
 
@@ -141,43 +149,160 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     if (type != TM_GEMM_PLAIN && type != TM_GEMM_FUSED_SILU_FFN) return TM_ERR_UNSUPPORTED;
     if (type == TM_GEMM_FUSED_SILU_FFN && m % 64) return TM_ERR_UNSUPPORTED;
 
-    GemmSmallPlan pl = gemm_small_plan(m, n, k, h->sm_count, h->max_smem, h->gemv_stages, h->gemv_groups);
-
-    float* ws_f = nullptr;
-    int*   ws_c = nullptr;
-    if (workspace) {
-        const size_t need = pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
-        if (workspace_bytes < need) return TM_ERR_WORKSPACE;
-        // counters first (they must start at zero and reset themselves), 256-byte aligned partials after
-        ws_c = (int*)workspace;
-        ws_f = (float*)((char*)workspace + ((pl.counter_ints * sizeof(int) + 255) / 256) * 256);
+    // One launch covers up to `n_launch` tokens; more tokens than the scratch can hold partial
+    // tiles for are processed in several launches over consecutive token ranges.
+    const size_t n_out = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;
+    int          n_launch = n;
+    for (;;) {
+        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem, h->gemv_stages);
+        const size_t  c_b  = ((pl.counter_ints * sizeof(int) + 255) / 256) * 256;
+        const size_t  need = pl.workspace_floats * sizeof(float) + c_b;
+        const bool    fits = workspace ? workspace_bytes >= need :
+                                         (pl.workspace_floats * sizeof(float) <= h->scratch_bytes
+                                          && pl.counter_ints <= h->counter_ints);
+        if (fits) break;
+        if (n_launch <= 32) return TM_ERR_WORKSPACE;
+        n_launch = ((n_launch / 2 + 31) / 32) * 32;
     }
-    else {
-        if (pl.workspace_floats * sizeof(float) > h->scratch_bytes || pl.counter_ints > h->counter_ints) {
-            return TM_ERR_WORKSPACE;
+
+    for (int t0 = 0; t0 < n; t0 += n_launch) {
+        const int     nt = n - t0 < n_launch ? n - t0 : n_launch;
+        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem, h->gemv_stages);
+        float*        ws_f;
+        int*          ws_c;
+        if (workspace) {
+            // tickets first (they start at zero and reset themselves), 256-byte aligned partials after
+            ws_c = (int*)workspace;
+            ws_f = (float*)((char*)workspace + ((pl.counter_ints * sizeof(int) + 255) / 256) * 256);
         }
-        ws_f = (float*)h->scratch;
-        ws_c = h->counters;
+        else {
+            ws_f = (float*)h->scratch;
+            ws_c = h->counters;
+        }
+        GemmSmallParams p{};
+        p.C          = (__half*)C + (size_t)t0 * n_out;
+        p.A          = (const unsigned char*)A;
+        p.X          = (const unsigned char*)B + (size_t)t0 * k * 2;
+        p.Q          = (const unsigned char*)Q;
+        p.workspace  = ws_f;
+        p.counters   = ws_c;
+        p.status     = h->status;
+        p.N          = m;
+        p.T          = nt;
+        p.K          = k;
+        p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+
+        cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream);
+        h->launches += 1;
+        if (e != cudaSuccess) {
+            h->last_cuda_error = (int)e;
+            return TM_ERR_CUDA;
+        }
+    }
+    return TM_OK;
+}
+
+extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* stream)
+{
+    if (!h || !a) return TM_ERR_INVALID_ARG;
+    if (!a->out || !a->q || !a->k || !a->v || !a->length_per_sample || !a->k_cache_per_sample || !a->v_cache_per_sample) {
+        return TM_ERR_INVALID_ARG;
+    }
+    if (a->batch_size <= 0 || a->num_heads <= 0 || a->num_kv_heads <= 0 || a->memory_max_len <= 0 || a->timestep < 0) {
+        return TM_ERR_INVALID_ARG;
+    }
+    if (a->hidden_size_per_head != 128) return TM_ERR_UNSUPPORTED;  // decoder_masked_multihead_attention.cu:28-34
+    if (a->num_heads % a->num_kv_heads) return TM_ERR_UNSUPPORTED;
+    if (a->rotary_embedding_dim < 0 || a->rotary_embedding_dim > 128 || a->rotary_embedding_dim % 2) return TM_ERR_UNSUPPORTED;
+    const bool int8 = (a->int8_mode & 4) != 0;
+    if (int8 && !(a->attention_k_scale > 0.f && a->attention_v_scale > 0.f)) return TM_ERR_INVALID_ARG;
+    // q, k, v must be the three column blocks of one fused buffer (the only form LLaMA uses)
+    const __half* q = (const __half*)a->q;
+    if ((const __half*)a->k != q + (size_t)a->num_heads * 128
+        || (const __half*)a->v != q + (size_t)(a->num_heads + a->num_kv_heads) * 128) {
+        return TM_ERR_UNSUPPORTED;
+    }
+    if (a->stride < (a->num_heads + 2 * a->num_kv_heads) * 128 || a->stride % 8) return TM_ERR_INVALID_ARG;
+    if (((uintptr_t)a->out | (uintptr_t)a->q) & 15u) return TM_ERR_INVALID_ARG;
+    const __half* bias = nullptr;
+    if (a->q_bias || a->k_bias || a->v_bias) {
+        if (!a->q_bias || (const __half*)a->k_bias != (const __half*)a->q_bias + (size_t)a->num_heads * 128
+            || (const __half*)a->v_bias != (const __half*)a->q_bias + (size_t)(a->num_heads + a->num_kv_heads) * 128) {
+            return TM_ERR_UNSUPPORTED;
+        }
+        bias = (const __half*)a->q_bias;
     }
 
-    GemmSmallParams p{};
-    p.C          = (__half*)C;
-    p.A          = (const unsigned char*)A;
-    p.X          = (const unsigned char*)B;
-    p.Q          = (const unsigned char*)Q;
-    p.workspace  = ws_f;
-    p.counters   = ws_c;
-    p.status     = h->status;
-    p.N          = m;
-    p.T          = n;
-    p.K          = k;
-    p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+    const int max_len = a->timestep < a->memory_max_len ? a->timestep : a->memory_max_len;
+    MmhaPlan  pl      = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, h->mmha_chunk);
+    while (pl.ws_floats * sizeof(float) > h->attn_scratch_bytes && pl.chunk < (1 << 20)) {
+        pl = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, pl.chunk * 2);
+    }
+    if (pl.ws_floats * sizeof(float) > h->attn_scratch_bytes || pl.counter_ints > h->attn_counter_ints) {
+        return TM_ERR_WORKSPACE;
+    }
 
-    cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream);
+    MmhaParams p{};
+    p.out             = (__half*)a->out;
+    p.qkv             = q;
+    p.bias            = bias;
+    p.k_cache         = a->k_cache_per_sample;
+    p.v_cache         = a->v_cache_per_sample;
+    p.cache_offset    = a->kv_cache_per_sample_offset;
+    p.lengths         = a->length_per_sample;
+    p.finished        = a->finished;
+    p.padding         = a->total_padding_tokens;
+    p.B               = a->batch_size;
+    p.H               = a->num_heads;
+    p.Hkv             = a->num_kv_heads;
+    p.stride          = a->stride;
+    p.S_max           = a->memory_max_len;
+    p.timestep        = a->timestep;
+    p.rot_dim         = a->rotary_embedding_dim;
+    p.max_pos         = a->max_position_embeddings;
+    p.use_dynamic_ntk = a->use_dynamic_ntk;
+    p.use_logn        = a->use_logn_attn;
+    p.rope_base       = a->rotary_embedding_base > 0.f ? a->rotary_embedding_base : 10000.f;
+    p.inv_sqrt_dh     = a->inv_sqrt_dh;
+    p.k_scale         = a->attention_k_scale;
+    p.k_zp            = a->attention_k_zp;
+    p.v_scale         = a->attention_v_scale;
+    p.v_zp            = a->attention_v_zp;
+    p.ws              = (float*)h->attn_scratch;
+    p.counters        = h->attn_counters;
+    p.status          = h->status;
+
+    cudaError_t e = mmha_launch(pl, p, int8, (cudaStream_t)stream);
     h->launches += 1;
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
         return TM_ERR_CUDA;
     }
     return TM_OK;
+}
+
+extern "C" int tm_rmsnorm(void* out, const void* in, const void* scale, float eps, int m, int n, void* stream)
+{
+    if (!out || !in || !scale || m < 0 || n <= 0) return TM_ERR_INVALID_ARG;
+    if (n % 8 || n > 16384) return TM_ERR_UNSUPPORTED;
+    if (((uintptr_t)out | (uintptr_t)in | (uintptr_t)scale) & 15u) return TM_ERR_INVALID_ARG;
+    if (m == 0) return TM_OK;
+    return rmsnorm_launch((__half*)out, (const __half*)in, (const __half*)scale, eps, m, n, (cudaStream_t)stream)
+                   == cudaSuccess ?
+               TM_OK :
+               TM_ERR_CUDA;
+}
+
+extern "C" int tm_add_residual_rmsnorm(
+    void* residual, void* in_out, const void* bias, const void* scale, float eps, int m, int n, void* stream)
+{
+    if (!residual || !in_out || !scale || m < 0 || n <= 0) return TM_ERR_INVALID_ARG;
+    if (n % 8 || n > 16384) return TM_ERR_UNSUPPORTED;
+    if (((uintptr_t)residual | (uintptr_t)in_out | (uintptr_t)scale | (uintptr_t)bias) & 15u) return TM_ERR_INVALID_ARG;
+    if (m == 0) return TM_OK;
+    return add_residual_rmsnorm_launch((__half*)residual, (__half*)in_out, (const __half*)bias, (const __half*)scale, eps,
+                                       m, n, (cudaStream_t)stream)
+                   == cudaSuccess ?
+               TM_OK :
+               TM_ERR_CUDA;
 }

@@ -18,10 +18,9 @@ enum : unsigned {
     kStatusMmhaPipeWait  = 1u << 4,
 };
 
-// Upper bound on polls of one mbarrier wait.  Each poll is an mbarrier.try_wait, which itself
-// blocks for a hardware-defined slice, so the bound is comfortably above any legitimate wait
-// (microseconds) and far below the host-side watchdog.
-constexpr uint32_t kMaxBarrierPolls = 1u << 22;
+// Upper bound, in SM clock cycles, on one mbarrier wait (about 0.15-0.3 s): far above any
+// legitimate wait (microseconds), far below a host-side watchdog.
+constexpr long long kMaxWaitCycles = 1ll << 29;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
@@ -68,15 +67,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the poll budget ran out (caller records the status bit).
+// Bounded wait.  Returns false when the time budget ran out (caller records the status bit).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
 {
-    for (uint32_t i = 0; i < kMaxBarrierPolls; ++i) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kMaxWaitCycles) {
+            return false;
         }
     }
-    return false;
+    return true;
 }
 
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.

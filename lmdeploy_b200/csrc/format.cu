@@ -196,9 +196,9 @@ extern "C" int tm_fuse_w1_w3_s4_k_m8(uint32_t* dst, const uint32_t* src, int m, 
 
 extern "C" int tm_dequantize_s4(void* dst, const uint32_t* src, size_t count, void* stream)
 {
+    if (count == 0) return TM_OK;
     if (!dst || !src) return TM_ERR_INVALID_ARG;
     if (!aligned16(dst)) return TM_ERR_INVALID_ARG;
-    if (count == 0) return TM_OK;
     dequantize_s4_kernel<<<grid_for(count, 256), 256, 0, (cudaStream_t)stream>>>((uint4*)dst, src, count);
     return launch_status();
 }

@@ -20,26 +20,25 @@ struct GemmSmallParams {
     int                  N, T, K;
     int                  fused_silu;
     // filled in by gemm_small_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, stages, consumer_groups;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, stages;
 };
 
 struct GemmSmallPlan {
     int    nt;             // 8-token MMA tiles per pass (1, 2 or 4)
     int    t_chunks;       // passes over the weight (grid.y)
-    int    n_col_tiles;    // 128-column tiles
-    int    total_units;    // 128x128 weight units
+    int    n_col_tiles;    // 512-column tiles
+    int    total_units;    // 32x512 weight units
     int    units_per_cta;
     int    ctas;
     int    slots_per_chunk;  // split-K scratch slots per token chunk (= ctas + n_col_tiles)
-    int    groups;         // consumer groups of 4 warps
     int    stages;
     size_t smem_bytes;
     size_t workspace_floats;
     size_t counter_ints;
 };
 
-size_t        gemm_small_smem_bytes(int nt, int stages, int groups);
-GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int want_stages, int want_groups);
+size_t        gemm_small_smem_bytes(int stages);
+GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int want_stages);
 cudaError_t   gemm_small_prepare(int max_smem);
 cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st);
 

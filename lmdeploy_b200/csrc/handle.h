@@ -2,6 +2,7 @@
 #pragma once
 
 #include "gemm_s4_f16.h"
+#include "mmha.h"
 
 struct tm_handle {
     int                device          = 0;
@@ -12,9 +13,13 @@ struct tm_handle {
     size_t             scratch_bytes   = 0;
     int*               counters        = nullptr;  // self-resetting arrival tickets
     size_t             counter_ints    = 0;
+    void*              attn_scratch    = nullptr;  // split-KV partials of the attention kernel
+    size_t             attn_scratch_bytes = 0;
+    int*               attn_counters   = nullptr;
+    size_t             attn_counter_ints = 0;
     unsigned*          status          = nullptr;  // device status word (bounded waits)
     int                last_cuda_error = 0;
     unsigned long long launches        = 0;
+    int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                gemv_stages     = 0;  // 0 = automatic; TM_B200_GEMV_STAGES overrides
-    int                gemv_groups     = 0;  // 0 = automatic; TM_B200_GEMV_GROUPS overrides
 };

@@ -1,0 +1,637 @@
+// Decode-step masked multi-head attention over a per-sequence KV cache (fp16 or int8), one new
+// query token per sequence.  Replaces mmha::masked_multihead_attention_kernel
+// (src/turbomind/kernels/decoder_masked_multihead_attention/
+// decoder_masked_multihead_attention_template.cuh:1218-1913 of lmdeploy v0.0.9), which walks the
+// whole sequence with one CTA per (head, sequence), three passes, no split along the sequence and
+// one KV read per *query* head.
+//
+// Here a CTA owns (sequence, KV head, split of the sequence).  All query heads that share the KV
+// head (up to 8 per CTA) ride on the same KV bytes.  Each of the 4 warps streams its own 16-token
+// blocks of K and V through a private cp.async ring (XOR-swizzled 16-byte chunks, so that every
+// shared-memory read below is conflict free) and keeps an online-softmax state:
+//   S^T[token, head] = K . Q^T      mma.m16n8k16, A = K rows (int8 expanded to exact fp16
+//                                   integers in registers), B = Q fragments held in registers
+//   P^T -> fp16, transposed in registers with movmatrix to become the B operand of
+//   O^T[d, head]     = V^T . P^T    A = V with token pairs interleaved by byte permutes
+// RoPE on the new q/k, the KV append (with int8 quantisation) and the new token's own score are
+// fused in.  Splits meet in scratch memory; the last CTA to arrive for a (sequence, KV head)
+// merges them in a fixed order (no CTA waits for another).
+#include "common.cuh"
+#include "mmha.h"
+
+#include <cfloat>
+
+namespace tmb {
+namespace {
+
+constexpr int kD          = 128;  // head dim
+constexpr int kWarps      = 4;
+constexpr int kBlockTok   = 16;   // tokens per warp block
+constexpr int kHeadsPerCta = 8;
+constexpr float kLog2e    = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid)
+{
+    const uint32_t d = smem_u32(dst);
+    const int      n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template<int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
+{
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+{
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return reinterpret_cast<const uint32_t&>(h);
+}
+__device__ __forceinline__ uint32_t lds32(const unsigned char* p)
+{
+    return *reinterpret_cast<const uint32_t*>(p);
+}
+__device__ __forceinline__ uint4 lds128(const unsigned char* p)
+{
+    return *reinterpret_cast<const uint4*>(p);
+}
+
+constexpr uint32_t kMagic64  = 0x64646464u;  // high bytes of half 1024 + x
+constexpr uint32_t kBias1152 = 0x64806480u;  // half2{1152, 1152}: 1024 + 128
+constexpr uint32_t kSignFlip = 0x80808080u;
+
+// four int8 (one word, sign bits already flipped) -> two half2 of exact integers
+__device__ __forceinline__ void s8x4_to_h2x2(uint32_t x, uint32_t& lo, uint32_t& hi)
+{
+    lo = hsub2(prmt(x, kMagic64, 0x4140), kBias1152);
+    hi = hsub2(prmt(x, kMagic64, 0x4342), kBias1152);
+}
+
+// query-fragment column of lane c at MMA step j: the 4 consecutive head-dim indices d0..d0+3
+// that K-slot (2c, 2c+1, 2c+8, 2c+9) stand for.  Chosen so that a lane reads whole 16-byte
+// chunks of a K row: int8 row = 8 chunks, lane c owns chunks {2c, 2c+1}; fp16 row = 16 chunks,
+// lane c owns {2c, 2c+1, 2c+8, 2c+9}.
+template<bool INT8>
+__device__ __forceinline__ int qk_d0(int c, int j)
+{
+    return INT8 ? 32 * c + 4 * j : 16 * c + 64 * (j >> 2) + 4 * (j & 3);
+}
+
+template<bool INT8>
+__global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
+{
+    constexpr int ROWB   = INT8 ? kD : 2 * kD;        // bytes per cached token row
+    constexpr int CPR    = ROWB / 16;                 // 16-byte chunks per row
+    constexpr int NSTAGE = INT8 ? 4 : 3;
+    constexpr int TILEB  = kBlockTok * ROWB;          // one K (or V) block of a warp
+    constexpr int WARPB  = NSTAGE * 2 * TILEB;        // ring of one warp
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    // [warps][NSTAGE][K tile | V tile]   (reused by the merge)  | q_s[8][128] half | knew[128] half |
+    // vnew[128] half | sumq[8] f32 | snew[8] f32 | flag
+    unsigned char* ring   = smem;
+    __half*        q_s    = reinterpret_cast<__half*>(smem + kWarps * WARPB);
+    __half*        knew_s = q_s + kHeadsPerCta * kD;
+    __half*        vnew_s = knew_s + kD;
+    float*         sumq_s = reinterpret_cast<float*>(vnew_s + kD);
+    float*         snew_s = sumq_s + kHeadsPerCta;
+    int*           flag_s = reinterpret_cast<int*>(snew_s + kHeadsPerCta);
+
+    const int tid  = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g    = lane >> 2;
+    const int c    = lane & 3;
+
+    const int bi = blockIdx.z;
+    if (p.finished != nullptr && p.finished[bi]) {
+        return;  // template.cuh:1298-1300: neither out nor the cache is touched
+    }
+    const int rep    = p.H / p.Hkv;
+    const int n_hb   = (rep + kHeadsPerCta - 1) / kHeadsPerCta;
+    const int kvh    = blockIdx.y / n_hb;
+    const int hb     = blockIdx.y - kvh * n_hb;
+    const int head0  = kvh * rep + hb * kHeadsPerCta;      // first query head of this CTA
+    const int nheads = min(kHeadsPerCta, rep - hb * kHeadsPerCta);
+
+    const int tlength = p.lengths[bi];
+    const int first   = max(0, tlength + 1 - p.S_max);
+    const int n_past  = tlength - first;
+    const int n_split = max(1, (n_past + p.chunk - 1) / p.chunk);
+    const int split   = blockIdx.x;
+    if (split >= n_split) {
+        return;
+    }
+    const bool last_split = (split == n_split - 1);
+    const int  s0         = first + split * p.chunk;
+    const int  s1         = min(s0 + p.chunk, tlength);
+    const int  n_blocks   = (max(s1 - s0, 0) + kBlockTok - 1) / kBlockTok;
+
+    const unsigned char* kc =
+        reinterpret_cast<const unsigned char*>(p.k_cache[bi]) + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
+    const unsigned char* vc =
+        reinterpret_cast<const unsigned char*>(p.v_cache[bi]) + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
+
+    // ---------------------------------------------------------------- KV ring: start the loads
+    unsigned char* my_ring = ring + warp * WARPB;
+    auto issue_block = [&](int blk, int stage) {
+        // blk: index among this warp's blocks; absolute first token of the block:
+        const int      tok0 = s0 + (blk * kWarps + warp) * kBlockTok;
+        unsigned char* ks   = my_ring + stage * 2 * TILEB;
+        unsigned char* vs   = ks + TILEB;
+#pragma unroll
+        for (int i = 0; i < kBlockTok * CPR / 32; ++i) {
+            const int    id    = lane + 32 * i;
+            const int    tok   = id / CPR;
+            const int    ch    = id % CPR;
+            const int    ti    = tok0 + tok;
+            const bool   valid = ti < s1;
+            const size_t row   = valid ? (size_t)(ti % p.S_max) * ROWB : 0;
+            const int    dst   = tok * ROWB + ((ch ^ (tok & 7)) << 4);
+            cp_async16(ks + dst, kc + row + ch * 16, valid);
+            cp_async16(vs + dst, vc + row + ch * 16, valid);
+        }
+    };
+    const int my_blocks = (n_blocks > warp) ? (n_blocks - warp + kWarps - 1) / kWarps : 0;
+#pragma unroll
+    for (int sidx = 0; sidx < NSTAGE - 1; ++sidx) {
+        if (sidx < my_blocks) {
+            issue_block(sidx, sidx);
+        }
+        cp_async_commit();
+    }
+
+    // ---------------------------------------------------------------- q (+k, v of the new token)
+    {
+        float base = p.rope_base;
+        if (p.use_dynamic_ntk) {
+            // decoder_masked_multihead_attention_utils.h:862-871, seq_len = length + 1
+            const float seq_len = (float)(tlength + 1);
+            if (seq_len >= (float)p.max_pos) {
+                const float alpha = fmaxf(exp2f(ceilf(log2f(seq_len / (float)p.max_pos) + 1.f)) - 1.f, 1.f);
+                base *= powf(alpha, (float)p.rot_dim / ((float)p.rot_dim - 2.f));
+            }
+        }
+        float logn = 1.f;
+        if (p.use_logn && (float)(tlength + 1) > (float)p.max_pos) {
+            logn = log2f((float)(tlength + 1)) / log2f((float)p.max_pos);  // utils.h:854-860
+        }
+        const int   pad  = p.padding ? p.padding[bi] : 0;
+        const float pos  = (float)(p.timestep - pad);  // template.cuh:1391-1395
+        const int   pr   = tid & 63;                    // pair index: elements 2pr, 2pr+1
+        const int   part = tid >> 6;                    // 0 / 1: which rows this thread handles
+        float       cs = 1.f, sn = 0.f;
+        const bool  rot = 2 * pr < p.rot_dim;
+        if (rot) {
+            const float inv_freq = pos / powf(base, (float)(2 * pr) / (float)p.rot_dim);  // utils.h:885-889
+            sincosf(inv_freq, &sn, &cs);
+        }
+        const __half* xrow = p.qkv + (size_t)bi * p.stride;
+        // rows 0..7: query heads (zero beyond nheads); row 8: k; row 9: v
+        for (int row = part; row < kHeadsPerCta + 2; row += 2) {
+            const bool is_q = row < kHeadsPerCta;
+            if (!is_q && !last_split) {
+                continue;
+            }
+            int col;  // column of the fused qkv row
+            if (is_q) {
+                col = (head0 + row) * kD;
+            }
+            else if (row == kHeadsPerCta) {
+                col = (p.H + kvh) * kD;
+            }
+            else {
+                col = (p.H + p.Hkv + kvh) * kD;
+            }
+            float2 x = make_float2(0.f, 0.f);
+            if (!is_q || row < nheads) {
+                __half2 h = *reinterpret_cast<const __half2*>(xrow + col + 2 * pr);
+                if (p.bias) {
+                    h = __hadd2(h, *reinterpret_cast<const __half2*>(p.bias + col + 2 * pr));  // fp16 add, :1381-1382
+                }
+                x = __half22float2(h);
+            }
+            if (rot && row <= kHeadsPerCta) {  // q and k only
+                const float2 y = make_float2(cs * x.x - sn * x.y, cs * x.y + sn * x.x);  // utils.h:891-897
+                x              = y;
+            }
+            __half2 h = __floats2half2_rn(x.x, x.y);
+            if (is_q && logn != 1.f) {
+                h = __hmul2(h, __float2half2_rn(logn));
+            }
+            __half* dstp = is_q ? q_s + row * kD : (row == kHeadsPerCta ? knew_s : vnew_s);
+            *reinterpret_cast<__half2*>(dstp + 2 * pr) = h;
+        }
+    }
+    __syncthreads();
+
+    // per-head sum of q (for a non-zero K zero point) and the new token's own score
+    for (int h = warp; h < kHeadsPerCta; h += kWarps) {
+        float sq = 0.f, dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float q = __half2float(q_s[h * kD + lane * 4 + i]);
+            sq += q;
+            if (last_split) {
+                dot += q * __half2float(knew_s[lane * 4 + i]);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, m);
+            dot += __shfl_xor_sync(0xffffffffu, dot, m);
+        }
+        if (lane == 0) {
+            sumq_s[h] = sq;
+            snew_s[h] = dot * p.inv_sqrt_dh * kLog2e;  // log2 units
+        }
+    }
+
+    // the new token goes into the cache (one CTA per sequence and KV head does it)
+    if (last_split && hb == 0) {
+        const size_t   slot = (size_t)(tlength % p.S_max) * ROWB;
+        unsigned char* kd   = const_cast<unsigned char*>(kc) + slot;
+        unsigned char* vd   = const_cast<unsigned char*>(vc) + slot;
+        if (INT8) {
+            if (tid < 64) {
+                const bool          is_v = tid >= 32;
+                const int           d    = (tid & 31) * 4;
+                const __half*       src  = is_v ? vnew_s : knew_s;
+                const float         sc   = is_v ? p.v_scale : p.k_scale;
+                const float         zp   = is_v ? p.v_zp : p.k_zp;
+                uint32_t            w    = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // template.cuh:976-981: round(clamp((x - zp) / scale)), round = half away from zero
+                    float v = __fdiv_rn(__half2float(src[d + i]) - zp, sc);
+                    v       = fmaxf(-128.f, fminf(127.f, v));
+                    w |= ((uint32_t)(int)roundf(v) & 0xffu) << (8 * i);
+                }
+                *reinterpret_cast<uint32_t*>((is_v ? vd : kd) + d) = w;
+            }
+        }
+        else {
+            if (tid < 32) {
+                const int d = tid * 8;  // 16 bytes of K and of V per thread
+                *reinterpret_cast<uint4*>(kd + d * 2) = *reinterpret_cast<const uint4*>(knew_s + d);
+                *reinterpret_cast<uint4*>(vd + d * 2) = *reinterpret_cast<const uint4*>(vnew_s + d);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---------------------------------------------------------------- Q fragments, softmax state
+    uint32_t qf[8][2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d0 = qk_d0<INT8>(c, j);
+        qf[j][0]     = *reinterpret_cast<const uint32_t*>(q_s + g * kD + d0);
+        qf[j][1]     = *reinterpret_cast<const uint32_t*>(q_s + g * kD + d0 + 2);
+    }
+    // logits in log2 units: t = S_raw * alpha + beta[head]
+    const float alpha = (INT8 ? p.k_scale : 1.f) * p.inv_sqrt_dh * kLog2e;
+    float       beta[2];
+    beta[0] = INT8 ? p.k_zp * sumq_s[2 * c] * p.inv_sqrt_dh * kLog2e : 0.f;
+    beta[1] = INT8 ? p.k_zp * sumq_s[2 * c + 1] * p.inv_sqrt_dh * kLog2e : 0.f;
+
+    float m_run[2] = {-INFINITY, -INFINITY};  // heads 2c, 2c+1
+    float l_run[2] = {0.f, 0.f};              // this lane's share (token rows g, g+8)
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+
+    // ---------------------------------------------------------------- main loop over this warp's blocks
+    for (int blk = 0; blk < my_blocks; ++blk) {
+        cp_async_wait<NSTAGE - 2>();
+        __syncwarp();
+        const int            stage = blk % NSTAGE;
+        const unsigned char* ks    = my_ring + stage * 2 * TILEB;
+        const unsigned char* vs    = ks + TILEB;
+        const int            tok0  = s0 + (blk * kWarps + warp) * kBlockTok;
+
+        // ---- S^T = K . Q^T -------------------------------------------------------------
+        float st[4] = {0.f, 0.f, 0.f, 0.f};
+        if (INT8) {
+            uint32_t kw[2][8];  // [token g / g+8][step]
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int            tok = g + 8 * hh;
+                const unsigned char* row = ks + tok * ROWB;
+                const uint4          a   = lds128(row + (((2 * c) ^ (tok & 7)) << 4));
+                const uint4          b   = lds128(row + (((2 * c + 1) ^ (tok & 7)) << 4));
+                kw[hh][0] = a.x; kw[hh][1] = a.y; kw[hh][2] = a.z; kw[hh][3] = a.w;
+                kw[hh][4] = b.x; kw[hh][5] = b.y; kw[hh][6] = b.z; kw[hh][7] = b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t af[4];
+                s8x4_to_h2x2(kw[0][j] ^ kSignFlip, af[0], af[2]);
+                s8x4_to_h2x2(kw[1][j] ^ kSignFlip, af[1], af[3]);
+                mma_m16n8k16(st, af, qf[j][0], qf[j][1]);
+            }
+        }
+        else {
+            uint32_t kw[2][16];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int            tok = g + 8 * hh;
+                const unsigned char* row = ks + tok * ROWB;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const int   ch = 2 * c + (m & 1) + 8 * (m >> 1);
+                    const uint4 a  = lds128(row + ((ch ^ (tok & 7)) << 4));
+                    kw[hh][4 * m + 0] = a.x; kw[hh][4 * m + 1] = a.y; kw[hh][4 * m + 2] = a.z; kw[hh][4 * m + 3] = a.w;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t af[4] = {kw[0][2 * j], kw[1][2 * j], kw[0][2 * j + 1], kw[1][2 * j + 1]};
+                mma_m16n8k16(st, af, qf[j][0], qf[j][1]);
+            }
+        }
+
+        // ---- online softmax (heads 2c, 2c+1; token rows g, g+8) --------------------------
+        float t[4];
+        {
+            const bool v0 = tok0 + g < s1;
+            const bool v1 = tok0 + g + 8 < s1;
+            t[0]          = v0 ? fmaf(st[0], alpha, beta[0]) : -INFINITY;
+            t[1]          = v0 ? fmaf(st[1], alpha, beta[1]) : -INFINITY;
+            t[2]          = v1 ? fmaf(st[2], alpha, beta[0]) : -INFINITY;
+            t[3]          = v1 ? fmaf(st[3], alpha, beta[1]) : -INFINITY;
+        }
+        float mx[2] = {fmaxf(t[0], t[2]), fmaxf(t[1], t[3])};
+#pragma unroll
+        for (int m = 4; m <= 16; m <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], m));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], m));
+        }
+        float scale[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const float m_new = fmaxf(m_run[e], mx[e]);  // finite: token tok0 of the block is valid
+            scale[e]          = exp2f(m_run[e] - m_new);
+            m_run[e]          = m_new;
+        }
+        const float p0 = exp2f(t[0] - m_run[0]);
+        const float p1 = exp2f(t[1] - m_run[1]);
+        const float p2 = exp2f(t[2] - m_run[0]);
+        const float p3 = exp2f(t[3] - m_run[1]);
+        l_run[0]       = l_run[0] * scale[0] + p0 + p2;
+        l_run[1]       = l_run[1] * scale[1] + p1 + p3;
+        if (__any_sync(0xffffffffu, scale[0] != 1.f || scale[1] != 1.f)) {
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                acc[a][0] *= scale[0];
+                acc[a][1] *= scale[1];
+                acc[a][2] *= scale[0];
+                acc[a][3] *= scale[1];
+            }
+        }
+        // P^T as the B operand: (tokens 2c, 2c+1 | head g) and (tokens 2c+8, 2c+9 | head g)
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
+
+        // ---- O^T += V^T . P^T ------------------------------------------------------------
+        const int tk[4] = {2 * c, 2 * c + 1, 2 * c + 8, 2 * c + 9};
+        if (INT8) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int wd = g + 8 * q;  // 4-byte word of the row: head-dim 4wd .. 4wd+3
+                uint32_t  w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    w[e] = lds32(vs + tk[e] * ROWB + ((((wd >> 2) ^ (tk[e] & 7)) << 4) | ((wd & 3) << 2))) ^ kSignFlip;
+                }
+                // interleave token pairs: [a0 b0 a1 b1], [a2 b2 a3 b3]
+                const uint32_t ab_lo = prmt(w[0], w[1], 0x5140), ab_hi = prmt(w[0], w[1], 0x7362);
+                const uint32_t cd_lo = prmt(w[2], w[3], 0x5140), cd_hi = prmt(w[2], w[3], 0x7362);
+                uint32_t       af[4], bfm[4];
+                // rows g -> d = 4wd, rows g+8 -> d = 4wd+1
+                s8x4_to_h2x2(ab_lo, af[0], af[1]);
+                s8x4_to_h2x2(cd_lo, af[2], af[3]);
+                mma_m16n8k16(acc[2 * q], af, pb0, pb1);
+                // rows g -> d = 4wd+2, rows g+8 -> d = 4wd+3
+                s8x4_to_h2x2(ab_hi, bfm[0], bfm[1]);
+                s8x4_to_h2x2(cd_hi, bfm[2], bfm[3]);
+                mma_m16n8k16(acc[2 * q + 1], bfm, pb0, pb1);
+            }
+        }
+        else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int wd = g + 8 * q;  // 4-byte word of the row: head-dim 2wd, 2wd+1
+                uint32_t  w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    w[e] = lds32(vs + tk[e] * ROWB + ((((wd >> 2) ^ (tk[e] & 7)) << 4) | ((wd & 3) << 2)));
+                }
+                const uint32_t af[4] = {prmt(w[0], w[1], 0x5410), prmt(w[0], w[1], 0x7632), prmt(w[2], w[3], 0x5410),
+                                        prmt(w[2], w[3], 0x7632)};
+                mma_m16n8k16(acc[q], af, pb0, pb1);
+            }
+        }
+
+        __syncwarp();
+        if (blk + NSTAGE - 1 < my_blocks) {
+            issue_block(blk + NSTAGE - 1, (blk + NSTAGE - 1) % NSTAGE);
+        }
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---------------------------------------------------------------- merge the warps (ring is free now)
+    // part[w]: m[8] | l[8] | o[8 heads][128]   (fp32, real units)
+    float* part = reinterpret_cast<float*>(ring);
+    constexpr int kPartFloats = 16 + kHeadsPerCta * kD;
+    {
+        float l0 = l_run[0], l1 = l_run[1];
+#pragma unroll
+        for (int m = 4; m <= 16; m <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, m);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, m);
+        }
+        float* mine = part + warp * kPartFloats;
+        if (g == 0) {
+            mine[2 * c]         = m_run[0];
+            mine[2 * c + 1]     = m_run[1];
+            mine[8 + 2 * c]     = l0;
+            mine[8 + 2 * c + 1] = l1;
+        }
+        const float vs0 = INT8 ? p.v_scale : 1.f;
+        const float vz  = INT8 ? p.v_zp : 0.f;
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            // row mapping of accumulator a: int8: d = 4(g + 8(a/2)) + 2(a&1) + {0,1}; fp16: d = 2(g + 8a) + {0,1}
+            const int d = INT8 ? 4 * (g + 8 * (a >> 1)) + 2 * (a & 1) : 2 * (g + 8 * a);
+            float*    o = mine + 16;
+            o[(2 * c) * kD + d]         = fmaf(vs0, acc[a][0], vz * l0);
+            o[(2 * c + 1) * kD + d]     = fmaf(vs0, acc[a][1], vz * l1);
+            o[(2 * c) * kD + d + 1]     = fmaf(vs0, acc[a][2], vz * l0);
+            o[(2 * c + 1) * kD + d + 1] = fmaf(vs0, acc[a][3], vz * l1);
+        }
+    }
+    __syncthreads();
+
+    // thread = head-dim index; loop over heads
+    const int d = tid;
+    float     M[kHeadsPerCta], L[kHeadsPerCta], O[kHeadsPerCta];
+#pragma unroll
+    for (int h = 0; h < kHeadsPerCta; ++h) {
+        float mm = last_split ? snew_s[h] : -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * kPartFloats + h]);
+        float ll = 0.f, oo = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float f = exp2f(part[w * kPartFloats + h] - mm);  // exp2(-inf) = 0 for idle warps
+            ll += part[w * kPartFloats + 8 + h] * f;
+            oo += part[w * kPartFloats + 16 + h * kD + d] * f;
+        }
+        if (last_split) {
+            const float f = exp2f(snew_s[h] - mm);
+            ll += f;
+            // the reference multiplies the fp16-rounded probability with the un-quantised v
+            oo += f * __half2float(vnew_s[d]);
+        }
+        M[h] = mm;
+        L[h] = ll;
+        O[h] = oo;
+    }
+
+    if (n_split == 1) {
+#pragma unroll
+        for (int h = 0; h < kHeadsPerCta; ++h) {
+            if (h < nheads) {
+                // template.cuh:1662: 1 / (sum + 1e-6)
+                p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(O[h] / (L[h] + 1.e-6f));
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- merge the splits
+    constexpr int kRec = 2 + kD;  // m | l | o[128]
+#pragma unroll
+    for (int h = 0; h < kHeadsPerCta; ++h) {
+        if (h < nheads) {
+            float* rec = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits + split) * kRec;
+            if (d == 0) {
+                __stcg(rec, M[h]);
+                __stcg(rec + 1, L[h]);
+            }
+            __stcg(rec + 2 + d, O[h]);
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int*      counter = p.counters + (size_t)bi * gridDim.y + blockIdx.y;
+        const int ticket  = atomicAdd(counter, 1);
+        const int is_last = ticket == n_split - 1;
+        if (is_last) {
+            *counter = 0;  // self-reset for the next launch
+        }
+        flag_s[0] = is_last;
+    }
+    __syncthreads();
+    if (!flag_s[0]) {
+        return;
+    }
+    __threadfence();
+    for (int h = 0; h < nheads; ++h) {
+        const float* rec0 = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits) * kRec;
+        float        mm   = -INFINITY;
+        for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(rec0 + (size_t)s * kRec));
+        float ll = 0.f, oo = 0.f;
+        for (int s = 0; s < n_split; ++s) {
+            const float* rec = rec0 + (size_t)s * kRec;
+            const float  f   = exp2f(__ldcg(rec) - mm);
+            ll += __ldcg(rec + 1) * f;
+            oo += __ldcg(rec + 2 + d) * f;
+        }
+        p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(oo / (ll + 1.e-6f));
+    }
+}
+
+template<bool INT8>
+constexpr size_t mmha_smem_bytes()
+{
+    constexpr int ROWB   = INT8 ? kD : 2 * kD;
+    constexpr int NSTAGE = INT8 ? 4 : 3;
+    return (size_t)kWarps * NSTAGE * 2 * kBlockTok * ROWB + (kHeadsPerCta + 2) * kD * 2 + 2 * kHeadsPerCta * 4 + 16;
+}
+
+}  // namespace
+
+cudaError_t mmha_prepare()
+{
+    cudaError_t e = cudaFuncSetAttribute(
+        mmha_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmha_smem_bytes<true>());
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(
+        mmha_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmha_smem_bytes<false>());
+}
+
+MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk)
+{
+    MmhaPlan  pl{};
+    const int rep = H / Hkv;
+    pl.head_blocks = (rep + kHeadsPerCta - 1) / kHeadsPerCta;
+    const long long items = (long long)B * Hkv * pl.head_blocks;
+    int             chunk = want_chunk;
+    if (chunk <= 0) {
+        // aim at ~8 CTAs per SM over the whole grid, 64..512 tokens per split
+        long long c = ((long long)max_len * items) / ((long long)sm_count * 8);
+        chunk       = (int)((c + 63) / 64 * 64);
+        if (chunk < 64) chunk = 64;
+        if (chunk > 512) chunk = 512;
+    }
+    chunk         = (chunk + 63) / 64 * 64;
+    pl.chunk      = chunk;
+    pl.max_splits = max_len > 0 ? (max_len + chunk - 1) / chunk : 1;
+    if (pl.max_splits < 1) pl.max_splits = 1;
+    pl.ws_floats    = (size_t)B * H * pl.max_splits * (2 + kD);
+    pl.counter_ints = (size_t)B * Hkv * pl.head_blocks;
+    return pl;
+}
+
+cudaError_t mmha_launch(const MmhaPlan& pl, MmhaParams p, bool int8, cudaStream_t st)
+{
+    p.chunk      = pl.chunk;
+    p.max_splits = pl.max_splits;
+    dim3 grid(pl.max_splits, p.Hkv * pl.head_blocks, p.B);
+    dim3 block(kWarps * 32);
+    if (int8) {
+        mmha_decode_kernel<true><<<grid, block, mmha_smem_bytes<true>(), st>>>(p);
+    }
+    else {
+        mmha_decode_kernel<false><<<grid, block, mmha_smem_bytes<false>(), st>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace tmb

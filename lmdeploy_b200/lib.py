@@ -39,6 +39,23 @@ lib = _load()
 
 _vp, _i, _sz, _u32p = C.c_void_p, C.c_int, C.c_size_t, C.c_void_p
 
+class TmMmhaParams(C.Structure):
+    """ctypes mirror of ``tm_mmha_params`` (include/tm_b200.h), field for field."""
+    _fields_ = [
+        ("out", C.c_void_p), ("q", C.c_void_p), ("q_bias", C.c_void_p), ("k", C.c_void_p), ("k_bias", C.c_void_p),
+        ("v", C.c_void_p), ("v_bias", C.c_void_p),
+        ("stride", C.c_int), ("batch_size", C.c_int), ("memory_max_len", C.c_int), ("num_heads", C.c_int),
+        ("num_kv_heads", C.c_int), ("hidden_size_per_head", C.c_int), ("rotary_embedding_dim", C.c_int),
+        ("timestep", C.c_int), ("inv_sqrt_dh", C.c_float), ("total_padding_tokens", C.c_void_p),
+        ("int8_mode", C.c_int), ("attention_k_scale", C.c_float), ("attention_k_zp", C.c_float),
+        ("attention_v_scale", C.c_float), ("attention_v_zp", C.c_float),
+        ("finished", C.c_void_p), ("length_per_sample", C.c_void_p), ("k_cache_per_sample", C.c_void_p),
+        ("v_cache_per_sample", C.c_void_p), ("kv_cache_per_sample_offset", C.c_size_t),
+        ("max_position_embeddings", C.c_int), ("use_dynamic_ntk", C.c_int), ("use_logn_attn", C.c_int),
+        ("rotary_embedding_base", C.c_float),
+    ]
+
+
 # name -> (restype, argtypes); must list every symbol declared in include/tm_b200.h
 SIGNATURES = {
     "tm_create": (_i, [C.POINTER(_vp), _i]),
@@ -54,6 +71,9 @@ SIGNATURES = {
     "tm_transpose_qk_s4_k_m8_hf": (_i, [_u32p, _u32p, _i, _i, _i, _vp]),
     "tm_fuse_w1_w3_s4_k_m8": (_i, [_u32p, _u32p, _i, _i, _vp]),
     "tm_dequantize_s4": (_i, [_vp, _u32p, _sz, _vp]),
+    "tm_mmha_decode": (_i, [_vp, C.POINTER(TmMmhaParams), _vp]),
+    "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
+    "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
 }
 
 

@@ -5,6 +5,10 @@ Same names, argument order and meaning as lmdeploy v0.0.9:
 * ``GemmS4F16.Run``            src/turbomind/kernels/gemm_s_f16/gemm_s4_f16.h:41-51
 * ``LlamaDenseWeight`` / ``WeightType``   src/turbomind/models/llama/LlamaDenseWeight.h:28-63
 * ``LlamaLinear.forward``      src/turbomind/models/llama/LlamaLinear.h:28-42
+* ``masked_multihead_attention`` + ``Masked_multihead_attention_params``
+                               src/turbomind/kernels/decoder_masked_multihead_attention.h:50-133
+* ``invokeRootMeanSquareNorm`` src/turbomind/models/llama/llama_kernels.cu:69-79
+* ``invokeFusedAddBiasResidualRMSNorm``  src/turbomind/models/llama/llama_decoder_kernels.cu:147-160
 * ``transpose_qk_s4_k_m8`` / ``fuse_w1_w3_s4_k_m8`` / ``convert_s4_k_m8`` / ``dequantize_s4``
                                the ``_turbomind`` helpers of src/turbomind/python/bind.cpp:414-465
 
@@ -119,3 +123,90 @@ def dequantize_s4(src, dst):
     if src.numel() * 8 != dst.numel():
         raise ValueError("dst must hold 8 halves per source word")  # bind.cpp:462
     _l.check(_l.lib.tm_dequantize_s4(_ptr(dst), _ptr(src), src.numel(), _stream()), "dequantize_s4")
+
+
+# ---- decode attention -----------------------------------------------------------------------
+
+QUANT_POLICY_CACHE_KV_INT8 = 0x04  # QuantPolicy::kCacheKVInt8, src/turbomind/models/llama/llama_utils.h:12-20
+
+
+@dataclass
+class Masked_multihead_attention_params:
+    """The fields ``fusedQKV_masked_attention_dispatch`` fills
+    (LlamaDecoderSelfAttentionLayer.cc:87-161); tensors instead of raw pointers.  ``q``, ``k``,
+    ``v`` are views into one fused ``[batch, stride]`` half buffer."""
+    out: torch.Tensor = None
+    q: torch.Tensor = None
+    k: torch.Tensor = None
+    v: torch.Tensor = None
+    q_bias: Optional[torch.Tensor] = None
+    k_bias: Optional[torch.Tensor] = None
+    v_bias: Optional[torch.Tensor] = None
+    stride: int = 0
+    batch_size: int = 0
+    memory_max_len: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    hidden_size_per_head: int = 128
+    rotary_embedding_dim: int = 128
+    rotary_embedding_base: float = 10000.0
+    max_position_embeddings: int = 0
+    use_dynamic_ntk: bool = False
+    use_logn_attn: bool = False
+    timestep: int = 0
+    inv_sqrt_dh: float = 0.0
+    total_padding_tokens: Optional[torch.Tensor] = None   # int32 [batch]
+    finished: Optional[torch.Tensor] = None               # bool [batch]
+    length_per_sample: torch.Tensor = None                # int32 [batch]
+    k_cache_per_sample: torch.Tensor = None               # int64 [batch] device array of base pointers
+    v_cache_per_sample: torch.Tensor = None
+    kv_cache_per_sample_offset: int = 0
+    int8_mode: int = 0
+    attention_k_scale: float = 0.0
+    attention_k_zp: float = 0.0
+    attention_v_scale: float = 0.0
+    attention_v_zp: float = 0.0
+
+
+def masked_multihead_attention(params: Masked_multihead_attention_params, stream=None, handle=None):
+    p = params
+    _need_cuda(p.out, p.length_per_sample, p.k_cache_per_sample, p.v_cache_per_sample, p.total_padding_tokens,
+               p.finished)
+    for t in (p.q, p.k, p.v):
+        if t is None or not t.is_cuda:
+            raise ValueError("q, k, v must be CUDA tensors")
+    c = _l.TmMmhaParams()
+    c.out, c.q, c.k, c.v = p.out.data_ptr(), p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr()
+    c.q_bias = 0 if p.q_bias is None else p.q_bias.data_ptr()
+    c.k_bias = 0 if p.k_bias is None else p.k_bias.data_ptr()
+    c.v_bias = 0 if p.v_bias is None else p.v_bias.data_ptr()
+    c.stride, c.batch_size, c.memory_max_len = p.stride, p.batch_size, p.memory_max_len
+    c.num_heads, c.num_kv_heads, c.hidden_size_per_head = p.num_heads, p.num_kv_heads, p.hidden_size_per_head
+    c.rotary_embedding_dim, c.timestep, c.inv_sqrt_dh = p.rotary_embedding_dim, p.timestep, p.inv_sqrt_dh
+    c.total_padding_tokens = 0 if p.total_padding_tokens is None else p.total_padding_tokens.data_ptr()
+    c.int8_mode = p.int8_mode
+    c.attention_k_scale, c.attention_k_zp = p.attention_k_scale, p.attention_k_zp
+    c.attention_v_scale, c.attention_v_zp = p.attention_v_scale, p.attention_v_zp
+    c.finished = 0 if p.finished is None else p.finished.data_ptr()
+    c.length_per_sample = p.length_per_sample.data_ptr()
+    c.k_cache_per_sample, c.v_cache_per_sample = p.k_cache_per_sample.data_ptr(), p.v_cache_per_sample.data_ptr()
+    c.kv_cache_per_sample_offset = p.kv_cache_per_sample_offset
+    c.max_position_embeddings, c.use_dynamic_ntk, c.use_logn_attn = (p.max_position_embeddings, int(p.use_dynamic_ntk),
+                                                                      int(p.use_logn_attn))
+    c.rotary_embedding_base = p.rotary_embedding_base
+    h = handle or _l.default_handle(p.out.device.index)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_mmha_decode(h.ptr, C.byref(c), st), "masked_multihead_attention")
+
+
+def invokeRootMeanSquareNorm(out, input, scale, eps, m, n, stream=None):
+    _need_cuda(out, input, scale)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_rmsnorm(_ptr(out), _ptr(input), _ptr(scale), eps, m, n, st), "invokeRootMeanSquareNorm")
+
+
+def invokeFusedAddBiasResidualRMSNorm(residual, in_out, bias, scale, eps, batch_size, n_dims, stream=None):
+    _need_cuda(residual, in_out, bias, scale)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_add_residual_rmsnorm(_ptr(residual), _ptr(in_out), _ptr(bias), _ptr(scale), eps, batch_size,
+                                            n_dims, st), "invokeFusedAddBiasResidualRMSNorm")
