@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
             }
         }
         else {
-            if (tid < 32) {
+            if (tid < kD / 8) {
                 const int d = tid * 8;  // 16 bytes of K and of V per thread
                 *reinterpret_cast<uint4*>(kd + d * 2) = *reinterpret_cast<const uint4*>(knew_s + d);
                 *reinterpret_cast<uint4*>(vd + d * 2) = *reinterpret_cast<const uint4*>(vnew_s + d);

@@ -115,7 +115,7 @@ class Handle:
         w = C.c_uint(0)
         st = lib.tm_check_device_status(self._h, _vp(stream), C.byref(w))
         if st != TM_OK:
-            raise TmError(st, f"device status word 0x{w.value:x}")
+            raise TmError(st, f"device status word 0x{w.value:x}, cudaError {lib.tm_last_cuda_error(self._h)}")
 
     def close(self):
         if self._h:

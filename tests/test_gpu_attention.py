@@ -98,7 +98,9 @@ def check_cache(got, want, int8, lengths, S_max, finished=None):
             assert d.max() <= 1 and (d != 0).mean() < 0.02, "int8 row differs by more than 1 LSB / too often"
         else:
             d = np.abs(g[:, slot].astype(np.float32) - w[:, slot].astype(np.float32))
-            assert (d <= 2.0 ** -9 * np.abs(w[:, slot].astype(np.float32)) + 1e-6).all(), "appended fp16 row off by > 2 ulp"
+            # RoPE mixes the two elements of a pair, so the error scale is the pair's magnitude (|x| ~ 1
+            # here, angle error ~ position * 1e-7), not the magnitude of the single rotated element
+            assert (d <= 2.0 ** -9 * np.abs(w[:, slot].astype(np.float32)) + 2e-3).all(), "appended fp16 row is off"
 
 
 @pytest.mark.parametrize("int8", [False, True])
