@@ -208,6 +208,88 @@ def run_gemm_workload(args, rank, world, device):
     return out
 
 
+def mmha_bytes(lengths, H, Hkv, e):
+    """algorithmic bytes of one decode-attention call (KV counted once per KV head)."""
+    B = len(lengths)
+    return int(sum(2 * Hkv * int(L) * 128 * e for L in lengths) + B * (H + 2 * Hkv) * 128 * 2 + B * H * 128 * 2
+               + B * 2 * Hkv * 128 * e)
+
+
+def run_mmha_workload(args, rank, world, device):
+    """Decode attention, batch 64, 32 heads of 128, KV length ~ U[128, 4096], int8 or fp16 cache.
+    Inputs larger than L2: one call reads ~1.1 GB (int8) / ~2.2 GB (fp16) of cache."""
+    import math
+    from lmdeploy_b200 import turbomind as tm
+    from lmdeploy_b200 import lib as l
+    torch.cuda.set_device(device)
+    h = l.default_handle(device)
+    B, H, Hkv, D, S_max = args.batch, args.heads, args.kv_heads, 128, 4224
+    int8 = args.kv == "int8"
+    rng = np.random.default_rng(1234 + rank)
+    lengths = rng.integers(128, 4097, size=B).astype(np.int32)
+    g = torch.Generator(device=device).manual_seed(7 + rank)
+    if int8:
+        kc = torch.randint(-127, 128, (B, Hkv, S_max, D), dtype=torch.int8, device=device, generator=g)
+        vc = torch.randint(-127, 128, (B, Hkv, S_max, D), dtype=torch.int8, device=device, generator=g)
+    else:
+        kc = torch.randn(B, Hkv, S_max, D, device=device, generator=g).half()
+        vc = torch.randn(B, Hkv, S_max, D, device=device, generator=g).half()
+    kp = torch.tensor([kc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
+    vp = torch.tensor([vc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
+    qkv = torch.randn(B, (H + 2 * Hkv) * D, device=device, generator=g).half()
+    out = torch.empty(B, H * D, dtype=torch.float16, device=device)
+    ld = torch.from_numpy(lengths).to(device)
+    ts = int(lengths.max())
+    pad = torch.from_numpy((ts - lengths).astype(np.int32)).to(device)
+    p = tm.Masked_multihead_attention_params(
+        out=out, q=qkv, k=qkv[:, H * D:], v=qkv[:, (H + Hkv) * D:], stride=(H + 2 * Hkv) * D, batch_size=B,
+        memory_max_len=S_max, num_heads=H, num_kv_heads=Hkv, timestep=ts, inv_sqrt_dh=1.0 / math.sqrt(D),
+        total_padding_tokens=pad, length_per_sample=ld, k_cache_per_sample=kp, v_cache_per_sample=vp)
+    if int8:
+        p.int8_mode = tm.QUANT_POLICY_CACHE_KV_INT8
+        p.attention_k_scale = p.attention_v_scale = 4.0 / 127.0
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            tm.masked_multihead_attention(p)
+        h.check_device_status(stream.cuda_stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            tm.masked_multihead_attention(p)
+        graph.replay()
+        barrier(world)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier(world)
+        ms = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+        h.check_device_status(stream.cuda_stream)
+    ms = max_over_ranks(ms, world)
+    nbytes = mmha_bytes(lengths, H, Hkv, 1 if int8 else 2)
+    peaks = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) * 1e-9
+    return {
+        "metric": "decode MMHA HBM GB/s vs peak", "value": round(gbs * world, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": f"f16 q, {args.kv} KV, f32 softmax/accumulate",
+        "data": "synthetic",
+        "config": {"workload": "mmha", "batch": B, "heads": H, "kv_heads": Hkv, "kv": args.kv,
+                   "kv_len": "uniform 128..4096", "l2": "inputs larger than L2 (one call reads > 1 GB of KV cache)",
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "kernel": "mmha_decode_kernel", "achieved": round(gbs, 1),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                     "peak_source": peaks["source"], "traffic": None},
+        "clocks": clocks, "gpu_launches": args.steps,
+    }
+
+
 def barrier(world):
     if world > 1:
         torch.distributed.barrier()
@@ -229,6 +311,10 @@ def main():
     ap.add_argument("--workload", default="gemm")
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=32)
+    ap.add_argument("--kv", default="int8", choices=["int8", "fp16"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -240,6 +326,8 @@ def main():
 
     if args.workload == "gemm":
         out = run_gemm_workload(args, rank, world, local)
+    elif args.workload == "mmha":
+        out = run_mmha_workload(args, rank, world, local)
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     if rank == 0:

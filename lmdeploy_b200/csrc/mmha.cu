@@ -82,11 +82,14 @@ constexpr uint32_t kMagic64  = 0x64646464u;  // high bytes of half 1024 + x
 constexpr uint32_t kBias1152 = 0x64806480u;  // half2{1152, 1152}: 1024 + 128
 constexpr uint32_t kSignFlip = 0x80808080u;
 
-// four int8 (one word, sign bits already flipped) -> two half2 of exact integers
+// four int8 (one word, sign bits already flipped) -> two half2 holding 1152 + value (exact in
+// fp16).  The constant 1152 is taken out again after the MMA, in fp32: from the scores through
+// the per-head sum of q, from the outputs through the sum of the probabilities.
+constexpr float kOffset = 1152.f;
 __device__ __forceinline__ void s8x4_to_h2x2(uint32_t x, uint32_t& lo, uint32_t& hi)
 {
-    lo = hsub2(prmt(x, kMagic64, 0x4140), kBias1152);
-    hi = hsub2(prmt(x, kMagic64, 0x4342), kBias1152);
+    lo = prmt(x, kMagic64, 0x4140);
+    hi = prmt(x, kMagic64, 0x4342);
 }
 
 // query-fragment column of lane c at MMA step j: the 4 consecutive head-dim indices d0..d0+3
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
 {
     constexpr int ROWB   = INT8 ? kD : 2 * kD;        // bytes per cached token row
     constexpr int CPR    = ROWB / 16;                 // 16-byte chunks per row
-    constexpr int NSTAGE = INT8 ? 4 : 3;
+    constexpr int NSTAGE = 3;
     constexpr int TILEB  = kBlockTok * ROWB;          // one K (or V) block of a warp
     constexpr int WARPB  = NSTAGE * 2 * TILEB;        // ring of one warp
 
@@ -156,22 +159,30 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
 
     // ---------------------------------------------------------------- KV ring: start the loads
     unsigned char* my_ring = ring + warp * WARPB;
+    // per-lane constants of the copy pattern: lane covers chunk (lane % CPR) of token rows
+    // (lane / CPR) + i * (32 / CPR)
+    constexpr int kRowsPerPass = 32 / CPR;
+    const int     cp_tok       = lane / CPR;
+    const int     cp_ch        = lane % CPR;
+    const int     slot_base    = s0 % p.S_max;  // ring slot of token s0
     auto issue_block = [&](int blk, int stage) {
-        // blk: index among this warp's blocks; absolute first token of the block:
-        const int      tok0 = s0 + (blk * kWarps + warp) * kBlockTok;
+        // blk: index among this warp's blocks; first token of the block relative to s0:
+        const int      rel0 = (blk * kWarps + warp) * kBlockTok;
         unsigned char* ks   = my_ring + stage * 2 * TILEB;
         unsigned char* vs   = ks + TILEB;
+        int            slot = slot_base + rel0 + cp_tok;  // < 3 * S_max: at most two wraps
+        if (slot >= p.S_max) slot -= p.S_max;
+        if (slot >= p.S_max) slot -= p.S_max;
 #pragma unroll
-        for (int i = 0; i < kBlockTok * CPR / 32; ++i) {
-            const int    id    = lane + 32 * i;
-            const int    tok   = id / CPR;
-            const int    ch    = id % CPR;
-            const int    ti    = tok0 + tok;
-            const bool   valid = ti < s1;
-            const size_t row   = valid ? (size_t)(ti % p.S_max) * ROWB : 0;
-            const int    dst   = tok * ROWB + ((ch ^ (tok & 7)) << 4);
-            cp_async16(ks + dst, kc + row + ch * 16, valid);
-            cp_async16(vs + dst, vc + row + ch * 16, valid);
+        for (int i = 0; i < kBlockTok / kRowsPerPass; ++i) {
+            const int      tok   = cp_tok + i * kRowsPerPass;
+            const bool     valid = s0 + rel0 + tok < s1;
+            const uint32_t src   = valid ? (uint32_t)slot * ROWB + cp_ch * 16 : 0u;
+            const int      dst   = tok * ROWB + ((cp_ch ^ (tok & 7)) << 4);
+            cp_async16(ks + dst, kc + src, valid);
+            cp_async16(vs + dst, vc + src, valid);
+            slot += kRowsPerPass;
+            if (slot >= p.S_max) slot -= p.S_max;
         }
     };
     const int my_blocks = (n_blocks > warp) ? (n_blocks - warp + kWarps - 1) / kWarps : 0;
@@ -313,14 +324,26 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
     // logits in log2 units: t = S_raw * alpha + beta[head]
     const float alpha = (INT8 ? p.k_scale : 1.f) * p.inv_sqrt_dh * kLog2e;
     float       beta[2];
-    beta[0] = INT8 ? p.k_zp * sumq_s[2 * c] * p.inv_sqrt_dh * kLog2e : 0.f;
-    beta[1] = INT8 ? p.k_zp * sumq_s[2 * c + 1] * p.inv_sqrt_dh * kLog2e : 0.f;
+    // int8: S_raw = sum_d q_d (1152 + k8_d); k = k8 * k_scale + k_zp
+    beta[0] = INT8 ? (p.k_zp - kOffset * p.k_scale) * sumq_s[2 * c] * p.inv_sqrt_dh * kLog2e : 0.f;
+    beta[1] = INT8 ? (p.k_zp - kOffset * p.k_scale) * sumq_s[2 * c + 1] * p.inv_sqrt_dh * kLog2e : 0.f;
 
     float m_run[2] = {-INFINITY, -INFINITY};  // heads 2c, 2c+1
     float l_run[2] = {0.f, 0.f};              // this lane's share (token rows g, g+8)
     float acc[8][4];
 #pragma unroll
     for (int a = 0; a < 8; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+    float psum[4] = {0.f, 0.f, 0.f, 0.f};  // int8: sum over tokens of the fp16 probabilities (every row alike)
+
+    // byte offset, inside a V tile, of word g of token rows 2c, 2c+1, 2c+8, 2c+9 (swizzled)
+    int v_off[4];
+    {
+        const int tk0[4] = {2 * c, 2 * c + 1, 2 * c + 8, 2 * c + 9};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v_off[e] = tk0[e] * ROWB + ((((g >> 2) ^ (tk0[e] & 7)) << 4) | ((g & 3) << 2));
+        }
+    }
 
     // ---------------------------------------------------------------- main loop over this warp's blocks
     for (int blk = 0; blk < my_blocks; ++blk) {
@@ -409,6 +432,8 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
                 acc[a][2] *= scale[0];
                 acc[a][3] *= scale[1];
             }
+            psum[0] *= scale[0];
+            psum[1] *= scale[1];
         }
         // P^T as the B operand: (tokens 2c, 2c+1 | head g) and (tokens 2c+8, 2c+9 | head g)
         const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
@@ -417,13 +442,18 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         // ---- O^T += V^T . P^T ------------------------------------------------------------
         const int tk[4] = {2 * c, 2 * c + 1, 2 * c + 8, 2 * c + 9};
         if (INT8) {
+            {
+                const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+                mma_m16n8k16(psum, ones, pb0, pb1);
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const int wd = g + 8 * q;  // 4-byte word of the row: head-dim 4wd .. 4wd+3
-                uint32_t  w[4];
+                // word wd = g + 8q of the row (head-dim 4wd .. 4wd+3); its swizzled address is the
+                // q = 0 address with bits 5..6 flipped by q
+                uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    w[e] = lds32(vs + tk[e] * ROWB + ((((wd >> 2) ^ (tk[e] & 7)) << 4) | ((wd & 3) << 2))) ^ kSignFlip;
+                    w[e] = lds32(vs + (v_off[e] ^ (q << 5))) ^ kSignFlip;
                 }
                 // interleave token pairs: [a0 b0 a1 b1], [a2 b2 a3 b3]
                 const uint32_t ab_lo = prmt(w[0], w[1], 0x5140), ab_hi = prmt(w[0], w[1], 0x7362);
@@ -442,11 +472,11 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         else {
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const int wd = g + 8 * q;  // 4-byte word of the row: head-dim 2wd, 2wd+1
-                uint32_t  w[4];
+                // word wd = g + 8q of the row (head-dim 2wd, 2wd+1)
+                uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    w[e] = lds32(vs + tk[e] * ROWB + ((((wd >> 2) ^ (tk[e] & 7)) << 4) | ((wd & 3) << 2)));
+                    w[e] = lds32(vs + (v_off[e] ^ (q << 5)));
                 }
                 const uint32_t af[4] = {prmt(w[0], w[1], 0x5410), prmt(w[0], w[1], 0x7632), prmt(w[2], w[3], 0x5410),
                                         prmt(w[2], w[3], 0x7632)};
@@ -483,15 +513,19 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         }
         const float vs0 = INT8 ? p.v_scale : 1.f;
         const float vz  = INT8 ? p.v_zp : 0.f;
+        // int8: acc = sum_t p16_t (1152 + v8); v = v8 * v_scale + v_zp.  psum (= sum_t p16_t) is the
+        // same in every accumulator row; columns are heads 2c, 2c+1.
+        const float off0 = INT8 ? kOffset * psum[0] : 0.f;
+        const float off1 = INT8 ? kOffset * psum[1] : 0.f;
 #pragma unroll
         for (int a = 0; a < 8; ++a) {
             // row mapping of accumulator a: int8: d = 4(g + 8(a/2)) + 2(a&1) + {0,1}; fp16: d = 2(g + 8a) + {0,1}
             const int d = INT8 ? 4 * (g + 8 * (a >> 1)) + 2 * (a & 1) : 2 * (g + 8 * a);
             float*    o = mine + 16;
-            o[(2 * c) * kD + d]         = fmaf(vs0, acc[a][0], vz * l0);
-            o[(2 * c + 1) * kD + d]     = fmaf(vs0, acc[a][1], vz * l1);
-            o[(2 * c) * kD + d + 1]     = fmaf(vs0, acc[a][2], vz * l0);
-            o[(2 * c + 1) * kD + d + 1] = fmaf(vs0, acc[a][3], vz * l1);
+            o[(2 * c) * kD + d]         = fmaf(vs0, acc[a][0] - off0, vz * l0);
+            o[(2 * c + 1) * kD + d]     = fmaf(vs0, acc[a][1] - off1, vz * l1);
+            o[(2 * c) * kD + d + 1]     = fmaf(vs0, acc[a][2] - off0, vz * l0);
+            o[(2 * c + 1) * kD + d + 1] = fmaf(vs0, acc[a][3] - off1, vz * l1);
         }
     }
     __syncthreads();
@@ -581,7 +615,7 @@ template<bool INT8>
 constexpr size_t mmha_smem_bytes()
 {
     constexpr int ROWB   = INT8 ? kD : 2 * kD;
-    constexpr int NSTAGE = INT8 ? 4 : 3;
+    constexpr int NSTAGE = 3;
     return (size_t)kWarps * NSTAGE * 2 * kBlockTok * ROWB + (kHeadsPerCta + 2) * kD * 2 + 2 * kHeadsPerCta * 4 + 16;
 }
 
@@ -604,11 +638,13 @@ MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_ch
     const long long items = (long long)B * Hkv * pl.head_blocks;
     int             chunk = want_chunk;
     if (chunk <= 0) {
-        // aim at ~8 CTAs per SM over the whole grid, 64..512 tokens per split
-        long long c = ((long long)max_len * items) / ((long long)sm_count * 8);
+        // A CTA pays a fixed start-up (q load, RoPE, pipeline fill) worth a few hundred tokens, so
+        // splits are kept long: about 16 CTAs per SM over the whole grid (4 resident at a time),
+        // 128..4096 tokens per split.
+        long long c = ((long long)max_len * items) / ((long long)sm_count * 16);
         chunk       = (int)((c + 63) / 64 * 64);
-        if (chunk < 64) chunk = 64;
-        if (chunk > 512) chunk = 512;
+        if (chunk < 128) chunk = 128;
+        if (chunk > 4096) chunk = 4096;
     }
     chunk         = (chunk + 63) / 64 * 64;
     pl.chunk      = chunk;
