@@ -290,6 +290,274 @@ def run_mmha_workload(args, rank, world, device):
     }
 
 
+DECODE_WORKLOADS = {
+    # name: (config attr, batch, prompt_lo, prompt_hi, new_tokens)
+    "decode7b": ("LLAMA2_7B", 64, 128, 1024, 256),
+    "decode70b": ("LLAMA2_70B", 128, 512, 512, 512),
+}
+
+
+def decode_step_bytes(cfg, tp, batch, mean_len, kv_bytes):
+    """algorithmic HBM bytes of one decode step on ONE rank: int4 weights + {zero, scale} of the four
+    projections of every layer, the lm-head slice, the KV cache at the current lengths."""
+    hid = cfg.hidden
+    shapes = [((cfg.head_num + 2 * cfg.kv_head_num) * 128 // tp, hid), (hid, hid // tp),
+              (2 * cfg.inter_size // tp, hid), (hid, cfg.inter_size // tp)]
+    w = sum(k * n // 2 + (k // 128) * n * 4 for n, k in shapes) * cfg.num_layer
+    head = cfg.vocab_size // tp * hid * 2
+    kv = batch * mean_len * 2 * cfg.num_layer * (cfg.kv_head_num // tp) * 128 * kv_bytes
+    return w + head + kv, w, head, kv
+
+
+def run_decode_workload(args, rank, world, device, name):
+    """Greedy decode of a random-init Llama-2 (W4A16, int8 KV): the prompts are consumed token by
+    token through the same decode path (teacher forced, aligned so that every sequence emits its first
+    new token at the same step), then `warmup` + `steps` decode steps; the timed region is `steps`
+    steps = steps * batch generated tokens."""
+    from lmdeploy_b200 import llama
+    from lmdeploy_b200 import lib as l
+    from lmdeploy_b200 import turbomind as tm
+    torch.cuda.set_device(device)
+    attr, B, p_lo, p_hi, new_tokens = DECODE_WORKLOADS[name]
+    cfg = getattr(llama, attr)
+    if args.batch_override:
+        B = args.batch_override
+    K, W = args.steps, args.warmup
+    rng = np.random.default_rng(2024)
+    prompt_len = rng.integers(p_lo, p_hi + 1, size=B).astype(np.int32)
+    if args.max_prompt:
+        prompt_len = np.minimum(prompt_len, args.max_prompt)
+    pmax = int(prompt_len.max())
+    max_steps = pmax + W + 2 * K + 8
+    session_len = ((pmax + max(new_tokens, W + 2 * K) + 8 + 63) // 64) * 64
+    comm = llama.Comm(world, rank, device) if world > 1 else None
+    t0 = time.time()
+    model = llama.LlamaModel(cfg, B, session_len, device, comm)
+    model.random_init(seed=0)
+    torch.cuda.synchronize()
+    t_init = time.time() - t0
+    start = (pmax - prompt_len).astype(np.int32)
+    forced = np.full((max_steps, B), -1, np.int32)
+    tokens = rng.integers(0, cfg.vocab_size, size=(pmax, B)).astype(np.int32)
+    for b in range(B):
+        forced[start[b]:pmax, b] = tokens[start[b]:pmax, b]
+    h = model.handle
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        st = model.new_state(B, max_steps, start, forced)
+        t0 = time.time()
+        model.decode(st, pmax, use_graph=True)            # prompts (not timed)
+        model.decode(st, W, use_graph=True)               # warm-up decode steps
+        h.check_device_status(stream.cuda_stream)
+        t_prefill = time.time() - t0
+        barrier(world)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        model.decode(st, K, use_graph=True)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier(world)
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        launches = model.last_launches()
+        h.check_device_status(stream.cuda_stream)
+        mean_len = float(st.lengths.float().mean().item()) - K / 2.0
+        assert int(st.step.item()) == pmax + W + K
+        assert bool((st.output_ids[pmax + W: pmax + W + K] >= 0).all()), "a sequence produced no token in the timed region"
+
+        # ---- end to end: one C-ABI call per step, host buffers in and out ---------------------
+        ids_host = torch.empty(B, dtype=torch.int32).pin_memory()
+        out_host = torch.empty(B, dtype=torch.int32).pin_memory()
+        ids_host.copy_(st.output_ids[pmax + W + K - 1].cpu())
+        torch.cuda.synchronize()
+        barrier(world)
+        w0 = time.perf_counter()
+        e0.record(stream)
+        for i in range(K):
+            s_idx = pmax + W + K + i
+            st.forced_ids[s_idx].copy_(ids_host, non_blocking=True)       # H2D: this step's input tokens
+            model.decode(st, 1, use_graph=True)
+            out_host.copy_(st.output_ids[s_idx], non_blocking=True)       # D2H: the picked tokens
+            stream.synchronize()
+            ids_host.copy_(out_host)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier(world)
+        ms_e2e = max((time.perf_counter() - w0) * 1e3, e0.elapsed_time(e1))
+
+        # ---- per-kernel device time on the same tensors (events around runs of launches) ------
+        per = time_decode_kernels(model, st, cfg, B, world, stream, tm, session_len)
+
+    ms_step = max_over_ranks(ms / K, world)
+    ms_e2e_step = max_over_ranks(ms_e2e / K, world)
+    peaks = measured_peaks()
+    kv_b = 1 if cfg.quant_policy & 4 else 2
+    total_b, w_b, head_b, kvb = decode_step_bytes(cfg, world, B, mean_len, kv_b)
+    dom = max(per.items(), key=lambda kv: kv[1]["us_per_step"])
+    out = {
+        "metric": "decode tokens/s Llama-2 W4A16", "value": round(B * 1e3 / ms_step, 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "int4 weights x f16 activations, f32 accumulate, int8 KV", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} W4A16 g128, int8 KV, greedy decode", "global_batch": B,
+                   "prompt_len": f"uniform {p_lo}..{p_hi}" if p_lo != p_hi else p_lo, "mean_kv_len_timed": round(mean_len, 1),
+                   "parallelism": f"tp{world}", "weights": "random init N(0,0.02), AWQ int4",
+                   "l2": "inputs larger than L2: every step streams all layer weights and the KV cache (GBs)"},
+        "e2e": {"value": round(B * 1e3 / ms_e2e_step, 1), "unit": "tokens/s", "h2d_bytes_per_step": B * 4,
+                "d2h_bytes_per_step": B * 4},
+        "roofline": {"bound": "hbm", "kernel": dom[0], "achieved": dom[1]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(dom[1]["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"], "traffic": None},
+        "step_roofline": {"bytes_per_step_per_gpu": int(total_b), "weights": int(w_b), "lm_head": int(head_b), "kv": int(kvb),
+                          "achieved_gbs_per_gpu": round(total_b / (ms_step * 1e-3) * 1e-9, 1),
+                          "frac_of_hbm_peak": round(total_b / (ms_step * 1e-3) * 1e-9 / peaks["hbm_gbs"], 4)},
+        "per_kernel": per, "clocks": clocks, "gpu_launches": int(launches),
+        "setup_s": {"weights": round(t_init, 1), "prompts_and_warmup": round(t_prefill, 1)},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_decode_baseline(cfg, B, int(mean_len), seconds=15.0)
+    model.close()
+    return out
+
+
+def time_decode_kernels(model, st, cfg, B, tp, stream, tm, session_len):
+    """Device time of the kernels of one decode step, each timed alone with CUDA events around a run
+    of launches on the model's own tensors (weights of a different layer every launch: larger than
+    L2 in total)."""
+    import math
+    dev = st.lengths.device
+    per = {}
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    layers = [model._keep[i:i + 6] for i in range(0, 6 * cfg.num_layer, 6)]   # norm, norm, qkv, o, w13, w2
+    op = tm.LlamaLinear(dev.index)
+    hid = cfg.hidden
+    names = [("gemm qkv", 2, False), ("gemm o", 3, False), ("gemm w13+silu", 4, True), ("gemm w2", 5, False)]
+    for nm, idx, fused in names:
+        w0 = layers[0][idx]
+        x = torch.randn(B, w0.input_dims, device=dev).half()
+        y = torch.empty(B, w0.output_dims // (2 if fused else 1), dtype=torch.float16, device=dev)
+        n_it = max(cfg.num_layer, 32)
+        for i in range(3):
+            op.forward(y, x, B, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm)
+        a, b = ev(), ev()
+        a.record(stream)
+        for i in range(n_it):
+            op.forward(y, x, B, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm)
+        b.record(stream)
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / n_it
+        nb = gemm_bytes(w0.output_dims, w0.input_dims, B, fused)
+        per[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1))
+    # attention over the caches as they stand (layer l of every sequence)
+    Hl, Hkvl = cfg.head_num // tp, cfg.kv_head_num // tp
+    qkv = torch.randn(B, (Hl + 2 * Hkvl) * 128, device=dev).half()
+    out = torch.empty(B, Hl * 128, dtype=torch.float16, device=dev)
+    lengths = st.lengths.clone()
+    p = tm.Masked_multihead_attention_params(
+        out=out, q=qkv, k=qkv[:, Hl * 128:], v=qkv[:, (Hl + Hkvl) * 128:], stride=(Hl + 2 * Hkvl) * 128, batch_size=B,
+        memory_max_len=session_len, num_heads=Hl, num_kv_heads=Hkvl, timestep=session_len - 1,
+        inv_sqrt_dh=1.0 / math.sqrt(128), length_per_sample=lengths, k_cache_per_sample=st.k_ptrs,
+        v_cache_per_sample=st.v_ptrs)
+    p.total_padding_tokens = (session_len - 1 - lengths).to(torch.int32)
+    if cfg.quant_policy & 4:
+        p.int8_mode, p.attention_k_scale, p.attention_v_scale = 4, 4.0 / 127, 4.0 / 127
+    n_it = max(cfg.num_layer, 32)
+    a, b = ev(), ev()
+    for rep in range(2):
+        a.record(stream)
+        for i in range(n_it):
+            p.kv_cache_per_sample_offset = (i % cfg.num_layer) * Hkvl * session_len * 128
+            tm.masked_multihead_attention(p)
+        b.record(stream)
+        torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / n_it
+    nb = mmha_bytes(lengths.cpu().numpy(), Hl, Hkvl, 1 if cfg.quant_policy & 4 else 2)
+    per["mmha_decode_kernel"] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1))
+    return per
+
+
+def cpu_decode_baseline(cfg, B, mean_len, seconds=15.0, layers_sample=1, threads=None):
+    """The reference's torch CPU path (pseudo-quant fp16 weights, fp32-accumulated linears, numpy
+    attention: the oracle) on a bounded sample: `layers_sample` decoder layers + the lm-head for one
+    batch step at KV length `mean_len`, repeated for about `seconds`; per-token time extrapolated
+    to the full depth."""
+    from oracle import attention as oa, awq as oawq, decoder as odec
+    if threads:
+        torch.set_num_threads(threads)
+    hid = cfg.hidden
+    g = torch.Generator().manual_seed(0)
+    small = dict(head_num=cfg.head_num, kv_head_num=cfg.kv_head_num, session_len=mean_len + 8, norm_eps=cfg.norm_eps,
+                 rope_theta=cfg.rope_theta)
+
+    def lin(n, k):
+        w = (torch.randn(n, k, generator=g) * 0.02).half()
+        return oawq.pseudo_quant_weight(oawq.quantize(w, 128), 128).t().contiguous().numpy()
+
+    layers = []
+    for _ in range(layers_sample):
+        layers.append(dict(attn_norm=np.ones(hid, np.float16), ffn_norm=np.ones(hid, np.float16),
+                           w_qkv=lin((cfg.head_num + 2 * cfg.kv_head_num) * 128, hid), w_o=lin(hid, hid),
+                           w13=lin(2 * cfg.inter_size, hid), w2=lin(hid, cfg.inter_size),
+                           kv_quant=oa.KvQuant(4.0 / 127, 0.0, 4.0 / 127, 0.0)))
+    rng = np.random.default_rng(0)
+    glob = dict(tok_embeddings=(rng.standard_normal((cfg.vocab_size, hid)) * 0.02).astype(np.float16),
+                output_norm=np.ones(hid, np.float16),
+                output_weight=(rng.standard_normal((cfg.vocab_size, hid)) * 0.02).astype(np.float16))
+    S = mean_len + 8
+    kc = [[rng.integers(-127, 128, size=(cfg.kv_head_num, S, 128), dtype=np.int8) for _ in range(B)] for _ in layers]
+    vc = [[rng.integers(-127, 128, size=(cfg.kv_head_num, S, 128), dtype=np.int8) for _ in range(B)] for _ in layers]
+    ids = rng.integers(0, cfg.vocab_size, size=B)
+    lengths = np.full(B, mean_len, np.int32)
+    odec.decode_step(ids, lengths, layers, glob, kc, vc, small)       # warm-up
+    t_head0 = time.perf_counter()
+    hfake = np.zeros((B, hid), np.float16)
+    _ = (torch.from_numpy(hfake).float() @ torch.from_numpy(glob["output_weight"]).float().t())
+    t_head = time.perf_counter() - t_head0
+    n, t0 = 0, time.perf_counter()
+    while True:
+        odec.decode_step(ids, lengths, layers, glob, kc, vc, small)
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or n >= 50:
+            break
+    t_step = el / n
+    t_layers = max(t_step - t_head, 1e-9) / layers_sample
+    t_full = t_layers * cfg.num_layer + t_head
+    return {"value": round(B / t_full, 3), "unit": "tokens/s", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+            "kind": "port",
+            "sample": f"{n} x one batch-{B} decode step of {layers_sample} of {cfg.num_layer} layers + lm-head at KV length "
+                      f"{mean_len} ({el:.1f} s of CPU work), per-token time extrapolated to {cfg.num_layer} layers"}
+
+
+def run_reference_arm(args, rank, world):
+    """`--impl reference`: the reference's CPU implementation of the path (torch pseudo-quant linears
+    + the attention restatement: the oracle port), all host threads, same config/metric/unit."""
+    if rank != 0:
+        return None
+    from lmdeploy_b200 import llama
+    name = "decode7b" if world == 1 and args.workload in ("decode", "decode7b") else "decode70b"
+    if args.workload in DECODE_WORKLOADS:
+        name = args.workload
+    attr, B, p_lo, p_hi, new_tokens = DECODE_WORKLOADS[name]
+    cfg = getattr(llama, attr)
+    mean_len = (p_lo + p_hi) // 2 + new_tokens // 2
+    torch.set_num_threads(os.cpu_count() or 1)
+    budget = min(120.0, max(10.0, 4.0 * (args.steps + args.warmup)))
+    cb = cpu_decode_baseline(cfg, B, mean_len, seconds=budget)
+    ms_step = B / cb["value"] * 1e3
+    return {"impl": "reference", "metric": "decode tokens/s Llama-2 W4A16", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 2),
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f16 pseudo-quant weights, f32 accumulate (torch CPU)", "data": "synthetic",
+            "config": {"workload": f"{cfg.name} W4A16 g128, int8 KV, greedy decode", "global_batch": B,
+                       "parallelism": "host cores"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
 def barrier(world):
     if world > 1:
         torch.distributed.barrier()
@@ -306,9 +574,13 @@ def max_over_ranks(v, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="gemm")
+    ap.add_argument("--workload", default="decode",
+                    help="decode (7B at 1 GPU, 70B tensor-parallel at N > 1) | decode7b | decode70b | gemm | mmha")
+    ap.add_argument("--batch-override", type=int, default=0, help="smaller batch for smoke runs")
+    ap.add_argument("--max-prompt", type=int, default=0, help="cap on the prompt length for smoke runs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--batch", type=int, default=64)
@@ -321,10 +593,18 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        out = run_reference_arm(args, rank, world)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        return
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    if args.workload == "gemm":
+    if args.workload in ("decode", "decode7b", "decode70b"):
+        name = args.workload if args.workload != "decode" else ("decode7b" if world == 1 else "decode70b")
+        out = run_decode_workload(args, rank, world, local, name)
+    elif args.workload == "gemm":
         out = run_gemm_workload(args, rank, world, local)
     elif args.workload == "mmha":
         out = run_mmha_workload(args, rank, world, local)

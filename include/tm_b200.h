@@ -158,6 +158,108 @@ TM_API int tm_rmsnorm(void* out, const void* in, const void* scale, float eps, i
 TM_API int tm_add_residual_rmsnorm(void* residual, void* in_out, const void* bias, const void* scale, float eps, int m,
                             int n, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Tensor-parallel communicator (one process per GPU; NCCL over NVLink).  Replaces
+ *   ftNcclAllReduceSum<half> / ftNcclAllGather (src/turbomind/utils/nccl_utils.h:94-99) and the
+ *   NcclParam set-up of src/turbomind/triton_backend/transformer_triton_backend.cpp:24-82.
+ * Rank 0 calls tm_comm_unique_id and hands the 128 bytes to the other ranks by any host channel.
+ * Collectives are issued on the caller's stream with no host synchronisation.
+ */
+typedef struct tm_comm tm_comm;
+TM_API int tm_comm_unique_id(void* id128);
+TM_API int tm_comm_create(tm_comm** out, int world_size, int rank, const void* id128, int device);
+TM_API int tm_comm_destroy(tm_comm* c);
+TM_API int tm_allreduce_sum_f16(tm_comm* c, void* buf, size_t count, void* stream);
+TM_API int tm_allgather(tm_comm* c, const void* send, void* recv, size_t bytes_per_rank, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * LLaMA decode driver: the per-step layer loop of LlamaDecoder::forward
+ *   (src/turbomind/models/llama/LlamaDecoder.cc:158-242) with
+ *   LlamaDecoderSelfAttentionLayer::forward (LlamaDecoderSelfAttentionLayer.cc:193-304),
+ *   LlamaFfnLayer::forward (LlamaFfnLayer.cc:66-116), the embedding lookup, lm-head and greedy
+ *   pick of LlamaV2 (LlamaV2.cc:184-201, 312-372), for int4 (W4A16) weights.
+ * Dimensions are GLOBAL; with tensor_para_size > 1 every rank holds the slices of
+ *   LlamaDecoderLayerWeight (LlamaDecoderLayerWeight.cc:30-79): qkv and w13 column-split
+ *   (this rank's q heads | k heads | v heads; gate/up interleaved), wo and w2 row-split, norms
+ *   and embeddings replicated, lm-head vocab-split.
+ * All weight pointers are caller-owned device memory that must outlive the model.
+ */
+typedef struct tm_llama_config {
+    int   head_num;
+    int   kv_head_num;
+    int   size_per_head; /* 128 */
+    int   inter_size;
+    int   num_layer;
+    int   vocab_size;
+    float norm_eps;
+    float rope_theta;
+    int   quant_policy; /* 4 = int8 KV cache, 0 = fp16 */
+    int   group_size;   /* 128 */
+    int   tensor_para_size;
+    int   tensor_para_rank;
+    int   max_batch_size;
+    int   session_len;  /* slots per sequence in the KV cache (memory_max_len) */
+} tm_llama_config;
+
+/* One decoder layer: the fields of LlamaDecoderLayerWeight (LlamaDecoderLayerWeight.h:60-64) that
+ * the int4 path uses.  qweight = runtime int4 layout, scales_zeros = half2 {64 + z, s}. */
+typedef struct tm_llama_layer_weights {
+    const void* self_attn_norm; /* half [hidden] */
+    const void* ffn_norm;       /* half [hidden] */
+    const void* qkv_qweight;
+    const void* qkv_scales_zeros;
+    const void* qkv_bias;       /* half [(H + 2 Hkv) * 128 / tp] or NULL */
+    const void* o_qweight;
+    const void* o_scales_zeros;
+    const void* w13_qweight;
+    const void* w13_scales_zeros;
+    const void* w2_qweight;
+    const void* w2_scales_zeros;
+    float       past_kv_scale[4]; /* k_scale, k_zp, v_scale, v_zp (LlamaDecoderLayerWeight.cc:296-306) */
+} tm_llama_layer_weights;
+
+typedef struct tm_llama tm_llama;
+TM_API int tm_llama_create(tm_llama** out, tm_handle* h, tm_comm* comm, const tm_llama_config* cfg);
+TM_API int tm_llama_destroy(tm_llama* m);
+TM_API int tm_llama_set_layer(tm_llama* m, int layer, const tm_llama_layer_weights* w);
+/* tok_embeddings half [vocab, hidden]; output_norm half [hidden]; output_weight half
+ * [vocab / tp (this rank's rows), hidden]. */
+TM_API int tm_llama_set_globals(tm_llama* m, const void* tok_embeddings, const void* output_norm, const void* output_weight);
+
+/* Decode state, all device memory owned by the caller:
+ *   k_cache_ptrs/v_cache_ptrs  [batch] base pointers; sequence b's cache is
+ *                              [num_layer][kv_head_num / tp][session_len][128]
+ *   sequence_lengths  int [batch]   tokens cached so far (updated by every step)
+ *   start_step        int [batch]   sequence b is inactive (skipped like a finished one) while
+ *                                   step < start_step[b]
+ *   forced_ids        int [max_steps][batch] or NULL: >= 0 forces the step's input token
+ *                                   (prompt tokens, teacher forcing), < 0 takes the previous pick
+ *   output_ids        int [max_steps][batch]  the token picked at every step (step major, as
+ *                                   src/turbomind/kernels/decoding_kernels.cu:69-106 stores ids)
+ *   step              int [1]       current step counter (updated by every step)
+ *   hidden_out        half [batch, hidden] or NULL: copy of the last normed hidden state
+ *   logits_out        float [batch, vocab] or NULL: copy of the logits (after the all-gather)
+ */
+typedef struct tm_llama_decode_state {
+    int         batch_size;
+    int         max_steps;
+    void**      k_cache_ptrs;
+    void**      v_cache_ptrs;
+    int*        sequence_lengths;
+    const int*  start_step;
+    const int*  forced_ids;
+    int*        output_ids;
+    int*        step;
+    void*       hidden_out;
+    float*      logits_out;
+} tm_llama_decode_state;
+
+/* Runs n_steps decode steps on `stream`.  With use_graph != 0 one step is captured into a CUDA
+ * graph on first use (per state/batch size) and replayed; the stream must not be capturing. */
+TM_API int tm_llama_decode(tm_llama* m, const tm_llama_decode_state* st, int n_steps, int use_graph, void* stream);
+/* Kernels (own + library) launched by the most recent tm_llama_decode call. */
+TM_API unsigned long long tm_llama_last_launches(const tm_llama* m);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,7 +81,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"] + nccl_l
+    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcublas"] + nccl_l
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode:
         sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

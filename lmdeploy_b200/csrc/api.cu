@@ -50,7 +50,7 @@ extern "C" int tm_create(tm_handle** out, int device)
         h->max_smem = (int)prop.sharedMemPerBlockOptin;
         h->l2_bytes = prop.l2CacheSize;
         // scratch: split-K partial tiles + self-resetting tickets, status word
-        h->scratch_bytes = 64u << 20;
+        h->scratch_bytes = 256u << 20;
         h->counter_ints  = 1u << 16;
         e                = cudaMalloc(&h->scratch, h->scratch_bytes);
     }
@@ -65,8 +65,10 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = cudaMalloc(&h->status, 256);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);
     if (e == cudaSuccess) e = gemm_small_prepare(h->max_smem);
+    if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    h->gemv_stages = env_int("TM_B200_GEMV_STAGES", 0);
+    h->gemv_stages   = env_int("TM_B200_GEMV_STAGES", 0);
+    h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
@@ -125,7 +127,13 @@ extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
     if (m <= 0 || n <= 0 || k <= 0 || k % 128 || m % 32) return 0;
     // device independent: the slot count grows with the grid, so plan for a grid no part exceeds
     GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024, 0);
-    return pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
+    size_t        b  = pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
+    if (n > 16) {
+        GemmTcPlan   tc = gemm_tc_plan(m, n < 128 ? n : 128, k, 256);
+        const size_t t  = tc.workspace_floats * sizeof(float) + tc.counter_ints * sizeof(int) + 256;
+        if (t > b) b = t;
+    }
+    return b;
 }
 
 extern "C" int tm_gemm_s4_f16(tm_handle*  h,
@@ -148,6 +156,46 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     if (group_size != 128 || k % 128 || m % 32) return TM_ERR_UNSUPPORTED;
     if (type != TM_GEMM_PLAIN && type != TM_GEMM_FUSED_SILU_FFN) return TM_ERR_UNSUPPORTED;
     if (type == TM_GEMM_FUSED_SILU_FFN && m % 64) return TM_ERR_UNSUPPORTED;
+
+    if (n >= h->gemm_tc_min_n) {
+        // tensor-core tiles; token ranges that would overflow the scratch go in several launches
+        const size_t n_out_tc = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;
+        int          per      = n;
+        for (;;) {
+            GemmTcPlan   pl   = gemm_tc_plan(m, per, k, h->sm_count);
+            const size_t c_b  = ((pl.counter_ints * sizeof(int) + 255) / 256) * 256;
+            const bool   fits = workspace ? workspace_bytes >= pl.workspace_floats * sizeof(float) + c_b :
+                                            (pl.workspace_floats * sizeof(float) <= h->scratch_bytes
+                                             && pl.counter_ints <= h->counter_ints);
+            if (fits) break;
+            if (per <= 128) return TM_ERR_WORKSPACE;
+            per = ((per / 2 + 127) / 128) * 128;
+        }
+        for (int t0 = 0; t0 < n; t0 += per) {
+            const int    nt = n - t0 < per ? n - t0 : per;
+            GemmTcPlan   pl = gemm_tc_plan(m, nt, k, h->sm_count);
+            GemmTcParams p{};
+            p.C          = (__half*)C + (size_t)t0 * n_out_tc;
+            p.A          = (const unsigned char*)A;
+            p.X          = (const unsigned char*)B + (size_t)t0 * k * 2;
+            p.Q          = (const unsigned char*)Q;
+            p.workspace  = workspace ? (float*)((char*)workspace + ((pl.counter_ints * sizeof(int) + 255) / 256) * 256) :
+                                       (float*)h->scratch;
+            p.counters   = workspace ? (int*)workspace : h->counters;
+            p.status     = h->status;
+            p.N          = m;
+            p.T          = nt;
+            p.K          = k;
+            p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+            cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
+            h->launches += 1;
+            if (e != cudaSuccess) {
+                h->last_cuda_error = (int)e;
+                return TM_ERR_CUDA;
+            }
+        }
+        return TM_OK;
+    }
 
     // One launch covers up to `n_launch` tokens; more tokens than the scratch can hold partial
     // tiles for are processed in several launches over consecutive token ranges.
@@ -202,7 +250,16 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     return TM_OK;
 }
 
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length);
+
 extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* stream)
+{
+    return tm_mmha_decode_impl(h, a, stream, 0);
+}
+
+// pos_from_length: the RoPE position of sequence b is length_per_sample[b] (what the engine's
+// timestep - padding evaluates to), so that nothing in the launch depends on the step number.
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length)
 {
     if (!h || !a) return TM_ERR_INVALID_ARG;
     if (!a->out || !a->q || !a->k || !a->v || !a->length_per_sample || !a->k_cache_per_sample || !a->v_cache_per_sample) {
@@ -262,6 +319,7 @@ extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* strea
     p.max_pos         = a->max_position_embeddings;
     p.use_dynamic_ntk = a->use_dynamic_ntk;
     p.use_logn        = a->use_logn_attn;
+    p.pos_from_length = pos_from_length;
     p.rope_base       = a->rotary_embedding_base > 0.f ? a->rotary_embedding_base : 10000.f;
     p.inv_sqrt_dh     = a->inv_sqrt_dh;
     p.k_scale         = a->attention_k_scale;

@@ -42,4 +42,37 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, i
 cudaError_t   gemm_small_prepare(int max_smem);
 cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st);
 
+// ---- tensor-core (tcgen05) kernel for more than 16 tokens ---------------------------------
+struct GemmTcParams {
+    __half*              C;
+    const unsigned char* A;
+    const unsigned char* X;
+    const unsigned char* Q;
+    float*               workspace;
+    int*                 counters;
+    unsigned*            status;
+    int                  N, T, K;
+    int                  fused_silu;
+    // filled in by gemm_tc_launch from the plan
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile;
+};
+
+struct GemmTcPlan {
+    int    token_tile;     // UMMA N: tokens per pass, multiple of 16, <= 128
+    int    t_chunks;       // passes over the weight (grid.y), 128 tokens each
+    int    n_col_tiles;    // 128-feature tiles
+    int    total_units;    // 128x128 weight units
+    int    units_per_cta;
+    int    ctas;
+    int    slots_per_chunk;
+    size_t smem_bytes;
+    size_t workspace_floats;
+    size_t counter_ints;
+};
+
+size_t      gemm_tc_smem_bytes(int token_tile);
+GemmTcPlan  gemm_tc_plan(int N, int T, int K, int sm_count);
+cudaError_t gemm_tc_prepare(int max_smem);
+cudaError_t gemm_tc_launch(const GemmTcPlan& plan, GemmTcParams p, cudaStream_t st);
+
 }  // namespace tmb

@@ -21,5 +21,6 @@ struct tm_handle {
     int                last_cuda_error = 0;
     unsigned long long launches        = 0;
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
+    int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
     int                gemv_stages     = 0;  // 0 = automatic; TM_B200_GEMV_STAGES overrides
 };

@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
             logn = log2f((float)(tlength + 1)) / log2f((float)p.max_pos);  // utils.h:854-860
         }
         const int   pad  = p.padding ? p.padding[bi] : 0;
-        const float pos  = (float)(p.timestep - pad);  // template.cuh:1391-1395
+        const float pos  = p.pos_from_length ? (float)tlength : (float)(p.timestep - pad);  // template.cuh:1391-1395
         const int   pr   = tid & 63;                    // pair index: elements 2pr, 2pr+1
         const int   part = tid >> 6;                    // 0 / 1: which rows this thread handles
         float       cs = 1.f, sn = 0.f;

@@ -18,6 +18,7 @@ struct MmhaParams {
     const unsigned char* finished;  // [B] or null
     const int*           padding;   // [B] or null (total_padding_tokens)
     int                  B, H, Hkv, stride, S_max, timestep, rot_dim, max_pos, use_dynamic_ntk, use_logn;
+    int                  pos_from_length;  // RoPE position = cached length (the decode driver; lets a CUDA graph be replayed)
     float                rope_base, inv_sqrt_dh, k_scale, k_zp, v_scale, v_zp;
     float*               ws;        // split partials
     int*                 counters;  // self-resetting tickets

@@ -56,6 +56,29 @@ class TmMmhaParams(C.Structure):
     ]
 
 
+class TmLlamaConfig(C.Structure):
+    """ctypes mirror of ``tm_llama_config``."""
+    _fields_ = [("head_num", C.c_int), ("kv_head_num", C.c_int), ("size_per_head", C.c_int), ("inter_size", C.c_int),
+                ("num_layer", C.c_int), ("vocab_size", C.c_int), ("norm_eps", C.c_float), ("rope_theta", C.c_float),
+                ("quant_policy", C.c_int), ("group_size", C.c_int), ("tensor_para_size", C.c_int),
+                ("tensor_para_rank", C.c_int), ("max_batch_size", C.c_int), ("session_len", C.c_int)]
+
+
+class TmLlamaLayerWeights(C.Structure):
+    """ctypes mirror of ``tm_llama_layer_weights``."""
+    _fields_ = [(n, C.c_void_p) for n in (
+        "self_attn_norm", "ffn_norm", "qkv_qweight", "qkv_scales_zeros", "qkv_bias", "o_qweight", "o_scales_zeros",
+        "w13_qweight", "w13_scales_zeros", "w2_qweight", "w2_scales_zeros")] + [("past_kv_scale", C.c_float * 4)]
+
+
+class TmLlamaDecodeState(C.Structure):
+    """ctypes mirror of ``tm_llama_decode_state``."""
+    _fields_ = [("batch_size", C.c_int), ("max_steps", C.c_int), ("k_cache_ptrs", C.c_void_p),
+                ("v_cache_ptrs", C.c_void_p), ("sequence_lengths", C.c_void_p), ("start_step", C.c_void_p),
+                ("forced_ids", C.c_void_p), ("output_ids", C.c_void_p), ("step", C.c_void_p),
+                ("hidden_out", C.c_void_p), ("logits_out", C.c_void_p)]
+
+
 # name -> (restype, argtypes); must list every symbol declared in include/tm_b200.h
 SIGNATURES = {
     "tm_create": (_i, [C.POINTER(_vp), _i]),
@@ -72,6 +95,17 @@ SIGNATURES = {
     "tm_fuse_w1_w3_s4_k_m8": (_i, [_u32p, _u32p, _i, _i, _vp]),
     "tm_dequantize_s4": (_i, [_vp, _u32p, _sz, _vp]),
     "tm_mmha_decode": (_i, [_vp, C.POINTER(TmMmhaParams), _vp]),
+    "tm_comm_unique_id": (_i, [_vp]),
+    "tm_comm_create": (_i, [C.POINTER(_vp), _i, _i, _vp, _i]),
+    "tm_comm_destroy": (_i, [_vp]),
+    "tm_allreduce_sum_f16": (_i, [_vp, _vp, _sz, _vp]),
+    "tm_allgather": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "tm_llama_create": (_i, [C.POINTER(_vp), _vp, _vp, C.POINTER(TmLlamaConfig)]),
+    "tm_llama_destroy": (_i, [_vp]),
+    "tm_llama_set_layer": (_i, [_vp, _i, C.POINTER(TmLlamaLayerWeights)]),
+    "tm_llama_set_globals": (_i, [_vp, _vp, _vp, _vp]),
+    "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
+    "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
     "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
 }

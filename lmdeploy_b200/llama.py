@@ -1,0 +1,177 @@
+"""Python face of the C++ decode driver (``tm_llama_*``): model set-up, tensor-parallel
+communicator, KV-cache slabs and the decode loop.  torch provides device memory, streams and the
+process group used to hand the NCCL id around; everything that computes is in ``libtm_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import awq
+from . import lib as _l
+from . import turbomind as tm
+
+
+@dataclass
+class LlamaConfig:
+    head_num: int
+    kv_head_num: int
+    inter_size: int
+    num_layer: int
+    vocab_size: int = 32000
+    size_per_head: int = 128
+    norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    quant_policy: int = 4          # int8 KV cache
+    group_size: int = 128
+    name: str = "llama"
+
+    @property
+    def hidden(self):
+        return self.head_num * self.size_per_head
+
+
+LLAMA2_7B = LlamaConfig(32, 32, 11008, 32, name="llama-2-7b")
+LLAMA2_70B = LlamaConfig(64, 8, 28672, 80, name="llama-2-70b")
+
+
+class Comm:
+    """tm_comm: one rank of the tensor-parallel group (NCCL)."""
+
+    def __init__(self, world: int, rank: int, device: int):
+        import torch.distributed as dist
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_ubyte * 128)()
+            _l.check(_l.lib.tm_comm_unique_id(buf), "tm_comm_unique_id")
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        if world > 1:
+            t = ident.cuda(device) if dist.get_backend() == "nccl" else ident
+            dist.broadcast(t, 0)
+            ident = t.cpu()
+        raw = (C.c_ubyte * 128)(*ident.tolist())
+        self._c = C.c_void_p()
+        _l.check(_l.lib.tm_comm_create(C.byref(self._c), world, rank, raw, device), "tm_comm_create")
+        self.world, self.rank = world, rank
+
+    @property
+    def ptr(self):
+        return self._c
+
+    def allreduce_sum_f16(self, t: torch.Tensor):
+        _l.check(_l.lib.tm_allreduce_sum_f16(self._c, t.data_ptr(), t.numel(), torch.cuda.current_stream().cuda_stream),
+                 "tm_allreduce_sum_f16")
+
+    def close(self):
+        if self._c:
+            _l.lib.tm_comm_destroy(self._c)
+            self._c = C.c_void_p()
+
+
+class LlamaModel:
+    """tm_llama + the tensors it points to."""
+
+    def __init__(self, cfg: LlamaConfig, max_batch_size: int, session_len: int, device: int = 0,
+                 comm: Optional[Comm] = None):
+        self.cfg, self.device, self.comm = cfg, device, comm
+        self.tp = comm.world if comm else 1
+        self.rank = comm.rank if comm else 0
+        self.session_len, self.max_batch_size = session_len, max_batch_size
+        self.handle = _l.default_handle(device)
+        c = _l.TmLlamaConfig(cfg.head_num, cfg.kv_head_num, cfg.size_per_head, cfg.inter_size, cfg.num_layer,
+                             cfg.vocab_size, cfg.norm_eps, cfg.rope_theta, cfg.quant_policy, cfg.group_size, self.tp,
+                             self.rank, max_batch_size, session_len)
+        self._m = C.c_void_p()
+        _l.check(_l.lib.tm_llama_create(C.byref(self._m), self.handle.ptr, comm.ptr if comm else None, C.byref(c)),
+                 "tm_llama_create")
+        self._keep: List[object] = []   # tensors the C side points to
+
+    # -- weights -----------------------------------------------------------------------------
+    def set_layer(self, l, attn_norm, ffn_norm, qkv: tm.LlamaDenseWeight, o: tm.LlamaDenseWeight,
+                  w13: tm.LlamaDenseWeight, w2: tm.LlamaDenseWeight, kv_scale=(1.0, 0.0, 1.0, 0.0)):
+        w = _l.TmLlamaLayerWeights()
+        w.self_attn_norm, w.ffn_norm = attn_norm.data_ptr(), ffn_norm.data_ptr()
+        w.qkv_qweight, w.qkv_scales_zeros = qkv.kernel.data_ptr(), qkv.scales_and_zeros.data_ptr()
+        w.qkv_bias = 0 if qkv.bias is None else qkv.bias.data_ptr()
+        w.o_qweight, w.o_scales_zeros = o.kernel.data_ptr(), o.scales_and_zeros.data_ptr()
+        w.w13_qweight, w.w13_scales_zeros = w13.kernel.data_ptr(), w13.scales_and_zeros.data_ptr()
+        w.w2_qweight, w.w2_scales_zeros = w2.kernel.data_ptr(), w2.scales_and_zeros.data_ptr()
+        w.past_kv_scale = (C.c_float * 4)(*kv_scale)
+        self._keep += [attn_norm, ffn_norm, qkv, o, w13, w2]
+        _l.check(_l.lib.tm_llama_set_layer(self._m, l, C.byref(w)), "tm_llama_set_layer")
+
+    def set_globals(self, tok_embeddings, output_norm, output_weight):
+        self._keep += [tok_embeddings, output_norm, output_weight]
+        _l.check(_l.lib.tm_llama_set_globals(self._m, tok_embeddings.data_ptr(), output_norm.data_ptr(),
+                                             output_weight.data_ptr()), "tm_llama_set_globals")
+
+    def random_init(self, seed: int = 0, kv_scale=(4.0 / 127, 0.0, 4.0 / 127, 0.0)):
+        """Random-init weights of this architecture: every linear W ~ N(0, 0.02) AWQ-quantised (group
+        128), norms 1, embeddings / lm-head ~ N(0, 0.02).  Each tensor-parallel rank draws its own
+        slices (seeded by layer and rank); replicated tensors are seeded by layer only."""
+        cfg, tp, dev = self.cfg, self.tp, torch.device("cuda", self.device)
+        hid = cfg.hidden
+        ones = torch.ones(hid, dtype=torch.float16, device=dev)
+        for l in range(cfg.num_layer):
+            g = torch.Generator(device=dev).manual_seed(seed * 1000003 + l * 131 + self.rank)
+            qkv = awq.random_linear((cfg.head_num + 2 * cfg.kv_head_num) * 128 // tp, hid, g)
+            o = awq.random_linear(hid, hid // tp, g)
+            w13 = awq.random_linear(2 * cfg.inter_size // tp, hid, g)
+            w2 = awq.random_linear(hid, cfg.inter_size // tp, g)
+            self.set_layer(l, ones, ones, qkv, o, w13, w2, kv_scale)
+        g = torch.Generator(device=dev).manual_seed(seed * 1000003 + 999983)
+        emb = (torch.randn(cfg.vocab_size, hid, device=dev, generator=g) * 0.02).half()
+        head = (torch.randn(cfg.vocab_size, hid, device=dev, generator=g) * 0.02).half()
+        lo = cfg.vocab_size // tp * self.rank
+        self.set_globals(emb, ones, head[lo: lo + cfg.vocab_size // tp].contiguous())
+
+    # -- decode state ------------------------------------------------------------------------
+    def new_state(self, batch: int, max_steps: int, start_step=None, forced_ids=None, keep_hidden=False,
+                  keep_logits=False):
+        return DecodeState(self, batch, max_steps, start_step, forced_ids, keep_hidden, keep_logits)
+
+    def decode(self, state: "DecodeState", n_steps: int, use_graph: bool = True, stream=None):
+        st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        _l.check(_l.lib.tm_llama_decode(self._m, C.byref(state.c), n_steps, int(use_graph), st), "tm_llama_decode")
+
+    def last_launches(self) -> int:
+        return int(_l.lib.tm_llama_last_launches(self._m))
+
+    def close(self):
+        if self._m:
+            _l.lib.tm_llama_destroy(self._m)
+            self._m = C.c_void_p()
+
+
+class DecodeState:
+    """Device buffers of ``tm_llama_decode_state`` (per-sequence KV slabs
+    ``[num_layer][kv_heads / tp][session_len][128]``, step-major id buffers)."""
+
+    def __init__(self, model: LlamaModel, batch, max_steps, start_step, forced_ids, keep_hidden, keep_logits):
+        cfg, dev = model.cfg, torch.device("cuda", model.device)
+        kvh = cfg.kv_head_num // model.tp
+        dt = torch.int8 if cfg.quant_policy & 4 else torch.float16
+        shape = (batch, cfg.num_layer, kvh, model.session_len, 128)
+        self.k_cache = torch.zeros(shape, dtype=dt, device=dev)
+        self.v_cache = torch.zeros(shape, dtype=dt, device=dev)
+        self.k_ptrs = torch.tensor([self.k_cache[b].data_ptr() for b in range(batch)], dtype=torch.int64, device=dev)
+        self.v_ptrs = torch.tensor([self.v_cache[b].data_ptr() for b in range(batch)], dtype=torch.int64, device=dev)
+        self.lengths = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.step = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.output_ids = torch.full((max_steps, batch), -1, dtype=torch.int32, device=dev)
+        self.start_step = None if start_step is None else torch.as_tensor(start_step, dtype=torch.int32).to(dev)
+        self.forced_ids = None if forced_ids is None else torch.as_tensor(forced_ids, dtype=torch.int32).to(dev).contiguous()
+        self.hidden = torch.zeros(batch, cfg.hidden, dtype=torch.float16, device=dev) if keep_hidden else None
+        self.logits = torch.zeros(batch, cfg.vocab_size, dtype=torch.float32, device=dev) if keep_logits else None
+        c = _l.TmLlamaDecodeState()
+        c.batch_size, c.max_steps = batch, max_steps
+        c.k_cache_ptrs, c.v_cache_ptrs = self.k_ptrs.data_ptr(), self.v_ptrs.data_ptr()
+        c.sequence_lengths, c.step, c.output_ids = self.lengths.data_ptr(), self.step.data_ptr(), self.output_ids.data_ptr()
+        c.start_step = 0 if self.start_step is None else self.start_step.data_ptr()
+        c.forced_ids = 0 if self.forced_ids is None else self.forced_ids.data_ptr()
+        c.hidden_out = 0 if self.hidden is None else self.hidden.data_ptr()
+        c.logits_out = 0 if self.logits is None else self.logits.data_ptr()
+        self.c = c

@@ -75,7 +75,7 @@ LLAMA7B = [("qkv", 12288, 4096), ("o", 4096, 4096), ("gate_up", 22016, 4096), ("
 
 
 @pytest.mark.parametrize("name,n,k", LLAMA7B)
-@pytest.mark.parametrize("t", [1, 8, 16])
+@pytest.mark.parametrize("t", [1, 8, 16, 17, 64, 128])
 def test_llama7b_projections(name, n, k, t):
     lin = _linear(n, k, 0)
     x = _x(t, k, t)
@@ -89,6 +89,23 @@ def test_llama70b_tp8_shapes(n, k):
     x = _x(5, k, 5)
     y = _run(lin, x, n, k)
     assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"70b/tp8 n={n} k={k}")
+
+
+@pytest.mark.parametrize("t", [129, 200, 512])
+def test_more_tokens_than_one_tile(t):
+    n, k = 4096, 4096
+    lin = _linear(n, k, 0)
+    x = _x(t, k, t)
+    assert_close(_run(lin, x, n, k), ogemm.gemm_s4_f16(x, lin["w_kn"]), f"o t={t}")
+
+
+def test_deterministic_and_repeatable_tensor_core_path():
+    n, k = 4096, 11008
+    lin = _linear(n, k, 0)
+    x = _x(64, k, 9)
+    a = _run(lin, x, n, k)
+    for _ in range(3):
+        assert np.array_equal(a.view(np.uint16), _run(lin, x, n, k).view(np.uint16))
 
 
 def test_deterministic_and_repeatable():

@@ -1,0 +1,118 @@
+"""GPU: the C++ decode driver (layer loop, embedding, lm-head, greedy pick, CUDA graph) against the
+numpy oracle, teacher-forced: the oracle free-runs, the GPU path is fed the oracle's token stream,
+and the normed hidden state and logits are compared step by step (max-abs 2e-2, mean-rel 1e-3 would
+be the single-kernel bar; through several layers the bound used is max-abs 3e-2 and mean-rel 5e-3).
+After every step the rows appended to the KV cache are compared (one LSB for int8) and the oracle
+continues from the GPU's cache, so that each step is judged on identical history."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oa
+from oracle import awq as oawq
+from oracle import decoder as odec
+from oracle import s4_format as f
+from tests.helpers import dev
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(head_num=4, kv_head_num=2, inter_size=1024, num_layer=2, vocab_size=1000, session_len=64, norm_eps=1e-6,
+           rope_theta=10000.0)
+
+
+def _linear(n, k, seed):
+    t, w_nk, _ = oawq.make_awq_linear(n, k, seed, 128, 0.05)
+    a, q = f.convert_s4_k_m8(t.qweight, t.scales, t.qzeros, n, k, 128)
+    return a, q, w_nk.t().contiguous().numpy()
+
+
+def build(int8):
+    from lmdeploy_b200 import llama, turbomind as tm
+    hid = CFG["head_num"] * 128
+    rng = np.random.default_rng(0)
+    kvq = oa.KvQuant(8.0 / 127, 0.0, 8.0 / 127, 0.0) if int8 else None
+    cfg = llama.LlamaConfig(CFG["head_num"], CFG["kv_head_num"], CFG["inter_size"], CFG["num_layer"], CFG["vocab_size"],
+                            quant_policy=4 if int8 else 0)
+    model = llama.LlamaModel(cfg, max_batch_size=4, session_len=CFG["session_len"], device=0)
+    layers = []
+    for l in range(CFG["num_layer"]):
+        an = (1 + 0.1 * rng.standard_normal(hid)).astype(np.float16)
+        fn = (1 + 0.1 * rng.standard_normal(hid)).astype(np.float16)
+        shapes = dict(w_qkv=((CFG["head_num"] + 2 * CFG["kv_head_num"]) * 128, hid), w_o=(hid, hid),
+                      w13=(2 * CFG["inter_size"], hid), w2=(hid, CFG["inter_size"]))
+        ow, dw = dict(attn_norm=an, ffn_norm=fn, kv_quant=kvq), {}
+        for i, (name, (n, k)) in enumerate(shapes.items()):
+            a, q, w = _linear(n, k, 100 * l + i)
+            ow[name] = w
+            dw[name] = tm.LlamaDenseWeight(k, n, dev(a, torch.int32), tm.WeightType.kINT4, None, dev(q), 128)
+        layers.append(ow)
+        scale = (kvq.k_scale, 0.0, kvq.v_scale, 0.0) if int8 else (1.0, 0.0, 1.0, 0.0)
+        model.set_layer(l, dev(an), dev(fn), dw["w_qkv"], dw["w_o"], dw["w13"], dw["w2"], scale)
+    g = dict(tok_embeddings=(rng.standard_normal((CFG["vocab_size"], hid)) * 0.5).astype(np.float16),
+             output_norm=(1 + 0.1 * rng.standard_normal(hid)).astype(np.float16),
+             output_weight=(rng.standard_normal((CFG["vocab_size"], hid)) * 0.05).astype(np.float16))
+    model.set_globals(dev(g["tok_embeddings"]), dev(g["output_norm"]), dev(g["output_weight"]))
+    return model, layers, g
+
+
+@pytest.mark.parametrize("int8", [True, False])
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_decode_steps_match_oracle(int8, use_graph):
+    model, layers, g = build(int8)
+    B, prompts = 3, [[5, 17, 900], [1, 2, 3, 4, 999], [7, 8]]
+    pmax, n_gen = max(len(p) for p in prompts), 4
+    steps = pmax + n_gen
+    start = np.array([pmax - len(p) for p in prompts], np.int32)
+    S, Hkv = CFG["session_len"], CFG["kv_head_num"]
+    dt = np.int8 if int8 else np.float16
+    kc = [[np.zeros((Hkv, S, 128), dt) for _ in range(B)] for _ in range(CFG["num_layer"])]
+    vc = [[np.zeros((Hkv, S, 128), dt) for _ in range(B)] for _ in range(CFG["num_layer"])]
+    lengths = np.zeros(B, np.int32)
+    picked = np.zeros(B, np.int32)
+    mr = 5e-3
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        st = model.new_state(B, steps, start, np.full((steps, B), -1, np.int32), keep_hidden=True, keep_logits=True)
+        agree = total = 0
+        for s in range(steps):
+            active = s >= start
+            ids = picked.copy()
+            for b, p in enumerate(prompts):
+                if start[b] <= s < pmax:
+                    ids[b] = p[s - start[b]]
+            want_h, want_l, want_p = odec.decode_step(ids, lengths, layers, g, kc, vc, CFG, active)
+            st.forced_ids[s] = torch.from_numpy(ids).cuda()
+            model.decode(st, 1, use_graph=use_graph)
+            model.handle.check_device_status(stream.cuda_stream)
+            hid = st.hidden.cpu().numpy()
+            lg = st.logits.cpu().numpy()
+            for b in range(B):
+                if not active[b]:
+                    continue
+                eh = np.abs(hid[b].astype(np.float32) - want_h[b].astype(np.float32))
+                el = np.abs(lg[b] - want_l[b])
+                assert eh.max() <= 3e-2 and eh.mean() / np.abs(want_h[b].astype(np.float32)).mean() <= mr, (s, b, eh.max())
+                assert el.max() <= 3e-2 and el.mean() / np.abs(want_l[b]).mean() <= mr, (s, b, el.max())
+                total += 1
+                agree += int(st.output_ids[s, b].item() == want_p[b])
+            assert (st.output_ids[s].cpu().numpy()[~active] == -1).all()
+            # appended cache rows: within one LSB (int8) / 2e-3 (fp16) of the oracle's; then the oracle
+            # continues from the GPU's cache so that every step is compared on identical history
+            gk, gv = st.k_cache.cpu().numpy(), st.v_cache.cpu().numpy()
+            for l in range(CFG["num_layer"]):
+                for b in range(B):
+                    if active[b]:
+                        for got, want in ((gk[b, l], kc[l][b]), (gv[b, l], vc[l][b])):
+                            w_row = want[:, lengths[b]].astype(np.float32)
+                            d = np.abs(got[:, lengths[b]].astype(np.float32) - w_row)
+                            tol = 1.0 if int8 else 2.0 ** -9 * np.abs(w_row) + 4e-3
+                            assert (d <= tol).all(), (s, l, b, d.max())
+                    kc[l][b][...] = gk[b, l]
+                    vc[l][b][...] = gv[b, l]
+            picked = np.where(active, want_p, picked)
+            lengths = lengths + active.astype(np.int32)
+        assert int(st.step.item()) == steps
+        assert np.array_equal(st.lengths.cpu().numpy(), lengths)
+        assert agree >= total - 1, f"greedy picks agree on {agree}/{total}"
+        assert model.last_launches() > 0
+    model.close()
