@@ -70,6 +70,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     h->gemv_stages   = env_int("TM_B200_GEMV_STAGES", 0);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
+    h->debug_counters = env_int("TM_B200_DEBUG_COUNTERS", 0);
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -120,6 +121,14 @@ extern "C" int tm_check_device_status(tm_handle* h, void* stream, unsigned* word
     }
     *word = w;
     return w ? TM_ERR_DEVICE_TIMEOUT : TM_OK;
+}
+
+extern "C" int tm_debug_counters(tm_handle* h, void* stream, long long* out24)
+{
+    if (!h || !out24) return TM_ERR_INVALID_ARG;
+    cudaError_t e = cudaMemcpyAsync(out24, (char*)h->status + 64, 24 * sizeof(long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    return e == cudaSuccess ? TM_OK : TM_ERR_CUDA;
 }
 
 extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
@@ -187,6 +196,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+            p.debug      = h->debug_counters ? (long long*)((char*)h->status + 64) : nullptr;
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
             h->launches += 1;
             if (e != cudaSuccess) {

@@ -53,8 +53,9 @@ struct GemmTcParams {
     unsigned*            status;
     int                  N, T, K;
     int                  fused_silu;
+    long long*           debug;  // developer counters (may be null)
     // filled in by gemm_tc_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, w_stages;
 };
 
 struct GemmTcPlan {
@@ -70,6 +71,7 @@ struct GemmTcPlan {
     size_t counter_ints;
 };
 
+int         gemm_tc_x_stages(int token_tile);
 size_t      gemm_tc_smem_bytes(int token_tile);
 GemmTcPlan  gemm_tc_plan(int N, int T, int K, int sm_count);
 cudaError_t gemm_tc_prepare(int max_smem);

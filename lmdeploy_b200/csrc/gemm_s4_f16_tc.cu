@@ -32,18 +32,22 @@ constexpr int kWBytes    = 4 * 4 * kTileBytes;  // [4 k32][4 column tiles][512 B
 constexpr int kQBytes    = kTileN * 4;
 constexpr int kWStage    = kWBytes + kQBytes;    // 8704
 constexpr int kABytes    = 2 * kTileN * 128;     // two 64-wide K blocks of 128 rows x 128 B
-constexpr int kWST       = 4;                    // packed-weight stages
+constexpr int kWSTMax    = 16;                   // packed-weight stages: as many as fit (the HBM latency is
+                                                 // hidden by the bytes in flight, ~64 KB per SM)
 constexpr int kAST       = 2;                    // expanded-weight stages
-constexpr int kXST       = 3;                    // activation stages
+constexpr int kXSTMax    = 8;                    // activation stages: as many as fit (GemmTcPlan::x_stages), and a
+                                                 // slice is published x_stages - 2 iterations after it was
+                                                 // issued: that many loads are in flight, and publishing
+                                                 // slice j waits at most for the MMA of slice j - 2
 constexpr int kDqWarps   = 8;
 constexpr int kXWarp     = 2 + kDqWarps;         // warp that streams the activations
 constexpr int kThreads   = (3 + kDqWarps) * 32;
 constexpr int kTmemCols  = 128;
 
 struct Bars {
-    uint64_t w_full[kWST], w_empty[kWST];
+    uint64_t w_full[kWSTMax], w_empty[kWSTMax];
     uint64_t a_full[kAST], a_empty[kAST];
-    uint64_t x_full[kXST], x_empty[kXST];
+    uint64_t x_full[kXSTMax], x_empty[kXSTMax];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
     int      flag;
@@ -115,8 +119,35 @@ __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 
+__device__ __forceinline__ void cp_async_wait_dyn(int n)
+{
+    switch (n) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    }
+}
+
+// bounded wait that also accumulates the cycles spent waiting (developer counters)
+__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, long long& acc)
+{
+    const long long t0 = clock64();
+    const bool      ok = mbar_wait(bar, parity);
+    acc += clock64() - t0;
+    return ok;
+}
+
 __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParams p)
 {
+    long long dbg_w0 = 0, dbg_w1 = 0, dbg_w2 = 0;
+    const long long dbg_t0 = clock64();
+    const int kXST  = p.x_stages;
+    const int kXLag = p.x_stages - 2;
+    const int kWST  = p.w_stages;
     extern __shared__ unsigned char smem_dyn[];
     // tiles the tensor core reads must sit on 1024-byte boundaries (the swizzle is a function of
     // the address bits)
@@ -146,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     const int n_tiles32 = p.N / 32;
 
     if (tid == 0) {
-        for (int s = 0; s < kWST; ++s) {
+        for (int s = 0; s < kWSTMax; ++s) {
             mbar_init(&bars->w_full[s], 1);
             mbar_init(&bars->w_empty[s], kDqWarps);
         }
@@ -154,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             mbar_init(&bars->a_full[s], kDqWarps);
             mbar_init(&bars->a_empty[s], 1);
         }
-        for (int s = 0; s < kXST; ++s) {
+        for (int s = 0; s < kXSTMax; ++s) {
             mbar_init(&bars->x_full[s], 32);
             mbar_init(&bars->x_empty[s], 1);
         }
@@ -183,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int ntw   = min(4, n_tiles32 - tile0);
             const int sw    = it % kWST;
             if (it >= kWST) {
-                const bool ok = mbar_wait(&bars->w_empty[sw], ((it / kWST) - 1) & 1);
+                const bool ok = timed_wait(&bars->w_empty[sw], ((it / kWST) - 1) & 1, dbg_w0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                     dead = true;
@@ -221,11 +252,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         const uint32_t sw1  = (uint32_t)((ch ^ (tr + 4)) << 4);  // rows tr + 4, tr + 12, ...
         bool           dead = false;
         int            g    = u_begin % G;
-        for (int it = 0; it < n_units + (kXST - 1); ++it) {
+        for (int it = 0; it < n_units + kXLag; ++it) {
             if (it < n_units) {
                 const int sx = it % kXST;
                 if (!dead && it >= kXST) {
-                    const bool ok = mbar_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1);
+                    const bool ok = timed_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dbg_w0);
                     if (!__all_sync(0xffffffffu, ok)) {
                         if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                         dead = true;
@@ -251,10 +282,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 if (++g == G) g = 0;
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
-            // the slice issued kXST-1 iterations ago has landed: publish it to the tensor core
-            const int done = it - (kXST - 1);
+            // the slice issued kXLag iterations ago has landed: publish it to the tensor core
+            const int done = it - kXLag;
             if (done >= 0) {
-                asm volatile("cp.async.wait_group %0;" ::"n"(kXST - 1) : "memory");
+                const long long tw = clock64();
+                cp_async_wait_dyn(kXLag);
+                dbg_w1 += clock64() - tw;
                 fence_proxy_async_smem();
                 if (!dead) mbar_arrive(&bars->x_full[done % kXST]);
             }
@@ -273,11 +306,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int sa = it % kAST, sx = it % kXST;
             if (first && seg_idx > 0 && !dead) {
                 // the epilogue of the previous segment must have drained the accumulator
-                const bool ok = mbar_wait(&bars->acc_empty, (seg_idx - 1) & 1);
+                const bool ok = timed_wait(&bars->acc_empty, (seg_idx - 1) & 1, dbg_w2);
                 if (!__all_sync(0xffffffffu, ok)) dead = true;
             }
             if (!dead) {
-                const bool ok = mbar_wait(&bars->a_full[sa], (it / kAST) & 1) && mbar_wait(&bars->x_full[sx], (it / kXST) & 1);
+                const bool ok = timed_wait(&bars->a_full[sa], (it / kAST) & 1, dbg_w0)
+                                && timed_wait(&bars->x_full[sx], (it / kXST) & 1, dbg_w1);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                     dead = true;
@@ -336,8 +370,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int sw = it % kWST, sa = it % kAST;
 
             if (!dead) {
-                bool ok = mbar_wait(&bars->w_full[sw], (it / kWST) & 1);
-                if (ok && it >= kAST) ok = mbar_wait(&bars->a_empty[sa], ((it / kAST) - 1) & 1);
+                bool ok = timed_wait(&bars->w_full[sw], (it / kWST) & 1, dbg_w0);
+                if (ok && it >= kAST) ok = timed_wait(&bars->a_empty[sa], ((it / kAST) - 1) & 1, dbg_w1);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                     dead = true;
@@ -403,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int n_split = c_last - c_first + 1;
             const int col0    = jt * kTileN;
             if (!dead) {
-                const bool ok = mbar_wait(&bars->acc_full, seg_idx & 1);
+                const bool ok = timed_wait(&bars->acc_full, seg_idx & 1, dbg_w2);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmTmemWait);
                     dead = true;
@@ -489,6 +523,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         }
     }
 
+    if (p.debug != nullptr && blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (warp <= 2 || warp == kXWarp)) {
+        // developer counters of CTA 1: per role {total cycles, wait 0, wait 1, wait 2}
+        const int role = warp == kXWarp ? 3 : warp;
+        p.debug[role * 4 + 0] = clock64() - dbg_t0;
+        p.debug[role * 4 + 1] = dbg_w0;
+        p.debug[role * 4 + 2] = dbg_w1;
+        p.debug[role * 4 + 3] = dbg_w2;
+        if (warp == 0) p.debug[16] = n_units;
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -498,9 +541,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
 
 }  // namespace
 
+int gemm_tc_x_stages(int token_tile)
+{
+    return token_tile > 64 ? 3 : 4;
+}
+
+int gemm_tc_w_stages(int token_tile)
+{
+    const size_t fixed = 1024 + (size_t)kAST * kABytes + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
+                         + sizeof(Bars) + 64;
+    int          n     = (int)((227 * 1024 - fixed) / (size_t)kWStage);
+    return n > kWSTMax ? kWSTMax : n;
+}
+
 size_t gemm_tc_smem_bytes(int token_tile)
 {
-    return 1024 + (size_t)kAST * kABytes + (size_t)kXST * 2 * token_tile * 128 + (size_t)kWST * kWStage + sizeof(Bars) + 64;
+    return 1024 + (size_t)kAST * kABytes + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
+           + (size_t)gemm_tc_w_stages(token_tile) * kWStage + sizeof(Bars) + 64;
 }
 
 GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
@@ -533,6 +590,8 @@ cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st
     p.slots_per_chunk = pl.slots_per_chunk;
     p.n_col_tiles     = pl.n_col_tiles;
     p.token_tile      = pl.token_tile;
+    p.x_stages        = gemm_tc_x_stages(pl.token_tile);
+    p.w_stages        = gemm_tc_w_stages(pl.token_tile);
     dim3 grid(pl.ctas, pl.t_chunks);
     gemm_s4_f16_tc_kernel<<<grid, kThreads, pl.smem_bytes, st>>>(p);
     return cudaGetLastError();
