@@ -71,6 +71,11 @@ extern "C" int tm_create(tm_handle** out, int device)
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->debug_counters = env_int("TM_B200_DEBUG_COUNTERS", 0);
+    h->tc_dev_mode    = env_int("TM_B200_TC_DEV_MODE", 0);
+    if (h->debug_counters && e == cudaSuccess) {
+        e = cudaMalloc((void**)&h->debug_buf, 64 << 10);
+        if (e == cudaSuccess) e = cudaMemset(h->debug_buf, 0, 64 << 10);
+    }
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -92,6 +97,7 @@ extern "C" int tm_destroy(tm_handle* h)
     if (h->attn_scratch) cudaFree(h->attn_scratch);
     if (h->attn_counters) cudaFree(h->attn_counters);
     if (h->status) cudaFree(h->status);
+    if (h->debug_buf) cudaFree(h->debug_buf);
     cudaSetDevice(prev);
     delete h;
     return TM_OK;
@@ -126,7 +132,8 @@ extern "C" int tm_check_device_status(tm_handle* h, void* stream, unsigned* word
 extern "C" int tm_debug_counters(tm_handle* h, void* stream, long long* out24)
 {
     if (!h || !out24) return TM_ERR_INVALID_ARG;
-    cudaError_t e = cudaMemcpyAsync(out24, (char*)h->status + 64, 24 * sizeof(long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (!h->debug_buf) return TM_ERR_INVALID_ARG;
+    cudaError_t e = cudaMemcpyAsync(out24, h->debug_buf, 2048 * sizeof(long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     return e == cudaSuccess ? TM_OK : TM_ERR_CUDA;
 }
@@ -196,7 +203,8 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
-            p.debug      = h->debug_counters ? (long long*)((char*)h->status + 64) : nullptr;
+            p.debug      = h->debug_counters ? h->debug_buf : nullptr;
+            p.dev_mode   = h->tc_dev_mode;
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
             h->launches += 1;
             if (e != cudaSuccess) {

@@ -54,8 +54,9 @@ struct GemmTcParams {
     int                  N, T, K;
     int                  fused_silu;
     long long*           debug;  // developer counters (may be null)
+    int                  dev_mode;  // developer experiments (TM_B200_TC_DEV_MODE): 1 no MMA, 2 no expand, 4 no X copy, 8 no drain
     // filled in by gemm_tc_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, w_stages;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, x_lag, w_stages;
 };
 
 struct GemmTcPlan {

@@ -3,15 +3,16 @@
 // A CTA computes C^T tiles of 128 output features x up to 128 tokens.  It is persistent and
 // stream-K balanced over (128-feature tile, 128-row quantisation group) units, like the
 // small-token kernel.  Warp roles:
-//   warp 0      producer: bulk copies (TMA, mbarrier completion) of the packed int4 weight and the
-//               {zero, scale} row of a unit into a ring
-//   warp 10     streams the activation slice of the unit with cp.async into the
-//               128-byte-swizzled K-major layout the tensor core reads
+//   warp 0      idle
+//   warp 10     idle
 //   warp 1      allocates TMEM; one elected lane issues tcgen05.mma (M = 128, N = token tile,
 //               K = 16 per instruction, fp16 x fp16 -> fp32) and commits completions to mbarriers
-//   warps 2..9  expand the packed weight: lop3 nibble unpack, exact (q - z) in fp16, one fp16
+//   warps 2..9  stream their own share of the packed weight (private cp.async rings) and 1/8 of the
+//               unit's activation slice (into the 128-byte-swizzled K-major layout the tensor core
+//               reads), and expand the weight: lop3 nibble unpack, exact (q - z) in fp16, one fp16
 //               multiply by the scale (bit-identical to the reference's dequantised weight,
-//               kernels/gemm_s_f16/common.h:115-156, 218-235), stmatrix into the swizzled A tile;
+//               kernels/gemm_s_f16/common.h:115-156, 218-235), tcgen05.st of the fragments straight
+//               into TMEM, from where the tensor core takes its A operand (no shared-memory round trip);
 //               at the end of a column tile they read the accumulator with tcgen05.ld and store C
 //               (optionally through the SiLU(gate) * up epilogue) or the split-K partial
 // Partial tiles of CTAs that share a column tile meet in scratch memory; the last CTA to arrive
@@ -21,6 +22,7 @@
 // 208-234; mma.sync tiles of gemm_template.h:338-444).
 #include "common.cuh"
 #include "gemm_s4_f16.h"
+// #define TM_B200_TC_TRACE 1   // developer build: per-unit event trace of CTA 1 into GemmTcParams::debug
 
 namespace tmb {
 namespace {
@@ -31,10 +33,11 @@ constexpr int kTileBytes = 512;
 constexpr int kWBytes    = 4 * 4 * kTileBytes;  // [4 k32][4 column tiles][512 B]
 constexpr int kQBytes    = kTileN * 4;
 constexpr int kWStage    = kWBytes + kQBytes;    // 8704
-constexpr int kABytes    = 2 * kTileN * 128;     // two 64-wide K blocks of 128 rows x 128 B
-constexpr int kWSTMax    = 16;                   // packed-weight stages: as many as fit (the HBM latency is
-                                                 // hidden by the bytes in flight, ~64 KB per SM)
-constexpr int kAST       = 2;                    // expanded-weight stages
+constexpr int kACols     = kGroup / 2;           // TMEM columns of one expanded weight stage (128 k as fp16 pairs)
+constexpr int kWarpStage = 2 * kTileBytes + 128; // per expanding warp and unit: 2 x 512 B of weight + 32 {zero, scale}
+constexpr int kWSTMax    = 7;                    // stages of those private rings (cp.async groups in flight <= 6)
+constexpr int kAST       = 6;                    // expanded-weight stages (in TMEM)
+constexpr int kAccCols   = 128;                  // accumulator columns (token tile <= 128)
 constexpr int kXSTMax    = 8;                    // activation stages: as many as fit (GemmTcPlan::x_stages), and a
                                                  // slice is published x_stages - 2 iterations after it was
                                                  // issued: that many loads are in flight, and publishing
@@ -42,13 +45,14 @@ constexpr int kXSTMax    = 8;                    // activation stages: as many a
 constexpr int kDqWarps   = 8;
 constexpr int kXWarp     = 2 + kDqWarps;         // warp that streams the activations
 constexpr int kThreads   = (3 + kDqWarps) * 32;
-constexpr int kTmemCols  = 128;
+constexpr int kMT        = 1;                    // column tiles that share one activation slice (see the loader)
+constexpr int kTmemCols  = 512;                  // accumulator + kAST x 64 columns of expanded weight, power of two
 
 struct Bars {
-    uint64_t w_full[kWSTMax], w_empty[kWSTMax];
     uint64_t a_full[kAST], a_empty[kAST];
     uint64_t x_full[kXSTMax], x_empty[kXSTMax];
     uint64_t acc_full, acc_empty;
+    uint64_t probe;  // developer probe: latency of tcgen05.commit -> mbarrier arrival
     uint32_t tmem_base;
     int      flag;
 };
@@ -60,19 +64,28 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
            | ((uint64_t)2 << 61);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+// D(tmem) (+)= A(tmem) x B(smem descriptor)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(tmem_d),
-        "l"(desc_a),
+        "r"(tmem_a),
         "l"(desc_b),
         "r"(idesc),
         "r"(accumulate)
         : "memory");
+}
+
+// 16 TMEM lanes x 8 columns from an mma A-fragment: regs = {rows r | k pair c, rows r+8 | k pair c,
+// rows r | k pair c+4, rows r+8 | k pair c+4} with r = lane / 4, c = lane % 4
+__device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3)
+{
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+                 : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint64_t* bar)
@@ -133,21 +146,41 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n)
 }
 
 // bounded wait that also accumulates the cycles spent waiting (developer counters)
+#ifdef TM_B200_TC_TRACE
+#define TC_TRACE(role, it, ev)                                                                                          \
+    do {                                                                                                                \
+        if (p.debug != nullptr && blockIdx.x == 1 && blockIdx.y == 0 && (it) < 40)                                      \
+            p.debug[1100 + (role) * 200 + (it) * 4 + (ev)] = clock64() - dbg_t0;                                        \
+    } while (0)
+#else
+#define TC_TRACE(role, it, ev) do {} while (0)
+#endif
+#ifdef TM_B200_TC_PROFILE
+#define TC_CLOCK() clock64()
+#else
+#define TC_CLOCK() 0ll
+#endif
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, long long& acc)
 {
-    const long long t0 = clock64();
+    const long long t0 = TC_CLOCK();
     const bool      ok = mbar_wait(bar, parity);
-    acc += clock64() - t0;
+    acc += TC_CLOCK() - t0;
     return ok;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParams p)
 {
-    long long dbg_w0 = 0, dbg_w1 = 0, dbg_w2 = 0;
+    long long dbg_w0 = 0, dbg_w1 = 0, dbg_w2 = 0, dbg_epi = 0;
+    unsigned long long gt_start, gt_last_unit = 0, gt_fin = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_start));
+#ifdef TM_B200_TC_TRACE
     const long long dbg_t0 = clock64();
+#else
+    const long long dbg_t0 = TC_CLOCK();
+#endif
     const int kXST  = p.x_stages;
-    const int kXLag = p.x_stages - 2;
-    const int kWST  = p.w_stages;
+    const int kXLag = p.x_lag;
+    const int kWST  = p.w_stages;  // copies of kWST - 1 units in flight per warp (weight + activation share)
     extern __shared__ unsigned char smem_dyn[];
     // tiles the tensor core reads must sit on 1024-byte boundaries (the swizzle is a function of
     // the address bits)
@@ -157,10 +190,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
 
     const int TT      = p.token_tile;             // UMMA N, multiple of 16, <= 128
     const int x_bytes = 2 * TT * 128;             // two K blocks of TT rows x 128 B
-    unsigned char* a_ring = sm;                                   // kAST x kABytes
-    unsigned char* x_ring = a_ring + kAST * kABytes;              // kXST x x_bytes (x_bytes % 1024 == 0 for TT % 8 == 0... TT*256)
+    unsigned char* x_ring = sm;                                   // kXST x x_bytes (multiples of 1024)
     unsigned char* w_ring = x_ring + kXST * x_bytes;              // kWST x kWStage
-    Bars*          bars   = reinterpret_cast<Bars*>(w_ring + kWST * kWStage);
+    Bars*          bars   = reinterpret_cast<Bars*>(w_ring + kWST * kDqWarps * kWarpStage);
 
     const int tid  = threadIdx.x;
     const int warp = tid >> 5;
@@ -177,10 +209,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     const int n_tiles32 = p.N / 32;
 
     if (tid == 0) {
-        for (int s = 0; s < kWSTMax; ++s) {
-            mbar_init(&bars->w_full[s], 1);
-            mbar_init(&bars->w_empty[s], kDqWarps);
-        }
         for (int s = 0; s < kAST; ++s) {
             mbar_init(&bars->a_full[s], kDqWarps);
             mbar_init(&bars->a_empty[s], 1);
@@ -189,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             mbar_init(&bars->x_full[s], 32);
             mbar_init(&bars->x_empty[s], 1);
         }
+        mbar_init(&bars->probe, 1);
         mbar_init(&bars->acc_full, 1);
         mbar_init(&bars->acc_empty, kDqWarps);
         fence_mbar_init();
@@ -203,57 +232,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    const long long dbg_t1 = TC_CLOCK();
 
     if (warp == 0) {
-        // ================================================================== weight producer
-        const uint64_t pol_w = policy_evict_first();
-        bool           dead  = false;
-        int            jt = u_begin / G, g = u_begin - jt * G;
-        for (int it = 0; it < n_units && !dead; ++it) {
-            const int tile0 = jt * 4;
-            const int ntw   = min(4, n_tiles32 - tile0);
-            const int sw    = it % kWST;
-            if (it >= kWST) {
-                const bool ok = timed_wait(&bars->w_empty[sw], ((it / kWST) - 1) & 1, dbg_w0);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
-                    dead = true;
-                    break;
-                }
-            }
-            unsigned char* sb = w_ring + sw * kWStage;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&bars->w_full[sw], (uint32_t)(4 * ntw * kTileBytes + ntw * 128));
-            }
-            __syncwarp();
-            if (lane < 4) {
-                const size_t k32 = (size_t)g * 4 + lane;
-                bulk_g2s_hint(sb + lane * 4 * kTileBytes, p.A + (k32 * n_tiles32 + tile0) * kTileBytes,
-                              (uint32_t)(ntw * kTileBytes), &bars->w_full[sw], pol_w);
-            }
-            else if (lane == 4) {
-                bulk_g2s_hint(sb + kWBytes, p.Q + ((size_t)g * p.N + (size_t)tile0 * 32) * 4, (uint32_t)(ntw * 128),
-                              &bars->w_full[sw], pol_w);
-            }
-            if (++g == G) {
-                g = 0;
-                ++jt;
-            }
-        }
+        // idle: the packed weight is streamed by the warps that expand it (private cp.async rings)
     }
     else if (warp == kXWarp) {
         // ================================================================== activation loader
-        // slice [TT rows][128 k] of the unit's group -> two 64-wide K blocks, rows of 128 B with
-        // their 16-byte chunks XOR-swizzled by (row & 7): the layout the tensor core expects.
-        // Lane = (row & 3, chunk): 4 rows per pass.
+        // slice [TT rows][128 k] of a group -> two 64-wide K blocks, rows of 128 B with their 16-byte
+        // chunks XOR-swizzled by (row & 7): the layout the tensor core expects.  One slice serves the
+        // kMT consecutive units (column tiles) that share the group.  Lane = (row & 3, chunk).
         const int      ch   = lane & 7;
         const int      tr   = lane >> 3;
         const uint32_t sw0  = (uint32_t)((ch ^ tr) << 4);        // rows tr, tr + 8, ...
         const uint32_t sw1  = (uint32_t)((ch ^ (tr + 4)) << 4);  // rows tr + 4, tr + 12, ...
         bool           dead = false;
-        int            g    = u_begin % G;
-        for (int it = 0; it < n_units + kXLag; ++it) {
-            if (it < n_units) {
+        const int      n_slices = (n_units + kMT - 1) / kMT;
+        int            g    = (u_begin / kMT) % G;
+        for (int it = 0; it < ((p.dev_mode & 32) ? 0 : n_slices + kXLag); ++it) {
+            if (it < n_slices) {
                 const int sx = it % kXST;
                 if (!dead && it >= kXST) {
                     const bool ok = timed_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dbg_w0);
@@ -262,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                         dead = true;
                     }
                 }
-                if (!dead) {
+                if (!dead && !(p.dev_mode & 4)) {
                     const uint32_t       xb      = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
                     const size_t         row_b   = (size_t)p.K * 2;
                     const unsigned char* src_col = p.X + ((size_t)g * kGroup + ch * 8) * 2;
@@ -285,14 +282,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             // the slice issued kXLag iterations ago has landed: publish it to the tensor core
             const int done = it - kXLag;
             if (done >= 0) {
-                const long long tw = clock64();
                 cp_async_wait_dyn(kXLag);
-                dbg_w1 += clock64() - tw;
                 fence_proxy_async_smem();
                 if (!dead) mbar_arrive(&bars->x_full[done % kXST]);
             }
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("cp.async.wait_all;" ::: "memory");
     }
     else if (warp == 1) {
         // ================================================================== MMA issuer
@@ -300,38 +295,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         bool dead    = false;
         int  seg_idx = 0;
         bool first   = true;  // first MMA of the current segment overwrites the accumulator
-        for (int it = 0; it < n_units; ++it) {
+        for (int it = 0; it < ((p.dev_mode & 32) ? 0 : n_units); ++it) {
             const int u  = u_begin + it;
             const int g  = u % G;
             const int sa = it % kAST, sx = it % kXST;
             if (first && seg_idx > 0 && !dead) {
                 // the epilogue of the previous segment must have drained the accumulator
-                const bool ok = timed_wait(&bars->acc_empty, (seg_idx - 1) & 1, dbg_w2);
+                const bool ok = timed_wait(&bars->acc_empty, (seg_idx - 1) & 1, dbg_w0);
                 if (!__all_sync(0xffffffffu, ok)) dead = true;
             }
             if (!dead) {
                 const bool ok = timed_wait(&bars->a_full[sa], (it / kAST) & 1, dbg_w0)
-                                && timed_wait(&bars->x_full[sx], (it / kXST) & 1, dbg_w1);
+                                && timed_wait(&bars->x_full[sx], (it / kXST) & 1, dbg_w0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                     dead = true;
                 }
             }
             tc_fence_after();
+            if (lane == 0) TC_TRACE(1, it, 0);
             if (!dead && lane == 0) {
-                const uint32_t a_addr = base + (uint32_t)(a_ring - sm) + sa * kABytes;
+                const long long ti0 = TC_CLOCK();
+                const uint32_t a_tmem = tmem + kAccCols + sa * kACols;
                 const uint32_t x_addr = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
 #pragma unroll
                 for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t da = make_desc(a_addr + kb * (kTileN * 128) + ks * 32);
+                        if (p.dev_mode & 1) continue;  // developer experiment: no MMA
                         const uint64_t db = make_desc(x_addr + kb * (TT * 128) + ks * 32);
-                        umma_f16(tmem, da, db, idesc, (first && kb == 0 && ks == 0) ? 0u : 1u);
+                        umma_f16_ts(tmem, a_tmem + (kb * 4 + ks) * 8, db, idesc, (first && kb == 0 && ks == 0) ? 0u : 1u);
                     }
                 }
+                const long long ti1 = TC_CLOCK();
                 umma_commit(&bars->a_empty[sa]);
                 umma_commit(&bars->x_empty[sx]);
+                dbg_w1 += ti1 - ti0;            // (developer counters: x_full waits are folded into w0 below)
+                dbg_w2 += TC_CLOCK() - ti1;
+                TC_TRACE(1, it, 1);
             }
             first = false;
             const bool seg_end = (it == n_units - 1) || (g == G - 1);
@@ -342,11 +343,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             }
             __syncwarp();
         }
+        if (p.debug != nullptr && blockIdx.x == 1 && lane == 0 && !dead) {
+            // developer probe: all MMAs have been issued; how long until a commit with nothing (new)
+            // in front of it reaches its barrier, and how long an empty commit takes right after
+            const long long c0 = clock64();
+            umma_commit(&bars->probe);
+            (void)mbar_wait(&bars->probe, 0);
+            const long long c1 = clock64();
+            umma_commit(&bars->probe);
+            (void)mbar_wait(&bars->probe, 1);
+            const long long c2 = clock64();
+            p.debug[19] = c1 - c0;
+            p.debug[20] = c2 - c1;
+        }
     }
     else {
         // ================================================================== expand + epilogue
         const int  dw   = warp - 2;       // 0..7
-        const int  tile = dw & 3;         // 32-feature column tile expanded by this warp
+        const int  tile = warp & 3;       // 32-feature column tile expanded by this warp = its TMEM lane quarter
         const int  kh   = dw >> 2;        // which pair of 32-row slabs of the group
         const int  r    = lane >> 2;
         const int  c    = lane & 3;
@@ -356,10 +370,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         int        seg_idx = 0;
         const int  dtid = tid - 64;
 
-        // stmatrix row address pattern: lane L supplies row (L & 7) of matrix (L >> 3):
-        // matrices = {rows +0, k +0}, {rows +8, k +0}, {rows +0, k +8}, {rows +8, k +8}
-        const int m_row = (lane & 7) + ((lane >> 3) & 1) * 8;  // row inside the 16-row half tile
-        const int m_k8  = (lane >> 4) & 1;                     // which 8-wide k chunk of the 16
+
+        // private ring of this warp: per unit its own 2 x 512 B of packed weight (column tile `tile`,
+        // 32-row slabs 2 kh, 2 kh + 1 of the group) + the 128 B of {zero, scale} of its 32 features
+        const uint32_t my_ring = base + (uint32_t)(w_ring - sm) + dw * kWST * kWarpStage;
+        int            ijt = u_begin / G, ig = u_begin - ijt * G;  // unit the next copy is issued for
+        int  i_it = 0;  // index (CTA-local) of the unit the next copy is issued for
+        auto issue_unit = [&](int stage) {
+            ++i_it;
+            const int tile0 = ijt * 4;
+            if (tile0 + tile < n_tiles32) {
+                const uint32_t       dst = my_ring + stage * kWarpStage + lane * 16;
+                const unsigned char* src = p.A + (((size_t)ig * 4 + kh * 2) * n_tiles32 + tile0 + tile) * kTileBytes + lane * 16;
+                cp_async16_zfill(dst, src, true);
+                cp_async16_zfill(dst + kTileBytes, src + (size_t)n_tiles32 * kTileBytes, true);
+                if (lane < 8) {
+                    cp_async16_zfill(dst + 2 * kTileBytes, p.Q + ((size_t)ig * p.N + (size_t)(tile0 + tile) * 32) * 4 + lane * 16, true);
+                }
+            }
+            if (++ig == G) {
+                ig = 0;
+                ++ijt;
+            }
+        };
+        for (int sidx = 0; sidx < kWST - 1; ++sidx) {
+            if (sidx < n_units) issue_unit(sidx);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
 
         for (int it = 0; it < n_units; ++it) {
             const int u     = u_begin + it;
@@ -368,19 +405,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int tile0 = jt * 4;
             const int ntw   = min(4, n_tiles32 - tile0);
             const int sw = it % kWST, sa = it % kAST;
+            cp_async_wait_dyn(kWST - 2);
+            __syncwarp();
+            if (warp == 2 && lane == 0) TC_TRACE(2, it, 0);
 
             if (!dead) {
-                bool ok = timed_wait(&bars->w_full[sw], (it / kWST) & 1, dbg_w0);
-                if (ok && it >= kAST) ok = timed_wait(&bars->a_empty[sa], ((it / kAST) - 1) & 1, dbg_w1);
+                bool ok = true;
+                if (it >= kAST && !(p.dev_mode & 32)) ok = timed_wait(&bars->a_empty[sa], ((it / kAST) - 1) & 1, dbg_w0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
                     dead = true;
                 }
             }
-            if (!dead && tile < ntw) {
+            const long long te0 = TC_CLOCK();
+            if (warp == 2 && lane == 0) TC_TRACE(2, it, 1);
+            if (!dead && tile < ntw && !(p.dev_mode & 2)) {
                 tc_fence_after();
-                const unsigned char* sb = w_ring + sw * kWStage;
-                const __half2*       qs = reinterpret_cast<const __half2*>(sb + kWBytes) + tile * 32;
+                const unsigned char* sb = w_ring + (dw * kWST + sw) * kWarpStage;
+                const __half2*       qs = reinterpret_cast<const __half2*>(sb + 2 * kTileBytes);
                 uint32_t z1024[2], nz64[2], s_lo[2], s_hi[2];
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
@@ -395,11 +437,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                     s_lo[a]  = reinterpret_cast<const uint32_t&>(sl2);
                     s_hi[a]  = reinterpret_cast<const uint32_t&>(sh2);
                 }
-                const uint32_t a_addr = base + (uint32_t)(a_ring - sm) + sa * kABytes;
+                const uint32_t a_tmem = tmem + kAccCols + sa * kACols + ((uint32_t)(tile * 32) << 16);
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
                     const int   k32 = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
-                    const uint4 w   = reinterpret_cast<const uint4*>(sb)[(k32 * 4 + tile) * 32 + lane];
+                    const uint4 w   = reinterpret_cast<const uint4*>(sb)[kk * 32 + lane];
                     const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                     for (int wi = 0; wi < 4; ++wi) {
@@ -411,25 +453,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                         f[1] = hmul2_ftz(f[1], s_hi[a]);
                         f[2] = hmul2_ftz(f[2], s_lo[a]);
                         f[3] = hmul2_ftz(f[3], s_hi[a]);
-                        // destination row / 16-byte chunk of this lane's stmatrix row
-                        const int n   = tile * 32 + a * 16 + m_row;           // row of the 128-row tile
-                        const int k   = k32 * 32 + k16 * 16 + m_k8 * 8;       // 0..127 inside the group
-                        const int kb  = k >> 6;
-                        const int ch  = (k & 63) >> 3;
-                        stmatrix_x4(a_addr + kb * (kTileN * 128) + n * 128 + ((ch ^ (n & 7)) << 4), f[0], f[1], f[2], f[3]);
+                        // rows tile*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
+                        tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), f[0], f[1], f[2],
+                                           f[3]);
                     }
                 }
             }
             // expanded tile visible to the tensor core; packed stage free again
-            fence_proxy_async_smem();
+            const long long te1 = TC_CLOCK();
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
             __syncwarp();
             if (lane == 0 && !dead) {
                 mbar_arrive(&bars->a_full[sa]);
-                mbar_arrive(&bars->w_empty[sw]);
             }
+            if (warp == 2 && lane == 0) TC_TRACE(2, it, 2);
+            // refill the slot that was read one unit ago (everyone in the warp is past its reads)
+            if (it + kWST - 1 < n_units) issue_unit((it + kWST - 1) % kWST);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            dbg_w1 += te1 - te0;
+            dbg_w2 += TC_CLOCK() - te1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_last_unit));
 
             const bool seg_end = (it == n_units - 1) || (g == G - 1);
-            if (!seg_end) continue;
+            if (!seg_end || (p.dev_mode & 32)) continue;
 
             // ---- column tile jt finished for this CTA: drain the accumulator ------------------
             const int c_first = (jt * G) / upc;
@@ -437,18 +484,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int n_split = c_last - c_first + 1;
             const int col0    = jt * kTileN;
             if (!dead) {
-                const bool ok = timed_wait(&bars->acc_full, seg_idx & 1, dbg_w2);
+                const bool ok = timed_wait(&bars->acc_full, seg_idx & 1, dbg_w0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicOr(p.status, kStatusGemmTmemWait);
                     dead = true;
                 }
             }
             tc_fence_after();
+            const long long tp0 = TC_CLOCK();
+            long long tp1 = tp0, tp2 = tp0, tp3 = tp0, tp4 = tp0;
             const int n_row   = q4 * 32 + lane;         // feature row of the tile held by this thread
             const int n_glob  = col0 + n_row;
             const int ccount  = TT / 2;                 // token columns per warp
             float*    slot    = p.workspace + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + jt) * (size_t)(128 * kTileN);
-            if (!dead) {
+            if (!dead && !(p.dev_mode & 8)) {
                 for (int cb = 0; cb < ccount; cb += 8) {
                     const int col = chalf * ccount + cb;
                     float     v[8];
@@ -480,9 +529,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             __syncwarp();
             if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
             ++seg_idx;
+            tp1 = TC_CLOCK();
 
             if (n_split > 1) {
                 __threadfence();
+                tp2 = TC_CLOCK();
                 named_bar_sync(1, kDqWarps * 32);
                 if (dtid == 0) {
                     int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + jt;
@@ -492,45 +543,104 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                     bars->flag = is_last;
                 }
                 named_bar_sync(1, kDqWarps * 32);
+                tp3 = TC_CLOCK();
                 if (bars->flag && !dead) {
+                    gt_fin += 1;
                     __threadfence();
+                    // fixed-order reduction of every CTA's partial.  Each thread owns up to 8 groups of
+                    // 4 adjacent features at a time and walks the slots with all 8 loads in flight.
                     const int n_cols = min(kTileN, p.N - col0);
-                    const int pairs  = n_cols / 2;
-                    for (int i = dtid; i < t_rows * pairs; i += kDqWarps * 32) {
-                        const int t  = i / pairs;
-                        const int n  = (i - t * pairs) * 2;
-                        float     v0 = 0.f, v1 = 0.f;
+                    const int quads  = n_cols / 4;  // N % 32 == 0
+                    const int items  = t_rows * quads;
+                    for (int i0 = dtid; i0 < items; i0 += kDqWarps * 32 * 8) {
+                        float4 acc[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         for (int cc = c_first; cc <= c_last; ++cc) {
                             const float* sl = p.workspace
                                               + ((size_t)blockIdx.y * p.slots_per_chunk + cc + jt) * (size_t)(128 * kTileN);
-                            const float2 v = __ldcg(reinterpret_cast<const float2*>(sl + (size_t)t * kTileN + n));
-                            v0 += v.x;
-                            v1 += v.y;
+                            float4 v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {  // all loads of the slot first: they overlap
+                                const int i  = i0 + j * kDqWarps * 32;
+                                const int ii = i < items ? i : i0;
+                                const int t  = ii / quads;
+                                const int n  = (ii - t * quads) * 4;
+                                v[j]         = __ldcg(reinterpret_cast<const float4*>(sl + (size_t)t * kTileN + n));
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                acc[j].x += v[j].x;
+                                acc[j].y += v[j].y;
+                                acc[j].z += v[j].z;
+                                acc[j].w += v[j].w;
+                            }
                         }
-                        const __half2 h = __floats2half2_rn(v0, v1);
-                        if (p.fused_silu) {
-                            const float2 uu   = __half22float2(h);
-                            const float  silu = uu.x / (1.f + __expf(-uu.x));
-                            p.C[(size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2] = __float2half_rn(silu * uu.y);
-                        }
-                        else {
-                            *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n) = h;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int i = i0 + j * kDqWarps * 32;
+                            if (i < items) {
+                                const int     t  = i / quads;
+                                const int     n  = (i - t * quads) * 4;
+                                const __half2 h0 = __floats2half2_rn(acc[j].x, acc[j].y);
+                                const __half2 h1 = __floats2half2_rn(acc[j].z, acc[j].w);
+                                if (p.fused_silu) {
+                                    const float2 u0 = __half22float2(h0), u1 = __half22float2(h1);
+                                    const float  s0 = u0.x / (1.f + __expf(-u0.x)), s1 = u1.x / (1.f + __expf(-u1.x));
+                                    *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2) =
+                                        __floats2half2_rn(s0 * u0.y, s1 * u1.y);
+                                }
+                                else {
+                                    __half2* dst = reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n);
+                                    dst[0]       = h0;
+                                    dst[1]       = h1;
+                                }
+                            }
                         }
                     }
                 }
                 named_bar_sync(1, kDqWarps * 32);
             }
+            tp4 = TC_CLOCK();
+            dbg_epi += tp4 - tp0;
+            if (p.debug != nullptr && blockIdx.y == 0 && dtid == 0 && blockIdx.x < 8) {
+                long long* e = p.debug + 940 + blockIdx.x * 8;
+                e[0] = tp0 - (tp0 - 0);  // placeholder keeps layout simple
+                e[1] = tp1 - tp0;        // drain + stores
+                e[2] = tp2 - tp1;        // __threadfence
+                e[3] = tp3 - tp2;        // ticket + barriers
+                e[4] = tp4 - tp3;        // finalize (if last) + barrier
+                e[5] = (long long)gt_fin;
+                e[6] = n_split;
+            }
         }
     }
 
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    if (p.debug != nullptr && blockIdx.y == 0 && warp == 2 && lane == 0) {
+        // developer timeline of every CTA: start, last unit expanded, end (ns, global timer), finalizes, units, SM id
+        unsigned long long gt_end;
+        unsigned           smid;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_end));
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        long long* row = p.debug + 32 + blockIdx.x * 6;
+        row[0] = (long long)gt_start;
+        row[1] = (long long)gt_last_unit;
+        row[2] = (long long)gt_end;
+        row[3] = (long long)gt_fin;
+        row[4] = n_units;
+        row[5] = smid;
+    }
     if (p.debug != nullptr && blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (warp <= 2 || warp == kXWarp)) {
         // developer counters of CTA 1: per role {total cycles, wait 0, wait 1, wait 2}
         const int role = warp == kXWarp ? 3 : warp;
-        p.debug[role * 4 + 0] = clock64() - dbg_t0;
+        p.debug[role * 4 + 0] = TC_CLOCK() - dbg_t0;
         p.debug[role * 4 + 1] = dbg_w0;
         p.debug[role * 4 + 2] = dbg_w1;
         p.debug[role * 4 + 3] = dbg_w2;
         if (warp == 0) p.debug[16] = n_units;
+        if (warp == 1) p.debug[17] = dbg_t1 - dbg_t0;
+        if (warp == 2) p.debug[18] = dbg_epi;
     }
     tc_fence_before();
     __syncthreads();
@@ -543,21 +653,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
 
 int gemm_tc_x_stages(int token_tile)
 {
-    return token_tile > 64 ? 3 : 4;
+    return token_tile > 64 ? 5 : 8;
 }
 
 int gemm_tc_w_stages(int token_tile)
 {
-    const size_t fixed = 1024 + (size_t)kAST * kABytes + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
-                         + sizeof(Bars) + 64;
-    int          n     = (int)((227 * 1024 - fixed) / (size_t)kWStage);
-    return n > kWSTMax ? kWSTMax : n;
+    // unit it + w_stages - 1 is issued while unit it is expanded; its activation slot must have been
+    // released by the MMA of unit it + w_stages - 1 - x_stages: keep that at least 3 units back
+    return gemm_tc_x_stages(token_tile) - 2;
 }
 
 size_t gemm_tc_smem_bytes(int token_tile)
 {
-    return 1024 + (size_t)kAST * kABytes + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
-           + (size_t)gemm_tc_w_stages(token_tile) * kWStage + sizeof(Bars) + 64;
+    return 1024 + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
+           + (size_t)gemm_tc_w_stages(token_tile) * kDqWarps * kWarpStage + sizeof(Bars) + 64;
 }
 
 GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
@@ -591,6 +700,9 @@ cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st
     p.n_col_tiles     = pl.n_col_tiles;
     p.token_tile      = pl.token_tile;
     p.x_stages        = gemm_tc_x_stages(pl.token_tile);
+    // loads in flight = x_lag slices; the ring is deeper than that so that issuing slice j + x_lag (and
+    // with it publishing slice j) only needs the MMA of slice j + x_lag - x_stages to have retired
+    p.x_lag           = pl.token_tile > 64 ? 2 : 3;
     p.w_stages        = gemm_tc_w_stages(pl.token_tile);
     dim3 grid(pl.ctas, pl.t_chunks);
     gemm_s4_f16_tc_kernel<<<grid, kThreads, pl.smem_bytes, st>>>(p);
