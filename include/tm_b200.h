@@ -77,6 +77,20 @@ TM_API size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k);
 TM_API int tm_gemm_s4_f16(tm_handle* h, void* C, const void* A, const void* B, const void* Q, int m, int n, int k,
                    int group_size, int type, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same GEMM for callers that cannot allocate device memory — a server plugin whose memory is
+ * owned by the server, a process that gave every free byte to its KV-cache pool, a loop that must
+ * not meet cudaMalloc's device-wide synchronisation.  No counterpart in the reference (its GEMM
+ * needs no scratch).  It takes no handle and calls no allocator: the split-K scratch is an 8 MB
+ * array built into the library image (every GPU that loads the library holds it until exit).
+ * Limits: n <= 16 tokens, and a shape whose partial tiles fit the 8 MB (all Llama-2 projections
+ * do); anything larger returns TM_ERR_WORKSPACE.  Runs on the CURRENT device, asynchronously on
+ * `stream`.  The first call on a device resolves the array's device address and sets kernel
+ * attributes: make that call before any stream capture.  All calls share the one array, so two
+ * calls that overlap on the GPU (different streams) race; calls on one stream are safe.  A
+ * bounded wait that gives up leaves the output incomplete and is not reported by this entry. */
+TM_API int tm_gemm_s4_f16_noalloc(void* C, const void* A, const void* B, const void* Q, int m, int n, int k,
+                           int group_size, int type, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * int4 format helpers.  Replace the functions of
  *   src/turbomind/kernels/gemm_s_f16/format.h:11-30 that src/turbomind/python/bind.cpp:414-465

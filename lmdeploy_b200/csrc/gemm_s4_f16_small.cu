@@ -14,6 +14,9 @@
 // tile is 8 and which has no split-K across CTAs.
 #include "common.cuh"
 #include "gemm_s4_f16.h"
+#include "tm_b200.h"
+
+#include <mutex>
 
 namespace tmb {
 
@@ -420,3 +423,101 @@ cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaSt
 }
 
 }  // namespace tmb
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the small-token GEMM (tm_gemm_s4_f16_noalloc in tm_b200.h).
+//
+// Some hosts of this library cannot call the CUDA allocator at all: an inference-server plugin
+// whose device memory is owned and budgeted by the server, a process that has already handed
+// every free byte to its KV-cache pool, or a latency-critical loop that must not hit
+// cudaMalloc's implicit device synchronisation.  tm_create() allocates the split-K scratch of
+// this kernel with cudaMalloc; the entry point below needs no handle and calls no allocator:
+// the scratch lives in the library image itself, in the fixed-size device array declared here,
+// which every GPU that loads the library holds until the process exits.
+//
+// Layout of the array: [0, 4 KB) arrival tickets (int) with the status word of the bounded waits
+// at byte 4092; [4 KB, end) split-K partial tiles (fp32).
+namespace tmb {
+namespace {
+
+constexpr size_t kStaticScratchBytes  = 8u << 20;  // 8 MB per GPU, the stated maximum
+constexpr size_t kStaticControlBytes  = 4096;
+constexpr int    kStaticMaxDevices    = 64;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratchDevice {
+    void* ptr      = nullptr;  // DEVICE address of g_static_scratch on this GPU
+    int   sm_count = 0;
+    int   max_smem = 0;
+    bool  ready    = false;
+};
+StaticScratchDevice g_static_dev[kStaticMaxDevices];  // guarded by g_static_mutex
+std::mutex          g_static_mutex;
+
+}  // namespace
+}  // namespace tmb
+
+extern "C" int tm_gemm_s4_f16_noalloc(
+    void* C, const void* A, const void* B, const void* Q, int m, int n, int k, int group_size, int type, void* stream)
+{
+    using namespace tmb;
+    if (!C || !A || !B || !Q) return TM_ERR_INVALID_ARG;
+    if (((uintptr_t)C | (uintptr_t)A | (uintptr_t)B | (uintptr_t)Q) & 15u) return TM_ERR_INVALID_ARG;
+    if (m <= 0 || n <= 0 || k <= 0) return TM_ERR_INVALID_ARG;
+    if (group_size != 128 || k % 128 || m % 32) return TM_ERR_UNSUPPORTED;
+    if (type != TM_GEMM_PLAIN && type != TM_GEMM_FUSED_SILU_FFN) return TM_ERR_UNSUPPORTED;
+    if (type == TM_GEMM_FUSED_SILU_FFN && m % 64) return TM_ERR_UNSUPPORTED;
+    if (n > 16) return TM_ERR_WORKSPACE;  // beyond the built-in scratch: only the small-token kernel is offered here
+
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TM_ERR_CUDA;
+    if (dev < 0 || dev >= kStaticMaxDevices) return TM_ERR_UNSUPPORTED;
+
+    StaticScratchDevice d;
+    {
+        // First call on this device: resolve the device address of the array (its name is only a
+        // host-side stand-in for the symbol), read two device attributes and raise the kernel's
+        // shared-memory limit.  None of these allocates.  Do this first call outside stream capture.
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        StaticScratchDevice&        s = g_static_dev[dev];
+        if (!s.ready) {
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return TM_ERR_CUDA;
+            int sms = 0, smem = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return TM_ERR_CUDA;
+            if (cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return TM_ERR_CUDA;
+            if (gemm_small_prepare(smem) != cudaSuccess) return TM_ERR_CUDA;
+            s.ptr      = p;
+            s.sm_count = sms;
+            s.max_smem = smem;
+            s.ready    = true;
+        }
+        d = s;
+    }
+
+    const GemmSmallPlan pl = gemm_small_plan(m, n, k, d.sm_count, d.max_smem, 0);
+    if (pl.counter_ints * sizeof(int) > kStaticControlBytes - 8
+        || pl.workspace_floats * sizeof(float) > kStaticScratchBytes - kStaticControlBytes) {
+        return TM_ERR_WORKSPACE;  // problem too large for the 8 MB built into the library
+    }
+    // The array keeps whatever the previous call left.  Tickets and the status word must start at
+    // zero (a call that was cut short may have left them otherwise); the partial tiles need no
+    // clearing, every slot is written before it is read.
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(d.ptr, 0, kStaticControlBytes, st) != cudaSuccess) return TM_ERR_CUDA;
+
+    GemmSmallParams p{};
+    p.C          = (__half*)C;
+    p.A          = (const unsigned char*)A;
+    p.X          = (const unsigned char*)B;
+    p.Q          = (const unsigned char*)Q;
+    p.workspace  = (float*)((char*)d.ptr + kStaticControlBytes);
+    p.counters   = (int*)d.ptr;
+    p.status     = (unsigned*)((char*)d.ptr + kStaticControlBytes - 4);
+    p.N          = m;
+    p.T          = n;
+    p.K          = k;
+    p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+    return gemm_small_launch(pl, p, st) == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}

@@ -90,6 +90,7 @@ SIGNATURES = {
     "tm_debug_counters": (_i, [_vp, _vp, C.POINTER(C.c_longlong)]),
     "tm_gemm_s4_f16_workspace_bytes": (_sz, [_i, _i, _i]),
     "tm_gemm_s4_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "tm_gemm_s4_f16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "tm_reformat_s4_k_m8": (_i, [_u32p, _u32p, _i, _i, _vp]),
     "tm_convert_s4_k_m8": (_i, [_u32p, _vp, _vp, _u32p, _vp, _u32p, _i, _i, _i, _vp]),
     "tm_transpose_qk_s4_k_m8_hf": (_i, [_u32p, _u32p, _i, _i, _i, _vp]),

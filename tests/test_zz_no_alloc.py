@@ -1,0 +1,54 @@
+"""GPU: the allocation-free GEMM entry point (``tm_gemm_s4_f16_noalloc``).
+
+It exists for hosts that may not call the CUDA allocator (memory owned by an embedding server,
+everything already given to a KV-cache pool, loops that cannot afford cudaMalloc's device-wide
+sync): its split-K scratch is a fixed 8 MB array inside the library.  The test calls it through the
+C ABI twice in a row — the shared array keeps the first call's contents, so the second call proves
+that nothing stale leaks — and compares with the handle-based entry point on the same inputs.
+This file sorts last on purpose: a run that stops at the first failure has then run everything else.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemm as ogemm
+from tests.helpers import assert_close, dev, make_linear
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,k,t,fused", [(4096, 4096, 4, False), (22016, 4096, 16, True), (160, 384, 1, False)])
+def test_noalloc_matches_handle_entry_point_twice(n, k, t, fused):
+    from lmdeploy_b200 import lib as l
+    lin = make_linear(n, k, 3)
+    A, Q = dev(lin["A"], torch.int32), dev(lin["Q"])
+    g = torch.Generator().manual_seed(t)
+    xs = [torch.randn(t, k, generator=g).half() for _ in range(2)]
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    n_out = n // 2 if fused else n
+    h = l.default_handle(torch.cuda.current_device())
+    for x in xs:                                   # two calls in a row, different activations
+        xd = x.cuda()
+        ref = torch.empty(t, n_out, dtype=torch.float16, device="cuda")
+        out = torch.full((t, n_out), 123.0, dtype=torch.float16, device="cuda")
+        assert l.lib.tm_gemm_s4_f16(h.ptr, ref.data_ptr(), A.data_ptr(), xd.data_ptr(), Q.data_ptr(), n, t, k, 128,
+                                    int(fused), None, 0, st) == l.TM_OK
+        assert l.lib.tm_gemm_s4_f16_noalloc(out.data_ptr(), A.data_ptr(), xd.data_ptr(), Q.data_ptr(), n, t, k, 128,
+                                            int(fused), st) == l.TM_OK
+        torch.cuda.synchronize()
+        assert_close(out.cpu().numpy(), ref.cpu().numpy(), "noalloc vs handle entry", rel_slack=2.0 ** -9 if fused else 0.0)
+        assert_close(out.cpu().numpy(), ogemm.gemm_s4_f16(x.numpy(), lin["w_kn"], fused_silu=fused), "noalloc vs oracle",
+                     rel_slack=2.0 ** -9 if fused else 0.0)
+
+
+def test_noalloc_rejects_what_does_not_fit():
+    from lmdeploy_b200 import lib as l
+    buf = torch.zeros(1 << 20, dtype=torch.float16, device="cuda")
+    p = buf.data_ptr()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert l.lib.tm_gemm_s4_f16_noalloc(p, p, p, p, 4096, 17, 4096, 128, 0, st) == l.TM_ERR_WORKSPACE     # > 16 tokens
+    assert l.lib.tm_gemm_s4_f16_noalloc(p, p, p, p, 1 << 22, 16, 128, 128, 0, st) == l.TM_ERR_WORKSPACE   # partials > 8 MB
+    assert l.lib.tm_gemm_s4_f16_noalloc(p, p, p, p, 4096, 1, 4096, 64, 0, st) == l.TM_ERR_UNSUPPORTED
+    assert l.lib.tm_gemm_s4_f16_noalloc(None, p, p, p, 4096, 1, 4096, 128, 0, st) == l.TM_ERR_INVALID_ARG
