@@ -175,3 +175,24 @@ class DecodeState:
         c.hidden_out = 0 if self.hidden is None else self.hidden.data_ptr()
         c.logits_out = 0 if self.logits is None else self.logits.data_ptr()
         self.c = c
+
+
+# -- tensor-parallel slicing of full (un-sharded) weights -------------------------------------------
+
+def tp_column_index(cfg: LlamaConfig, tp: int, rank: int):
+    """Output-feature indices each rank owns, as the reference slices them
+    (LlamaDecoderLayerWeight.cc:49-77, deploy.py:251-260 `merge_qkv`, :668-670 `tp_m_s4`):
+    qkv -> this rank's q heads | k heads | v heads; w13 -> a contiguous run of interleaved
+    (gate, up) pairs; o / w2 are split along their INPUT features (rows of the [K, N] weight)."""
+    import numpy as np
+    d = cfg.size_per_head
+    hq, hkv = cfg.head_num // tp, cfg.kv_head_num // tp
+    q = np.arange(rank * hq * d, (rank + 1) * hq * d)
+    k = cfg.head_num * d + np.arange(rank * hkv * d, (rank + 1) * hkv * d)
+    v = (cfg.head_num + cfg.kv_head_num) * d + np.arange(rank * hkv * d, (rank + 1) * hkv * d)
+    inter = cfg.inter_size // tp
+    return dict(qkv_cols=np.concatenate([q, k, v]),
+                o_rows=np.arange(rank * hq * d, (rank + 1) * hq * d),
+                w13_cols=np.arange(rank * 2 * inter, (rank + 1) * 2 * inter),
+                w2_rows=np.arange(rank * inter, (rank + 1) * inter),
+                vocab_rows=np.arange(rank * (cfg.vocab_size // tp), (rank + 1) * (cfg.vocab_size // tp)))
