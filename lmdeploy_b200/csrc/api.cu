@@ -67,7 +67,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_small_prepare(h->max_smem);
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    h->gemv_stages   = env_int("TM_B200_GEMV_STAGES", 0);
+    h->gemv_dev_mode = env_int("TM_B200_GEMV_DEV_MODE", 0);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->debug_counters = env_int("TM_B200_DEBUG_COUNTERS", 0);
@@ -142,7 +142,7 @@ extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
 {
     if (m <= 0 || n <= 0 || k <= 0 || k % 128 || m % 32) return 0;
     // device independent: the slot count grows with the grid, so plan for a grid no part exceeds
-    GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024, 0);
+    GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024);
     size_t        b  = pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
     if (n > 16) {
         GemmTcPlan   tc = gemm_tc_plan(m, n < 128 ? n : 128, k, 256);
@@ -220,7 +220,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     const size_t n_out = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;
     int          n_launch = n;
     for (;;) {
-        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem, h->gemv_stages);
+        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem);
         const size_t  c_b  = ((pl.counter_ints * sizeof(int) + 255) / 256) * 256;
         const size_t  need = pl.workspace_floats * sizeof(float) + c_b;
         const bool    fits = workspace ? workspace_bytes >= need :
@@ -233,7 +233,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
 
     for (int t0 = 0; t0 < n; t0 += n_launch) {
         const int     nt = n - t0 < n_launch ? n - t0 : n_launch;
-        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem, h->gemv_stages);
+        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem);
         float*        ws_f;
         int*          ws_c;
         if (workspace) {
@@ -257,6 +257,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
         p.T          = nt;
         p.K          = k;
         p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+        p.dev_mode   = h->gemv_dev_mode;
 
         cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream);
         h->launches += 1;

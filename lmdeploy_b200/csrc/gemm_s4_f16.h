@@ -19,6 +19,7 @@ struct GemmSmallParams {
     unsigned*            status;
     int                  N, T, K;
     int                  fused_silu;
+    int                  dev_mode;  // developer experiments (TM_B200_GEMV_DEV_MODE): 1 no unpack/MMA, 2 no publish
     // filled in by gemm_small_launch from the plan
     int units_per_cta, total_units, slots_per_chunk, n_col_tiles, stages;
 };
@@ -27,7 +28,7 @@ struct GemmSmallPlan {
     int    nt;             // 8-token MMA tiles per pass (1, 2 or 4)
     int    t_chunks;       // passes over the weight (grid.y)
     int    n_col_tiles;    // 512-column tiles
-    int    total_units;    // 32x512 weight units
+    int    total_units;    // 64x512 weight units
     int    units_per_cta;
     int    ctas;
     int    slots_per_chunk;  // split-K scratch slots per token chunk (= ctas + n_col_tiles)
@@ -37,8 +38,8 @@ struct GemmSmallPlan {
     size_t counter_ints;
 };
 
-size_t        gemm_small_smem_bytes(int stages);
-GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int want_stages);
+size_t        gemm_small_smem_bytes(int nt);
+GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem);
 cudaError_t   gemm_small_prepare(int max_smem);
 cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st);
 

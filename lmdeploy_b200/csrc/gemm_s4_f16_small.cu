@@ -1,17 +1,27 @@
-// W4A16 GEMM for small token counts (the HBM-bound regime): a persistent, stream-K balanced
-// kernel.  A few producer lanes stream the packed int4 weight (one contiguous 8 KB run per copy:
-// 32 input rows x 512 output columns) and the {zero, scale} rows through a ring of
-// shared-memory stages with bulk copies (TMA, mbarrier completion).  Sixteen consumer warps, one
-// per 32-column tile, unpack nibbles with lop3, subtract the zero point exactly in fp16, feed the
-// integers to mma.m16n8k16 (the runtime int4 layout IS that instruction's A fragment; the
-// activations come straight from L1/L2 as B fragments) and apply the group scale to the fp32
-// group sums.  K is split across CTAs (every CTA gets the same number of 32x512 weight units);
-// partial tiles meet in a scratch buffer and the last CTA to arrive for a column tile reduces
-// them in a fixed order, so the result is deterministic and no CTA ever waits for another.
+// W4A16 GEMM for small token counts (the HBM-bound regime): persistent, stream-K balanced, two CTAs
+// per SM for up to 8 tokens.  Work unit = 64 input rows x 512 output columns of the packed weight:
+// two slabs of 16 tiles (512 B each), every slab one contiguous 8 KB run.  Each of the 8 warps owns
+// two adjacent 32-column tiles of every slab and streams them through its own cp.async ring
+// (16 bytes per lane, a whole 512-byte tile per instruction); the activations of the unit (64 B per
+// token and slab) go to a slab shared by the CTA, stored with a chunk swizzle so that ldmatrix
+// delivers them as B fragments without bank conflicts.  One __syncthreads per unit publishes the
+// activations and frees the slot that is refilled next.
+// A tile is exactly four mma.m16n8k16 A fragments of packed nibbles; a warp turns a packed word into
+// tensor-core operands with five integer instructions (one shift, four lop3) and nothing else: the
+// fp16 values fed to the MMA are 1024 + q (rows r) and 1024 + 16 q (rows r + 8), and zero point,
+// offsets and scale are applied once per 128-row group to the fp32 group sums, using the group sum
+// of the activations that an extra MMA against an all-ones fragment delivers in the same register
+// layout:
+//     y += s (P - (1024 + z) SX)            rows r
+//     y += s/16 (P' - (1024 + 16 z) SX)     rows r + 8
+// K is split across CTAs (every CTA gets the same number of units); partial column tiles meet in a
+// scratch buffer and the last CTA to arrive for a column tile reduces them in a fixed order, so the
+// result is deterministic and no CTA ever waits for another.
 //
 // Replaces the small-n end of GemmS4F16::Run (src/turbomind/kernels/gemm_s_f16/
 // gemm_s4_f16.cu:208-234) / gemm_s4_f16_nn (gemm_template.h:338-444), whose smallest token
-// tile is 8 and which has no split-K across CTAs.
+// tile is 8 and which has no split-K across CTAs.  The weight seen by the MMA differs from the
+// reference's fp16_rn((q - z) s) only by that one rounding (the products are exact in fp32 here).
 #include "common.cuh"
 #include "gemm_s4_f16.h"
 #include "tm_b200.h"
@@ -22,266 +32,294 @@ namespace tmb {
 
 namespace {
 
-constexpr int kColsPerTile   = 32;   // one packed 32x32 tile = 512 B
-constexpr int kTileBytes     = 512;
-constexpr int kTilesPerUnit  = 16;   // column tiles per unit: one contiguous 8 KB run of the packed weight
-constexpr int kUnitCols      = kColsPerTile * kTilesPerUnit;  // 512
-constexpr int kWBytes        = kTilesPerUnit * kTileBytes;    // 8192
-constexpr int kQBytes        = kUnitCols * 4;                 // 2048
-constexpr int kStageBytes    = kWBytes + kQBytes;
-constexpr int kConsumers     = kTilesPerUnit;                 // one consumer warp per column tile
-constexpr int kConsThreads   = kConsumers * 32;
-constexpr int kProducerLanes = 4;                             // lanes of warp 0 that issue bulk copies
+constexpr int kColsPerTile  = 32;   // one packed 32x32 tile = 512 B
+constexpr int kTileBytes    = 512;
+constexpr int kTilesPerUnit = 16;   // column tiles per unit
+constexpr int kUnitCols     = kColsPerTile * kTilesPerUnit;  // 512
+constexpr int kUnitRows     = 64;   // input rows per unit: two 32-row slabs
+constexpr int kWarps        = 8;
+constexpr int kTilesPerWarp = kTilesPerUnit / kWarps;        // 2
+constexpr int kThreads      = kWarps * 32;
+constexpr int kSlabBytes    = kTilesPerWarp * kTileBytes;    // a warp's part of one slab: 1 KB
+constexpr int kWarpStage    = 2 * kSlabBytes + 256;          // two slabs + {zero, scale} of the 64 columns
 
-// dynamic shared memory: [stages][kStageBytes] | full[stages] | empty[stages] | flag
+// stages of the cp.async rings per token-tile count
+__host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 4 : 6; }
 
-// B fragments (activations) of one 32-row slab for NT token tiles, straight from global memory.
-template<int NT>
-__device__ __forceinline__ void
-load_x_frags(uint32_t (&bf)[NT][4], const unsigned char* X, int K, int T, int t0, int k32, int r, int c)
+// dynamic shared memory: [warps][stages][kWarpStage] | [stages][2 slabs][TP x 64 B] | flag
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 {
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const int t = t0 + j * 8 + r;
-        if (t < T) {
-            const uint32_t* xr = reinterpret_cast<const uint32_t*>(X + ((size_t)t * K + (size_t)k32 * 32) * 2) + c;
-            bf[j][0]           = __ldg(xr);
-            bf[j][1]           = __ldg(xr + 4);
-            bf[j][2]           = __ldg(xr + 8);
-            bf[j][3]           = __ldg(xr + 12);
-        }
-        else {
-            bf[j][0] = bf[j][1] = bf[j][2] = bf[j][3] = 0u;
-        }
-    }
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template<int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// One packed word -> A fragment {1024 + q | rows r, 1024 + 16 q | rows r + 8, same for k + 8}
+__device__ __forceinline__ void unpack_s4_biased(uint32_t w, uint32_t (&out)[4])
+{
+    constexpr uint32_t kLut   = (0xf0 & 0xcc) | 0xaa;  // (a & b) | c
+    constexpr uint32_t kBot   = 0x000f000f;
+    constexpr uint32_t kTop   = 0x00f000f0;
+    constexpr uint32_t kMagic = 0x64006400;  // half2{1024, 1024}
+    const uint32_t     hi     = w >> 8;
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(out[0]) : "r"(w), "n"(kBot), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(out[1]) : "r"(w), "n"(kTop), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(out[2]) : "r"(hi), "n"(kBot), "n"(kMagic), "n"(kLut));
+    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(out[3]) : "r"(hi), "n"(kTop), "n"(kMagic), "n"(kLut));
+}
+
+// B fragments (activations) of one 32-row slab for one 8-token tile.  A slab holds [tokens][4 chunks
+// of 16 B]; chunk i of token t sits at position i ^ ((t >> 1) & 3), which makes both the cp.async
+// writes and these ldmatrix reads free of bank conflicts.  `addr` = tile base + this lane's row.
+__device__ __forceinline__ void load_x_frag(uint32_t (&bf)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3])
+                 : "r"(addr));
 }
 
 template<int NT>
-__global__ void __launch_bounds__(32 + kConsThreads, 1) gemm_s4_f16_small_kernel(GemmSmallParams p)
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_kernel(GemmSmallParams p)
 {
-    constexpr int TP = NT * 8;
+    constexpr int TP     = NT * 8;
+    constexpr int ST     = stages_for(NT);
+    constexpr int kXSlab = TP * 64;      // activations of one 32-row slab
+    constexpr int kXUnit = 2 * kXSlab;   // ... of one unit
     extern __shared__ __align__(128) unsigned char smem_raw[];
 
-    const int stages = p.stages;
-
-    unsigned char* stage_base = smem_raw;
-    uint64_t*      full_bar   = reinterpret_cast<uint64_t*>(smem_raw + (size_t)stages * kStageBytes);
-    uint64_t*      empty_bar  = full_bar + stages;
-    int*           s_flag     = reinterpret_cast<int*>(empty_bar + stages);
+    constexpr int  kXRingOff = kWarps * ST * kWarpStage;
+    const uint32_t smem_s    = smem_u32(smem_raw);
+    int*           s_flag    = reinterpret_cast<int*>(smem_raw + kXRingOff + ST * kXUnit);
 
     const int tid  = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    const int r    = lane >> 2;  // fragment row
+    const int c    = lane & 3;   // fragment column pair
 
     // token chunk handled by this CTA row
     const int t0     = blockIdx.y * TP;
     const int t_rows = min(TP, p.T - t0);
 
-    const int G32       = p.K / 32;  // units (32-row slabs) per column tile
+    const int G         = p.K / kUnitRows;  // units per column tile
     const int upc       = p.units_per_cta;
     const int u_begin   = blockIdx.x * upc;
-    const int u_end     = min(u_begin + upc, p.total_units);
-    const int n_units   = u_end - u_begin;
+    const int n_units   = min(u_begin + upc, p.total_units) - u_begin;
     const int n_tiles32 = p.N / kColsPerTile;
 
-    if (tid == 0) {
-        for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kConsumers);
-        }
-        fence_mbar_init();
-    }
-    __syncthreads();
-
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        // lane l issues the copies of units l, l + kProducerLanes, ...: several copies are being
-        // issued at any time, each a single contiguous run of up to 8 KB.
-        if (lane < kProducerLanes) {
-            const uint64_t pol_w  = policy_evict_first();
-            bool           dead   = false;
-            int            issued = -1;
-            for (int it = lane; it < n_units && !dead; it += kProducerLanes) {
-                const int s = it % stages;
-                if (it >= stages) {
-                    if (!mbar_wait(&empty_bar[s], ((it / stages) - 1) & 1)) {
-                        atomicOr(p.status, kStatusGemvEmptyWait);
-                        dead = true;
-                        break;
-                    }
-                }
-                const int  u      = u_begin + it;
-                const int  jt     = u / G32;
-                const int  k32    = u - jt * G32;
-                const int  tile0  = jt * kTilesPerUnit;
-                const int  ntw    = min(kTilesPerUnit, n_tiles32 - tile0);
-                const bool need_q = (it == 0) || ((k32 & 3) == 0);
-
-                unsigned char* sb = stage_base + (size_t)s * kStageBytes;
-                const uint32_t tx = (uint32_t)(ntw * kTileBytes + (need_q ? ntw * kColsPerTile * 4 : 0));
-                mbar_arrive_expect_tx(&full_bar[s], tx);
-                bulk_g2s_hint(sb,
-                              p.A + ((size_t)k32 * n_tiles32 + tile0) * kTileBytes,
-                              (uint32_t)(ntw * kTileBytes),
-                              &full_bar[s],
-                              pol_w);
-                if (need_q) {
-                    bulk_g2s_hint(sb + kWBytes,
-                                  p.Q + ((size_t)(k32 >> 2) * p.N + (size_t)tile0 * kColsPerTile) * 4,
-                                  (uint32_t)(ntw * kColsPerTile * 4),
-                                  &full_bar[s],
-                                  pol_w);
-                }
-                issued = it;
-            }
-            if (dead) {
-                // consumers may have stopped too: make sure none of this lane's copies is still
-                // in flight towards this CTA's shared memory before the CTA can retire.
-                for (int j = issued; j >= 0 && j > issued - stages; j -= kProducerLanes) {
-                    (void)mbar_wait(&full_bar[j % stages], (j / stages) & 1);
-                }
+    // rows of the activation slabs that no token fills stay zero for the whole kernel
+    if (t_rows < TP) {
+        for (int i = tid; i < ST * 2 * TP * 4; i += kThreads) {
+            if (((i >> 2) % TP) >= t_rows) {
+                *reinterpret_cast<uint4*>(smem_raw + kXRingOff + i * 16) = make_uint4(0, 0, 0, 0);
             }
         }
     }
-    else {
-        // ------------------------------------------------------------------ consumers
-        const int wt   = warp - 1;   // column tile inside the unit
-        const int r    = lane >> 2;  // fragment row
-        const int c    = lane & 3;   // fragment column pair
-        const int ctid = tid - 32;
-        bool      dead = false;
 
-        float tot[2][NT][4];
-        float acc[2][NT][4];
+    // ---- copies: each warp feeds its private weight ring, the first threads also the shared slabs ----
+    const uint32_t ring_s = smem_s + warp * (ST * kWarpStage);
+    // activation chunk of this thread: token x_row, 16-byte piece x_sub of the unit's 128 B per token
+    const int      x_row    = tid >> 3;
+    const int      x_sub    = tid & 7;
+    const bool     x_loader = x_row < t_rows;  // implies tid < TP * 8
+    const unsigned char* const x_base =
+        p.X + ((size_t)(t0 + (x_loader ? x_row : 0)) * p.K) * 2 + x_sub * 16;
+    const uint32_t x_dst = smem_s + kXRingOff + (x_sub >> 2) * kXSlab + x_row * 64
+                           + (((x_sub & 3) ^ ((x_row >> 1) & 3)) << 4);
+    const size_t slab_stride = (size_t)n_tiles32 * kTileBytes;  // bytes between 32-row slabs of the weight
+
+    // state of the copy front (runs ST - 1 units ahead of the math)
+    int                  i_jt = u_begin / G, i_k = u_begin - i_jt * G;
+    bool                 i_first = true;
+    int                  i_tile  = 0;
+    const unsigned char* i_w     = nullptr;  // this lane's 16 B of the warp's first tile, slab 2 i_k
+    auto                 i_seek  = [&]() {
+        i_tile = i_jt * kTilesPerUnit + warp * kTilesPerWarp;
+        i_w    = p.A + ((size_t)(2 * i_k) * n_tiles32 + i_tile) * kTileBytes + lane * 16;
+    };
+    i_seek();
+    auto issue_unit = [&](int stage) {
+        const uint32_t dst = ring_s + stage * kWarpStage + lane * 16;
+        if (i_tile < n_tiles32) {
+            // the warp's two tiles are adjacent in memory: 1 KB contiguous per slab
+            cp_async16(dst, i_w);
+            cp_async16(dst + kSlabBytes, i_w + slab_stride);
+            if (i_tile + 1 < n_tiles32) {
+                cp_async16(dst + kTileBytes, i_w + kTileBytes);
+                cp_async16(dst + kSlabBytes + kTileBytes, i_w + slab_stride + kTileBytes);
+            }
+            if (i_first || (i_k & 1) == 0) {
+                // {64 + z, s} of the warp's 64 columns for this group: 256 B
+                if (lane < 16 && i_tile * kColsPerTile + lane * 4 < p.N) {
+                    cp_async16(dst + 2 * kSlabBytes,
+                               p.Q + ((size_t)(i_k >> 1) * p.N + (size_t)i_tile * kColsPerTile) * 4 + lane * 16);
+                }
+            }
+        }
+        if (x_loader) cp_async16(x_dst + stage * kXUnit, x_base + (size_t)i_k * (kUnitRows * 2));
+        i_first = false;
+        i_w += 2 * slab_stride;
+        if (++i_k == G) {
+            i_k = 0;
+            ++i_jt;
+            i_seek();
+        }
+    };
+#pragma unroll
+    for (int sidx = 0; sidx < ST - 1; ++sidx) {
+        if (sidx < n_units) issue_unit(sidx);
+        cp_async_commit();
+    }
+
+    // per (tile, 16-row half): Z = offset + zero (rows r / r + 8) and the scale (s, s / 16)
+    float zl[kTilesPerWarp][2], zh[kTilesPerWarp][2], sl[kTilesPerWarp][2], sh[kTilesPerWarp][2];
+#pragma unroll
+    for (int w = 0; w < kTilesPerWarp; ++w)
+#pragma unroll
+        for (int a = 0; a < 2; ++a) zl[w][a] = zh[w][a] = sl[w][a] = sh[w][a] = 0.f;
+
+    float tot[kTilesPerWarp][2][NT][4];
+    float acc[kTilesPerWarp][2][NT][4];
+    float sx[NT][4];
+#pragma unroll
+    for (int w = 0; w < kTilesPerWarp; ++w)
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    tot[a][j][i] = 0.f;
-                    acc[a][j][i] = 0.f;
-                }
+                for (int i = 0; i < 4; ++i) tot[w][a][j][i] = acc[w][a][j][i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) sx[j][0] = sx[j][1] = sx[j][2] = sx[j][3] = 0.f;
 
-        uint32_t z1024[2] = {0u, 0u}, nz64[2] = {0u, 0u};
-        float    sc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
+    const int      my_t0   = warp * kTilesPerWarp;  // first tile of this warp inside the unit
+    // this lane's row address inside an activation tile (ldmatrix: row = lane % 8, matrix = lane / 8)
+    const uint32_t x_lane = smem_s + kXRingOff + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
 
-        // with few token tiles the next unit's activations are requested one unit ahead
-        constexpr bool kPrefetchX = NT <= 2;
-        uint32_t       bf[NT][4];
-        if (kPrefetchX && n_units > 0) {
-            load_x_frags<NT>(bf, p.X, p.K, p.T, t0, u_begin % G32, r, c);
-        }
+    int jt = u_begin / G, kk = u_begin - jt * G;
+    int s = 0, s_fill = ST - 1;  // slot read now / slot refilled now (the one read one unit ago)
+    for (int it = 0; it < n_units; ++it) {
+        const int  tile0   = jt * kTilesPerUnit;
+        const int  ntw     = min(kTilesPerUnit, n_tiles32 - tile0) - my_t0;  // tiles of this warp that exist
+        const bool need_q  = (it == 0) || ((kk & 1) == 0);
+        const bool last    = (it == n_units - 1);
+        const bool seg_end = last || (kk == G - 1);
+        const bool grp_end = seg_end || ((kk & 1) == 1);
 
-        for (int it = 0; it < n_units; ++it) {
-            const int  u       = u_begin + it;
-            const int  jt      = u / G32;
-            const int  k32     = u - jt * G32;
-            const int  tile0   = jt * kTilesPerUnit;
-            const int  ntw     = min(kTilesPerUnit, n_tiles32 - tile0);
-            const bool need_q  = (it == 0) || ((k32 & 3) == 0);
-            const bool last    = (it == n_units - 1);
-            const bool seg_end = last || (k32 == G32 - 1);
-            const bool grp_end = seg_end || ((k32 & 3) == 3);
-            const int  s       = it % stages;
+        cp_async_wait<ST - 2>();
+        // every thread's copies for this unit have landed, and every warp is done with the unit before
+        __syncthreads();
+        if (it + ST - 1 < n_units) issue_unit(s_fill);
+        cp_async_commit();
 
-            // activations of the next unit: requested before this unit's math
-            uint32_t bn[kPrefetchX ? NT : 1][4];
-            if constexpr (kPrefetchX) {
-                if (!last) {
-                    load_x_frags<NT>(bn, p.X, p.K, p.T, t0, (u + 1) % G32, r, c);
-                }
-            }
-            else {
-                load_x_frags<NT>(bf, p.X, p.K, p.T, t0, k32, r, c);
-            }
-
-            if (!dead) {
-                // the verdict is made warp-uniform: the shuffles below need every lane
-                const bool ok = mbar_wait(&full_bar[s], (it / stages) & 1);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (lane == 0) atomicOr(p.status, kStatusGemvFullWait);
-                    dead = true;
-                }
-            }
-            if (!dead && wt < ntw) {
-                const unsigned char* sb = stage_base + (size_t)s * kStageBytes;
-                if (need_q) {
-                    // {64+z, s} of the four rows this lane owns: n16 in {0,1} x {r, r+8}
-                    const __half2* qs = reinterpret_cast<const __half2*>(sb + kWBytes) + wt * kColsPerTile;
+        const unsigned char* sb = smem_raw + (warp * ST + s) * kWarpStage;
+        if (need_q) {
+            const __half2* qs = reinterpret_cast<const __half2*>(sb + 2 * kSlabBytes);
+#pragma unroll
+            for (int w = 0; w < kTilesPerWarp; ++w) {
+                if (w < ntw) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
-                        const __half2 q_lo = qs[a * 16 + r];
-                        const __half2 q_hi = qs[a * 16 + r + 8];
-                        const __half2 zl2  = __half2half2(__hadd(__low2half(q_lo), __float2half_rn(960.f)));
-                        const __half2 zh2  = __half2half2(__hneg(__low2half(q_hi)));
-                        z1024[a]           = reinterpret_cast<const uint32_t&>(zl2);
-                        nz64[a]            = reinterpret_cast<const uint32_t&>(zh2);
-                        sc[a][0]           = __high2float(q_lo);
-                        sc[a][1]           = __high2float(q_hi);
-                    }
-                }
-                const uint4    w     = reinterpret_cast<const uint4*>(sb)[wt * 32 + lane];
-                const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const int k16 = wi >> 1;
-                    const int a   = wi & 1;
-                    uint32_t  af[4];
-                    unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], af);
-#pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        mma_m16n8k16(acc[a][j], af, bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                        const float2 q_lo = __half22float2(qs[w * 32 + a * 16 + r]);      // {64 + z, s} of row r
+                        const float2 q_hi = __half22float2(qs[w * 32 + a * 16 + r + 8]);  // row r + 8
+                        zl[w][a] = 960.f + q_lo.x;           // 1024 + z
+                        zh[w][a] = 16.f * q_hi.x;            // 1024 + 16 z
+                        sl[w][a] = q_lo.y;
+                        sh[w][a] = q_hi.y * 0.0625f;
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0 && !dead) {
-                mbar_arrive(&empty_bar[s]);
+        }
+        if (!(p.dev_mode & 1)) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t bf[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) load_x_frag(bf[j], x_lane + s * kXUnit + h * kXSlab + j * 512);
+                // group sums of the activations, in the accumulator layout (every row alike)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mma_m16n8k16(sx[j], ones, bf[j][0], bf[j][1]);
+                    mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
+                }
+#pragma unroll
+                for (int w = 0; w < kTilesPerWarp; ++w) {
+                    if (w < ntw) {
+                        const uint4    wq    = reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes)[lane];
+                        const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) {
+                            const int k16 = wi >> 1;
+                            const int a   = wi & 1;
+                            uint32_t  af[4];
+                            unpack_s4_biased(wv[wi], af);
+#pragma unroll
+                            for (int j = 0; j < NT; ++j) {
+                                mma_m16n8k16(acc[w][a][j], af, bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                            }
+                        }
+                    }
+                }
             }
-            if (grp_end) {
+        }
+        s      = (s == ST - 1) ? 0 : s + 1;
+        s_fill = (s_fill == ST - 1) ? 0 : s_fill + 1;
+
+        if (grp_end) {
+#pragma unroll
+            for (int w = 0; w < kTilesPerWarp; ++w)
 #pragma unroll
                 for (int a = 0; a < 2; ++a)
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        tot[a][j][0] = fmaf(sc[a][0], acc[a][j][0], tot[a][j][0]);
-                        tot[a][j][1] = fmaf(sc[a][0], acc[a][j][1], tot[a][j][1]);
-                        tot[a][j][2] = fmaf(sc[a][1], acc[a][j][2], tot[a][j][2]);
-                        tot[a][j][3] = fmaf(sc[a][1], acc[a][j][3], tot[a][j][3]);
-                        acc[a][j][0] = acc[a][j][1] = acc[a][j][2] = acc[a][j][3] = 0.f;
+                        tot[w][a][j][0] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][0], acc[w][a][j][0]), tot[w][a][j][0]);
+                        tot[w][a][j][1] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][1], acc[w][a][j][1]), tot[w][a][j][1]);
+                        tot[w][a][j][2] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][0], acc[w][a][j][2]), tot[w][a][j][2]);
+                        tot[w][a][j][3] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][1], acc[w][a][j][3]), tot[w][a][j][3]);
+                        acc[w][a][j][0] = acc[w][a][j][1] = acc[w][a][j][2] = acc[w][a][j][3] = 0.f;
                     }
-            }
-            if constexpr (kPrefetchX) {
-                if (!last) {
 #pragma unroll
-                    for (int j = 0; j < NT; ++j)
+            for (int j = 0; j < NT; ++j) sx[j][0] = sx[j][1] = sx[j][2] = sx[j][3] = 0.f;
+        }
+        const int this_jt = jt;
+        if (++kk == G) {
+            kk = 0;
+            ++jt;
+        }
+        if (!seg_end || (p.dev_mode & 2)) {
+            continue;
+        }
+
+        // ---- segment end: publish this CTA's part of column tile this_jt --------------------------
+        const int c_first = (this_jt * G) / upc;
+        const int c_last  = ((this_jt + 1) * G - 1) / upc;
+        const int n_split = c_last - c_first + 1;
+        const int n_cols  = min(kTilesPerUnit, n_tiles32 - tile0) * kColsPerTile;
+        const int col0    = tile0 * kColsPerTile;
+
+        if (n_split == 1) {
+            // this CTA saw the whole K range: straight from registers to C
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) bf[j][i] = bn[j][i];
-                }
-            }
-            if (!seg_end) {
-                continue;
-            }
-
-            // ---- segment end: publish this CTA's part of column tile jt ----------------------
-            const int c_first = (jt * G32) / upc;
-            const int c_last  = ((jt + 1) * G32 - 1) / upc;
-            const int n_split = c_last - c_first + 1;
-            const int n_cols  = ntw * kColsPerTile;
-            const int col0    = tile0 * kColsPerTile;
-
-            if (n_split == 1) {
-                // this CTA saw the whole K range: straight from registers to C
-                if (!dead && wt < ntw) {
+            for (int w = 0; w < kTilesPerWarp; ++w) {
+                if (w < ntw) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a)
 #pragma unroll
                         for (int j = 0; j < NT; ++j)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const int   n = col0 + wt * kColsPerTile + a * 16 + r + (i >> 1) * 8;
+                                const int   n = col0 + (my_t0 + w) * kColsPerTile + a * 16 + r + (i >> 1) * 8;
                                 const int   t = t0 + j * 8 + 2 * c + (i & 1);
-                                const float v = tot[a][j][i];
+                                const float v = tot[w][a][j][i];
                                 if (p.fused_silu) {
                                     // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pair;
                                     // the partner column n^1 lives in lane^4
@@ -298,98 +336,117 @@ __global__ void __launch_bounds__(32 + kConsThreads, 1) gemm_s4_f16_small_kernel
                             }
                 }
             }
-            else {
-                // (cta + column tile) is unique per segment: along the unit order either the CTA
-                // or the column tile advances, never both backwards.
-                float* slot = p.workspace
-                              + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + jt) * (size_t)(TP * kUnitCols);
+        }
+        else {
+            // (cta + column tile) is unique per segment: along the unit order either the CTA or the
+            // column tile advances, never both backwards.
+            float* slot = p.workspace
+                          + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + this_jt) * (size_t)(TP * kUnitCols);
+#pragma unroll
+            for (int w = 0; w < kTilesPerWarp; ++w)
 #pragma unroll
                 for (int a = 0; a < 2; ++a)
 #pragma unroll
                     for (int j = 0; j < NT; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int n = wt * kColsPerTile + a * 16 + r + (i >> 1) * 8;
+                            const int n = (my_t0 + w) * kColsPerTile + a * 16 + r + (i >> 1) * 8;
                             const int t = j * 8 + 2 * c + (i & 1);
-                            __stcg(slot + t * kUnitCols + n, tot[a][j][i]);
+                            if (t < t_rows) __stcg(slot + t * kUnitCols + n, tot[w][a][j][i]);
                         }
-                __threadfence();
-                named_bar_sync(1, kConsThreads);
-                if (ctid == 0) {
-                    int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + jt;
-                    const int ticket  = atomicAdd(counter, 1);
-                    const int is_last = (ticket == n_split - 1);
-                    if (is_last) {
-                        *counter = 0;  // self-reset for the next launch
-                    }
-                    s_flag[0] = is_last;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + this_jt;
+                const int ticket  = atomicAdd(counter, 1);
+                const int is_last = (ticket == n_split - 1);
+                if (is_last) {
+                    *counter = 0;  // self-reset for the next launch
                 }
-                named_bar_sync(1, kConsThreads);
-                const bool finalize = s_flag[0] != 0;
-                if (finalize && !dead) {
-                    __threadfence();
-                    // fixed-order reduction of every CTA's partial, two adjacent columns per thread
-                    const int pairs = n_cols / 2;
-                    for (int i = ctid; i < t_rows * pairs; i += kConsThreads) {
-                        const int t  = i / pairs;
-                        const int n  = (i - t * pairs) * 2;
-                        float     v0 = 0.f, v1 = 0.f;
-                        for (int cc = c_first; cc <= c_last; ++cc) {
-                            const float* sl = p.workspace
-                                              + ((size_t)blockIdx.y * p.slots_per_chunk + cc + jt)
-                                                    * (size_t)(TP * kUnitCols);
-                            const float2 v = __ldcg(reinterpret_cast<const float2*>(sl + t * kUnitCols + n));
-                            v0 += v.x;
-                            v1 += v.y;
-                        }
-                        const __half2 h = __floats2half2_rn(v0, v1);
-                        if (p.fused_silu) {
-                            const float2 u    = __half22float2(h);
-                            const float  silu = u.x / (1.f + __expf(-u.x));
-                            p.C[(size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2] = __float2half_rn(silu * u.y);
-                        }
-                        else {
-                            *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n) = h;
-                        }
-                    }
-                }
-                named_bar_sync(1, kConsThreads);  // s_flag is reused by the next segment
+                s_flag[0] = is_last;
             }
+            __syncthreads();
+            if (s_flag[0] != 0) {
+                __threadfence();
+                // fixed-order reduction of every CTA's partial: four adjacent columns per thread, the
+                // loads of up to four slots in flight together
+                const int quads = n_cols / 4;
+                for (int i = tid; i < t_rows * quads; i += kThreads) {
+                    const int t = i / quads;
+                    const int n = (i - t * quads) * 4;
+                    float4    v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int cc = c_first; cc <= c_last; cc += 4) {
+                        float4 part[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int    ce = min(cc + e, c_last);
+                            const float* sl2 = p.workspace
+                                               + ((size_t)blockIdx.y * p.slots_per_chunk + ce + this_jt) * (size_t)(TP * kUnitCols);
+                            part[e] = __ldcg(reinterpret_cast<const float4*>(sl2 + t * kUnitCols + n));
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (cc + e <= c_last) {
+                                v.x += part[e].x;
+                                v.y += part[e].y;
+                                v.z += part[e].z;
+                                v.w += part[e].w;
+                            }
+                        }
+                    }
+                    const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+                    if (p.fused_silu) {
+                        const float2 u0 = __half22float2(h0), u1 = __half22float2(h1);
+                        const float  s0 = u0.x / (1.f + __expf(-u0.x)), s1 = u1.x / (1.f + __expf(-u1.x));
+                        *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2) =
+                            __floats2half2_rn(s0 * u0.y, s1 * u1.y);
+                    }
+                    else {
+                        __half2* dst = reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n);
+                        dst[0]       = h0;
+                        dst[1]       = h1;
+                    }
+                }
+            }
+            __syncthreads();  // s_flag is reused by the next segment
+        }
+#pragma unroll
+        for (int w = 0; w < kTilesPerWarp; ++w)
 #pragma unroll
             for (int a = 0; a < 2; ++a)
 #pragma unroll
                 for (int j = 0; j < NT; ++j)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) tot[a][j][i] = 0.f;
-        }
+                    for (int i = 0; i < 4; ++i) tot[w][a][j][i] = 0.f;
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 }  // namespace
 
-size_t gemm_small_smem_bytes(int stages)
+size_t gemm_small_smem_bytes(int nt)
 {
-    return (size_t)stages * kStageBytes + (size_t)stages * 16 + 16;
+    const int st = stages_for(nt);
+    return (size_t)st * (kWarps * kWarpStage + 2 * nt * 512) + 16;
 }
 
-GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int want_stages)
+GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem)
 {
+    (void)max_smem;
     GemmSmallPlan pl{};
     pl.nt = T <= 8 ? 1 : (T <= 16 ? 2 : 4);
     const int tp   = pl.nt * 8;
     pl.t_chunks    = (T + tp - 1) / tp;
     pl.n_col_tiles = (N / kColsPerTile + kTilesPerUnit - 1) / kTilesPerUnit;
-    const int G32  = K / 32;
-    pl.total_units = pl.n_col_tiles * G32;
-    int ctas       = sm_count < pl.total_units ? sm_count : pl.total_units;
-    pl.units_per_cta   = (pl.total_units + ctas - 1) / ctas;
-    pl.ctas            = (pl.total_units + pl.units_per_cta - 1) / pl.units_per_cta;
-    pl.slots_per_chunk = pl.ctas + pl.n_col_tiles;
-    int stages         = want_stages > 0 ? want_stages : 20;
-    if (stages > pl.units_per_cta) stages = pl.units_per_cta < 2 ? 2 : pl.units_per_cta;
-    while (stages > 2 && gemm_small_smem_bytes(stages) > (size_t)max_smem) --stages;
-    pl.stages           = stages;
-    pl.smem_bytes       = gemm_small_smem_bytes(stages);
+    const int G    = K / kUnitRows;
+    pl.total_units = pl.n_col_tiles * G;
+    const int slots = sm_count * (pl.nt == 1 ? 2 : 1);  // co-resident CTAs
+    int       ctas  = slots < pl.total_units ? slots : pl.total_units;
+    pl.units_per_cta    = (pl.total_units + ctas - 1) / ctas;
+    pl.ctas             = (pl.total_units + pl.units_per_cta - 1) / pl.units_per_cta;
+    pl.slots_per_chunk  = pl.ctas + pl.n_col_tiles;
+    pl.stages           = stages_for(pl.nt);
+    pl.smem_bytes       = gemm_small_smem_bytes(pl.nt);
     pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * tp * kUnitCols;
     pl.counter_ints     = (size_t)pl.t_chunks * pl.n_col_tiles;
     return pl;
@@ -413,7 +470,7 @@ cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaSt
     p.n_col_tiles     = pl.n_col_tiles;
     p.stages          = pl.stages;
     dim3 grid(pl.ctas, pl.t_chunks);
-    dim3 block(32 + kConsThreads);
+    dim3 block(kThreads);
     switch (pl.nt) {
         case 1: gemm_s4_f16_small_kernel<1><<<grid, block, pl.smem_bytes, st>>>(p); break;
         case 2: gemm_s4_f16_small_kernel<2><<<grid, block, pl.smem_bytes, st>>>(p); break;
@@ -496,7 +553,7 @@ extern "C" int tm_gemm_s4_f16_noalloc(
         d = s;
     }
 
-    const GemmSmallPlan pl = gemm_small_plan(m, n, k, d.sm_count, d.max_smem, 0);
+    const GemmSmallPlan pl = gemm_small_plan(m, n, k, d.sm_count, d.max_smem);
     if (pl.counter_ints * sizeof(int) > kStaticControlBytes - 8
         || pl.workspace_floats * sizeof(float) > kStaticScratchBytes - kStaticControlBytes) {
         return TM_ERR_WORKSPACE;  // problem too large for the 8 MB built into the library

@@ -25,5 +25,5 @@ struct tm_handle {
     int                debug_counters  = 0;  // TM_B200_DEBUG_COUNTERS=1: kernels of CTA 1 record wait cycles
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
-    int                gemv_stages     = 0;  // 0 = automatic; TM_B200_GEMV_STAGES overrides
+    int                gemv_dev_mode   = 0;  // TM_B200_GEMV_DEV_MODE: timing experiments (results are then wrong)
 };
