@@ -52,10 +52,6 @@ TM_API int tm_last_cuda_error(const tm_handle* h);
 /* Synchronises `stream`, then reads and clears the device status word written by bounded
  * waits inside the kernels.  *word == 0 means no kernel gave up. */
 TM_API int tm_check_device_status(tm_handle* h, void* stream, unsigned* word);
-/* Developer aid: with TM_B200_DEBUG_COUNTERS=1 in the environment the tensor-core GEMM records, for
- * one CTA, the cycles each warp role spent waiting and a start/end timeline of every CTA; this copies
- * the 1024 counters out. */
-TM_API int tm_debug_counters(tm_handle* h, void* stream, long long* out1024);
 /* Number of kernel launches issued through this handle since creation. */
 TM_API unsigned long long tm_launch_count(const tm_handle* h);
 

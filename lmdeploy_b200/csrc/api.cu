@@ -68,14 +68,9 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->gemv_dev_mode = env_int("TM_B200_GEMV_DEV_MODE", 0);
+    h->tc_dev_mode   = env_int("TM_B200_TC_DEV_MODE", 0);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
-    h->debug_counters = env_int("TM_B200_DEBUG_COUNTERS", 0);
-    h->tc_dev_mode    = env_int("TM_B200_TC_DEV_MODE", 0);
-    if (h->debug_counters && e == cudaSuccess) {
-        e = cudaMalloc((void**)&h->debug_buf, 64 << 10);
-        if (e == cudaSuccess) e = cudaMemset(h->debug_buf, 0, 64 << 10);
-    }
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -97,7 +92,6 @@ extern "C" int tm_destroy(tm_handle* h)
     if (h->attn_scratch) cudaFree(h->attn_scratch);
     if (h->attn_counters) cudaFree(h->attn_counters);
     if (h->status) cudaFree(h->status);
-    if (h->debug_buf) cudaFree(h->debug_buf);
     cudaSetDevice(prev);
     delete h;
     return TM_OK;
@@ -127,15 +121,6 @@ extern "C" int tm_check_device_status(tm_handle* h, void* stream, unsigned* word
     }
     *word = w;
     return w ? TM_ERR_DEVICE_TIMEOUT : TM_OK;
-}
-
-extern "C" int tm_debug_counters(tm_handle* h, void* stream, long long* out24)
-{
-    if (!h || !out24) return TM_ERR_INVALID_ARG;
-    if (!h->debug_buf) return TM_ERR_INVALID_ARG;
-    cudaError_t e = cudaMemcpyAsync(out24, h->debug_buf, 2048 * sizeof(long long), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
-    return e == cudaSuccess ? TM_OK : TM_ERR_CUDA;
 }
 
 extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
@@ -203,7 +188,6 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
-            p.debug      = h->debug_counters ? h->debug_buf : nullptr;
             p.dev_mode   = h->tc_dev_mode;
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
             h->launches += 1;

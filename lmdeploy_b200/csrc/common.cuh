@@ -134,6 +134,14 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// D(16x8,f32) = A * B (the accumulator starts at zero)
+__device__ __forceinline__ void mma_m16n8k16_init(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 // One packed word of the runtime int4 layout -> the four half2 registers of an m16n8k16 A
 // fragment holding the exact integers (nibble - zero):
 //   out[0] = nibbles {0,4} (row r,   k pair low)     out[1] = nibbles {1,5} (row r+8, k pair low)

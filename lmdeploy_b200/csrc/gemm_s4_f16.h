@@ -54,17 +54,16 @@ struct GemmTcParams {
     unsigned*            status;
     int                  N, T, K;
     int                  fused_silu;
-    long long*           debug;  // developer counters (may be null)
-    int                  dev_mode;  // developer experiments (TM_B200_TC_DEV_MODE): 1 no MMA, 2 no expand, 4 no X copy, 8 no drain
+    int                  dev_mode;  // developer experiments (TM_B200_TC_DEV_MODE): 1 no TMEM store, 2 no expand math, 4 no MMA, 8 no weight copies
     // filled in by gemm_tc_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, x_lag, w_stages;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, a_stages, acc_stride;
 };
 
 struct GemmTcPlan {
     int    token_tile;     // UMMA N: tokens per pass, multiple of 16, <= 128
     int    t_chunks;       // passes over the weight (grid.y), 128 tokens each
-    int    n_col_tiles;    // 128-feature tiles
-    int    total_units;    // 128x128 weight units
+    int    n_col_tiles;    // 256-feature tiles
+    int    total_units;    // 128x256 weight units
     int    units_per_cta;
     int    ctas;
     int    slots_per_chunk;
@@ -73,7 +72,6 @@ struct GemmTcPlan {
     size_t counter_ints;
 };
 
-int         gemm_tc_x_stages(int token_tile);
 size_t      gemm_tc_smem_bytes(int token_tile);
 GemmTcPlan  gemm_tc_plan(int N, int T, int K, int sm_count);
 cudaError_t gemm_tc_prepare(int max_smem);

@@ -138,34 +138,33 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
 
     // state of the copy front (runs ST - 1 units ahead of the math)
     int                  i_jt = u_begin / G, i_k = u_begin - i_jt * G;
-    bool                 i_first = true;
     int                  i_tile  = 0;
     const unsigned char* i_w     = nullptr;  // this lane's 16 B of the warp's first tile, slab 2 i_k
+    const unsigned char* i_q     = nullptr;  // this lane's 16 B of the {zero, scale} row of the group of i_k
+    int                  i_step  = 0;        // bytes to the warp's second tile (0 where N ends after the first)
+    bool                 i_qok   = false;
     auto                 i_seek  = [&]() {
-        i_tile = i_jt * kTilesPerUnit + warp * kTilesPerWarp;
+        // a warp whose tiles lie beyond N re-reads the last pair; what it computes is never stored
+        i_tile = min(i_jt * kTilesPerUnit + warp * kTilesPerWarp, (n_tiles32 - 1) & ~1);
+        i_step = i_tile + 1 < n_tiles32 ? kTileBytes : 0;
         i_w    = p.A + ((size_t)(2 * i_k) * n_tiles32 + i_tile) * kTileBytes + lane * 16;
+        i_q    = p.Q + ((size_t)(i_k >> 1) * p.N + (size_t)i_tile * kColsPerTile) * 4 + (lane & 15) * 16;
+        i_qok  = lane < 16 && i_tile * kColsPerTile + lane * 4 < p.N;
     };
     i_seek();
     auto issue_unit = [&](int stage) {
         const uint32_t dst = ring_s + stage * kWarpStage + lane * 16;
-        if (i_tile < n_tiles32) {
-            // the warp's two tiles are adjacent in memory: 1 KB contiguous per slab
-            cp_async16(dst, i_w);
-            cp_async16(dst + kSlabBytes, i_w + slab_stride);
-            if (i_tile + 1 < n_tiles32) {
-                cp_async16(dst + kTileBytes, i_w + kTileBytes);
-                cp_async16(dst + kSlabBytes + kTileBytes, i_w + slab_stride + kTileBytes);
-            }
-            if (i_first || (i_k & 1) == 0) {
-                // {64 + z, s} of the warp's 64 columns for this group: 256 B
-                if (lane < 16 && i_tile * kColsPerTile + lane * 4 < p.N) {
-                    cp_async16(dst + 2 * kSlabBytes,
-                               p.Q + ((size_t)(i_k >> 1) * p.N + (size_t)i_tile * kColsPerTile) * 4 + lane * 16);
-                }
-            }
+        // the warp's two tiles are adjacent in memory: 1 KB contiguous per slab
+        cp_async16(dst, i_w);
+        cp_async16(dst + kTileBytes, i_w + i_step);
+        cp_async16(dst + kSlabBytes, i_w + slab_stride);
+        cp_async16(dst + kSlabBytes + kTileBytes, i_w + slab_stride + i_step);
+        if ((i_k & 1) == 0) {
+            // {64 + z, s} of the warp's 64 columns for this group: 256 B
+            if (i_qok) cp_async16(dst + 2 * kSlabBytes, i_q);
+            i_q += (size_t)p.N * 4;
         }
         if (x_loader) cp_async16(x_dst + stage * kXUnit, x_base + (size_t)i_k * (kUnitRows * 2));
-        i_first = false;
         i_w += 2 * slab_stride;
         if (++i_k == G) {
             i_k = 0;
@@ -205,28 +204,26 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
     // this lane's row address inside an activation tile (ldmatrix: row = lane % 8, matrix = lane / 8)
     const uint32_t x_lane = smem_s + kXRingOff + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
 
+    // Every CTA owns whole 128-row groups (an even number of units), so the two units of a group are
+    // unrolled: the first fetches {zero, scale}, the second ends the group.
     int jt = u_begin / G, kk = u_begin - jt * G;
     int s = 0, s_fill = ST - 1;  // slot read now / slot refilled now (the one read one unit ago)
-    for (int it = 0; it < n_units; ++it) {
-        const int  tile0   = jt * kTilesPerUnit;
-        const int  ntw     = min(kTilesPerUnit, n_tiles32 - tile0) - my_t0;  // tiles of this warp that exist
-        const bool need_q  = (it == 0) || ((kk & 1) == 0);
-        const bool last    = (it == n_units - 1);
-        const bool seg_end = last || (kk == G - 1);
-        const bool grp_end = seg_end || ((kk & 1) == 1);
-
-        cp_async_wait<ST - 2>();
-        // every thread's copies for this unit have landed, and every warp is done with the unit before
-        __syncthreads();
-        if (it + ST - 1 < n_units) issue_unit(s_fill);
-        cp_async_commit();
-
-        const unsigned char* sb = smem_raw + (warp * ST + s) * kWarpStage;
-        if (need_q) {
-            const __half2* qs = reinterpret_cast<const __half2*>(sb + 2 * kSlabBytes);
+    int to_issue = n_units - (ST - 1);  // units the copy front still has to start
+    for (int it = 0; it < n_units; it += 2) {
 #pragma unroll
-            for (int w = 0; w < kTilesPerWarp; ++w) {
-                if (w < ntw) {
+        for (int u = 0; u < 2; ++u) {
+            cp_async_wait<ST - 2>();
+            // every thread's copies for this unit have landed, and every warp is done with the unit before
+            __syncthreads();
+            if (to_issue > 0) issue_unit(s_fill);
+            --to_issue;
+            cp_async_commit();
+
+            const unsigned char* sb = smem_raw + (warp * ST + s) * kWarpStage + lane * 16;
+            if (u == 0) {
+                const __half2* qs = reinterpret_cast<const __half2*>(sb - lane * 16 + 2 * kSlabBytes);
+#pragma unroll
+                for (int w = 0; w < kTilesPerWarp; ++w) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
                         const float2 q_lo = __half22float2(qs[w * 32 + a * 16 + r]);      // {64 + z, s} of row r
@@ -238,23 +235,27 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
                     }
                 }
             }
-        }
-        if (!(p.dev_mode & 1)) {
+            if (!(p.dev_mode & 1)) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t bf[NT][4];
+                for (int h = 0; h < 2; ++h) {
+                    const bool fresh = (u == 0 && h == 0);  // first slab of the group: accumulators start at zero
+                    uint32_t   bf[NT][4];
 #pragma unroll
-                for (int j = 0; j < NT; ++j) load_x_frag(bf[j], x_lane + s * kXUnit + h * kXSlab + j * 512);
-                // group sums of the activations, in the accumulator layout (every row alike)
+                    for (int j = 0; j < NT; ++j) load_x_frag(bf[j], x_lane + s * kXUnit + h * kXSlab + j * 512);
+                    // group sums of the activations, in the accumulator layout (every row alike)
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    mma_m16n8k16(sx[j], ones, bf[j][0], bf[j][1]);
-                    mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
-                }
+                    for (int j = 0; j < NT; ++j) {
+                        if (fresh) {
+                            mma_m16n8k16_init(sx[j], ones, bf[j][0], bf[j][1]);
+                        }
+                        else {
+                            mma_m16n8k16(sx[j], ones, bf[j][0], bf[j][1]);
+                        }
+                        mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
+                    }
 #pragma unroll
-                for (int w = 0; w < kTilesPerWarp; ++w) {
-                    if (w < ntw) {
-                        const uint4    wq    = reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes)[lane];
+                    for (int w = 0; w < kTilesPerWarp; ++w) {
+                        const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes);
                         const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
                         for (int wi = 0; wi < 4; ++wi) {
@@ -264,34 +265,39 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
                             unpack_s4_biased(wv[wi], af);
 #pragma unroll
                             for (int j = 0; j < NT; ++j) {
-                                mma_m16n8k16(acc[w][a][j], af, bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                                if (fresh && k16 == 0) {
+                                    mma_m16n8k16_init(acc[w][a][j], af, bf[j][0], bf[j][1]);
+                                }
+                                else {
+                                    mma_m16n8k16(acc[w][a][j], af, bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                                }
                             }
                         }
                     }
                 }
             }
+            s      = (s == ST - 1) ? 0 : s + 1;
+            s_fill = (s_fill == ST - 1) ? 0 : s_fill + 1;
         }
-        s      = (s == ST - 1) ? 0 : s + 1;
-        s_fill = (s_fill == ST - 1) ? 0 : s_fill + 1;
 
-        if (grp_end) {
+        // ---- end of the group: remove offsets and zero point, apply the scale ----------------------
 #pragma unroll
-            for (int w = 0; w < kTilesPerWarp; ++w)
+        for (int w = 0; w < kTilesPerWarp; ++w)
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+            for (int a = 0; a < 2; ++a)
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        tot[w][a][j][0] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][0], acc[w][a][j][0]), tot[w][a][j][0]);
-                        tot[w][a][j][1] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][1], acc[w][a][j][1]), tot[w][a][j][1]);
-                        tot[w][a][j][2] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][0], acc[w][a][j][2]), tot[w][a][j][2]);
-                        tot[w][a][j][3] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][1], acc[w][a][j][3]), tot[w][a][j][3]);
-                        acc[w][a][j][0] = acc[w][a][j][1] = acc[w][a][j][2] = acc[w][a][j][3] = 0.f;
-                    }
-#pragma unroll
-            for (int j = 0; j < NT; ++j) sx[j][0] = sx[j][1] = sx[j][2] = sx[j][3] = 0.f;
-        }
-        const int this_jt = jt;
-        if (++kk == G) {
+                for (int j = 0; j < NT; ++j) {
+                    tot[w][a][j][0] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][0], acc[w][a][j][0]), tot[w][a][j][0]);
+                    tot[w][a][j][1] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[j][1], acc[w][a][j][1]), tot[w][a][j][1]);
+                    tot[w][a][j][2] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][0], acc[w][a][j][2]), tot[w][a][j][2]);
+                    tot[w][a][j][3] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][1], acc[w][a][j][3]), tot[w][a][j][3]);
+                }
+        const int  this_jt = jt;
+        const int  tile0   = jt * kTilesPerUnit;
+        const int  ntw     = min(kTilesPerUnit, n_tiles32 - tile0) - my_t0;  // tiles of this warp that exist
+        const bool seg_end = (it + 2 >= n_units) || (kk + 2 == G);
+        kk += 2;
+        if (kk == G) {
             kk = 0;
             ++jt;
         }
@@ -369,29 +375,30 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
             if (s_flag[0] != 0) {
                 __threadfence();
                 // fixed-order reduction of every CTA's partial: four adjacent columns per thread, the
-                // loads of up to four slots in flight together
-                const int quads = n_cols / 4;
+                // loads of up to eight slots in flight together
+                constexpr int kBatch = 8;
+                const int     quads  = n_cols / 4;
+                const float*  slot0  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(TP * kUnitCols);
                 for (int i = tid; i < t_rows * quads; i += kThreads) {
-                    const int t = i / quads;
-                    const int n = (i - t * quads) * 4;
-                    float4    v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int cc = c_first; cc <= c_last; cc += 4) {
-                        float4 part[4];
+                    const int    t    = i / quads;
+                    const int    n    = (i - t * quads) * 4;
+                    const float* base = slot0 + t * kUnitCols + n;
+                    float4       v    = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int cc = c_first; cc <= c_last; cc += kBatch) {
+                        float4 part[kBatch];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int    ce = min(cc + e, c_last);
-                            const float* sl2 = p.workspace
-                                               + ((size_t)blockIdx.y * p.slots_per_chunk + ce + this_jt) * (size_t)(TP * kUnitCols);
-                            part[e] = __ldcg(reinterpret_cast<const float4*>(sl2 + t * kUnitCols + n));
+                        for (int e = 0; e < kBatch; ++e) {
+                            part[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (cc + e <= c_last) {
+                                part[e] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)(cc + e + this_jt) * (TP * kUnitCols)));
+                            }
                         }
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (cc + e <= c_last) {
-                                v.x += part[e].x;
-                                v.y += part[e].y;
-                                v.z += part[e].z;
-                                v.w += part[e].w;
-                            }
+                        for (int e = 0; e < kBatch; ++e) {
+                            v.x += part[e].x;  // absent slots add +0
+                            v.y += part[e].y;
+                            v.z += part[e].z;
+                            v.w += part[e].w;
                         }
                     }
                     const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
@@ -443,6 +450,7 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem)
     const int slots = sm_count * (pl.nt == 1 ? 2 : 1);  // co-resident CTAs
     int       ctas  = slots < pl.total_units ? slots : pl.total_units;
     pl.units_per_cta    = (pl.total_units + ctas - 1) / ctas;
+    pl.units_per_cta += pl.units_per_cta & 1;  // whole 128-row groups: two units
     pl.ctas             = (pl.total_units + pl.units_per_cta - 1) / pl.units_per_cta;
     pl.slots_per_chunk  = pl.ctas + pl.n_col_tiles;
     pl.stages           = stages_for(pl.nt);

@@ -1,20 +1,21 @@
-// W4A16 GEMM for more than 16 tokens: tcgen05 tensor-core tiles with the accumulator in TMEM.
+// W4A16 GEMM for more than 16 tokens: tcgen05 tensor-core tiles with the accumulators in TMEM.
 //
-// A CTA computes C^T tiles of 128 output features x up to 128 tokens.  It is persistent and
-// stream-K balanced over (128-feature tile, 128-row quantisation group) units, like the
-// small-token kernel.  Warp roles:
-//   warp 0      idle
-//   warp 10     idle
-//   warp 1      allocates TMEM; one elected lane issues tcgen05.mma (M = 128, N = token tile,
-//               K = 16 per instruction, fp16 x fp16 -> fp32) and commits completions to mbarriers
-//   warps 2..9  stream their own share of the packed weight (private cp.async rings) and 1/8 of the
-//               unit's activation slice (into the 128-byte-swizzled K-major layout the tensor core
-//               reads), and expand the weight: lop3 nibble unpack, exact (q - z) in fp16, one fp16
-//               multiply by the scale (bit-identical to the reference's dequantised weight,
-//               kernels/gemm_s_f16/common.h:115-156, 218-235), tcgen05.st of the fragments straight
-//               into TMEM, from where the tensor core takes its A operand (no shared-memory round trip);
-//               at the end of a column tile they read the accumulator with tcgen05.ld and store C
-//               (optionally through the SiLU(gate) * up epilogue) or the split-K partial
+// A CTA computes C^T tiles of 256 output features (two 128-feature UMMA tiles that share one
+// activation slice) x up to 128 tokens.  It is persistent and stream-K balanced over
+// (256-feature tile, 128-row quantisation group) units, like the small-token kernel.  Warp roles:
+//   warp 0       one lane streams the activation slices: two tensor-map copies (TMA, 128-byte
+//                swizzle, tokens beyond T read as zero) per unit, completion on an mbarrier
+//   warps 1, 2   one issuer per 128-feature tile (warp 1 also allocates TMEM): an elected lane issues
+//                tcgen05.mma (M = 128, N = token tile, K = 16 per instruction, fp16 x fp16 -> fp32, A
+//                from TMEM, B from shared memory) and commits completions to mbarriers
+//   warps 3..18  two teams of eight, one per 128-feature tile.  Every warp streams its own share of
+//                the packed weight through a private cp.async ring and expands it: lop3 nibble
+//                unpack, exact (q - z) in fp16, one fp16 multiply by the scale (bit-identical to the
+//                reference's dequantised weight, kernels/gemm_s_f16/common.h:115-156, 218-235),
+//                tcgen05.st of the fragments straight into TMEM, from where the tensor core takes
+//                its A operand (no shared-memory round trip); at the end of a column tile the
+//                warps read the accumulators with tcgen05.ld and store C (optionally through the
+//                SiLU(gate) * up epilogue) or the split-K partial
 // Partial tiles of CTAs that share a column tile meet in scratch memory; the last CTA to arrive
 // reduces them in a fixed order.  Every wait is bounded.
 //
@@ -22,37 +23,33 @@
 // 208-234; mma.sync tiles of gemm_template.h:338-444).
 #include "common.cuh"
 #include "gemm_s4_f16.h"
-// #define TM_B200_TC_TRACE 1   // developer build: per-unit event trace of CTA 1 into GemmTcParams::debug
+
+#include <cuda.h>  // CUtensorMap (types only: the encoder is looked up through the runtime)
 
 namespace tmb {
 namespace {
 
-constexpr int kTileN     = 128;  // output features per CTA tile (UMMA M)
+constexpr int kTileN     = 128;  // output features per UMMA tile (UMMA M)
+constexpr int kTeams     = 2;    // UMMA tiles per CTA tile
+constexpr int kSuperN    = kTileN * kTeams;
 constexpr int kGroup     = 128;  // K extent of a unit
 constexpr int kTileBytes = 512;
-constexpr int kWBytes    = 4 * 4 * kTileBytes;  // [4 k32][4 column tiles][512 B]
-constexpr int kQBytes    = kTileN * 4;
-constexpr int kWStage    = kWBytes + kQBytes;    // 8704
 constexpr int kACols     = kGroup / 2;           // TMEM columns of one expanded weight stage (128 k as fp16 pairs)
 constexpr int kWarpStage = 2 * kTileBytes + 128; // per expanding warp and unit: 2 x 512 B of weight + 32 {zero, scale}
-constexpr int kWSTMax    = 7;                    // stages of those private rings (cp.async groups in flight <= 6)
-constexpr int kAST       = 6;                    // expanded-weight stages (in TMEM)
-constexpr int kAccCols   = 128;                  // accumulator columns (token tile <= 128)
-constexpr int kXSTMax    = 8;                    // activation stages: as many as fit (GemmTcPlan::x_stages), and a
-                                                 // slice is published x_stages - 2 iterations after it was
-                                                 // issued: that many loads are in flight, and publishing
-                                                 // slice j waits at most for the MMA of slice j - 2
-constexpr int kDqWarps   = 8;
-constexpr int kXWarp     = 2 + kDqWarps;         // warp that streams the activations
-constexpr int kThreads   = (3 + kDqWarps) * 32;
-constexpr int kMT        = 1;                    // column tiles that share one activation slice (see the loader)
-constexpr int kTmemCols  = 512;                  // accumulator + kAST x 64 columns of expanded weight, power of two
+constexpr int kWST       = 5;                    // stages of those private rings (cp.async groups in flight <= 4)
+constexpr int kASTMax    = 3;                    // expanded-weight stages per team (in TMEM)
+constexpr int kXSTMax    = 6;                    // activation stages
+constexpr int kTeamWarps = 8;
+constexpr int kDqWarps   = kTeams * kTeamWarps;
+constexpr int kDqThreads = kDqWarps * 32;
+constexpr int kDqWarp0   = 1 + kTeams;           // first expanding warp
+constexpr int kThreads   = (kDqWarp0 + kDqWarps) * 32;
+constexpr int kTmemCols  = 512;                  // accumulators + expanded-weight stages, power of two
 
 struct Bars {
-    uint64_t a_full[kAST], a_empty[kAST];
+    uint64_t a_full[kTeams][kASTMax], a_empty[kTeams][kASTMax];
     uint64_t x_full[kXSTMax], x_empty[kXSTMax];
     uint64_t acc_full, acc_empty;
-    uint64_t probe;  // developer probe: latency of tcgen05.commit -> mbarrier arrival
     uint32_t tmem_base;
     int      flag;
 };
@@ -93,6 +90,17 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One box of the activation tensor map -> shared memory, completion counted on an mbarrier
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(x),
+                 "r"(y),
+                 "r"(smem_u32(bar))
+                 : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before()
 {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -113,12 +121,6 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8])
     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3)
-{
-    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-                 : "memory");
-}
-
 __device__ __forceinline__ uint32_t hmul2_ftz(uint32_t a, uint32_t b)
 {
     uint32_t r;
@@ -126,61 +128,57 @@ __device__ __forceinline__ uint32_t hmul2_ftz(uint32_t a, uint32_t b)
     return r;
 }
 
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 {
-    const int n = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-__device__ __forceinline__ void cp_async_wait_dyn(int n)
+// Non-suspending probe of an mbarrier phase
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
 {
-    switch (n) {
-        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-        default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded spin on an mbarrier phase (the waits of this kernel are short and on its critical path)
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity)
+{
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_test_wait(bar, parity)) {
+        if (clock64() - t0 > kMaxWaitCycles) return false;
+    }
+    return true;
+}
+
+// Bounded wait of a whole warp; on a time-out the warp records `bit` and plays dead from then on.
+__device__ __forceinline__ void warp_wait(uint64_t* bar, uint32_t parity, bool& dead, unsigned* status, unsigned bit)
+{
+    if (dead) return;
+    // one lane polls; the shuffle hands the outcome (and, as a warp-level sync, the ordering) to the rest
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_spin(bar, parity) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) {
+        if ((threadIdx.x & 31) == 0) atomicOr(status, bit);
+        dead = true;
     }
 }
 
-// bounded wait that also accumulates the cycles spent waiting (developer counters)
-#ifdef TM_B200_TC_TRACE
-#define TC_TRACE(role, it, ev)                                                                                          \
-    do {                                                                                                                \
-        if (p.debug != nullptr && blockIdx.x == 1 && blockIdx.y == 0 && (it) < 40)                                      \
-            p.debug[1100 + (role) * 200 + (it) * 4 + (ev)] = clock64() - dbg_t0;                                        \
-    } while (0)
-#else
-#define TC_TRACE(role, it, ev) do {} while (0)
-#endif
-#ifdef TM_B200_TC_PROFILE
-#define TC_CLOCK() clock64()
-#else
-#define TC_CLOCK() 0ll
-#endif
-__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, long long& acc)
+__global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParams p, const __grid_constant__ CUtensorMap x_map)
 {
-    const long long t0 = TC_CLOCK();
-    const bool      ok = mbar_wait(bar, parity);
-    acc += TC_CLOCK() - t0;
-    return ok;
-}
-
-__global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParams p)
-{
-    long long dbg_w0 = 0, dbg_w1 = 0, dbg_w2 = 0, dbg_epi = 0;
-    unsigned long long gt_start, gt_last_unit = 0, gt_fin = 0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_start));
-#ifdef TM_B200_TC_TRACE
-    const long long dbg_t0 = clock64();
-#else
-    const long long dbg_t0 = TC_CLOCK();
-#endif
-    const int kXST  = p.x_stages;
-    const int kXLag = p.x_lag;
-    const int kWST  = p.w_stages;  // copies of kWST - 1 units in flight per warp (weight + activation share)
+    const int kXST = p.x_stages;
+    const int kAST = p.a_stages;    // per team
+    const int accS = p.acc_stride;  // TMEM columns between the two accumulators
     extern __shared__ unsigned char smem_dyn[];
     // tiles the tensor core reads must sit on 1024-byte boundaries (the swizzle is a function of
     // the address bits)
@@ -191,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     const int TT      = p.token_tile;             // UMMA N, multiple of 16, <= 128
     const int x_bytes = 2 * TT * 128;             // two K blocks of TT rows x 128 B
     unsigned char* x_ring = sm;                                   // kXST x x_bytes (multiples of 1024)
-    unsigned char* w_ring = x_ring + kXST * x_bytes;              // kWST x kWStage
+    unsigned char* w_ring = x_ring + kXST * x_bytes;              // kDqWarps x kWST x kWarpStage
     Bars*          bars   = reinterpret_cast<Bars*>(w_ring + kWST * kDqWarps * kWarpStage);
 
     const int tid  = threadIdx.x;
@@ -201,24 +199,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     const int t0     = blockIdx.y * 128;
     const int t_rows = min(TT, p.T - t0);
 
-    const int G       = p.K / kGroup;
-    const int upc     = p.units_per_cta;
-    const int u_begin = blockIdx.x * upc;
-    const int u_end   = min(u_begin + upc, p.total_units);
-    const int n_units = u_end - u_begin;
+    const int G         = p.K / kGroup;
+    const int upc       = p.units_per_cta;
+    const int u_begin   = blockIdx.x * upc;
+    const int n_units   = min(u_begin + upc, p.total_units) - u_begin;
     const int n_tiles32 = p.N / 32;
 
     if (tid == 0) {
-        for (int s = 0; s < kAST; ++s) {
-            mbar_init(&bars->a_full[s], kDqWarps);
-            mbar_init(&bars->a_empty[s], 1);
+        for (int m = 0; m < kTeams; ++m) {
+            for (int s = 0; s < kASTMax; ++s) {
+                mbar_init(&bars->a_full[m][s], kTeamWarps);
+                mbar_init(&bars->a_empty[m][s], 1);
+            }
         }
         for (int s = 0; s < kXSTMax; ++s) {
-            mbar_init(&bars->x_full[s], 32);
-            mbar_init(&bars->x_empty[s], 1);
+            mbar_init(&bars->x_full[s], 1);
+            mbar_init(&bars->x_empty[s], kTeams);
         }
-        mbar_init(&bars->probe, 1);
-        mbar_init(&bars->acc_full, 1);
+        mbar_init(&bars->acc_full, kTeams);
         mbar_init(&bars->acc_empty, kDqWarps);
         fence_mbar_init();
     }
@@ -231,108 +229,66 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = bars->tmem_base;
-    const long long dbg_t1 = TC_CLOCK();
+    const uint32_t tmem   = bars->tmem_base;
+    const uint32_t a_base = tmem + kTeams * accS;  // first expanded-weight stage
 
     if (warp == 0) {
-        // idle: the packed weight is streamed by the warps that expand it (private cp.async rings)
-    }
-    else if (warp == kXWarp) {
         // ================================================================== activation loader
-        // slice [TT rows][128 k] of a group -> two 64-wide K blocks, rows of 128 B with their 16-byte
-        // chunks XOR-swizzled by (row & 7): the layout the tensor core expects.  One slice serves the
-        // kMT consecutive units (column tiles) that share the group.  Lane = (row & 3, chunk).
-        const int      ch   = lane & 7;
-        const int      tr   = lane >> 3;
-        const uint32_t sw0  = (uint32_t)((ch ^ tr) << 4);        // rows tr, tr + 8, ...
-        const uint32_t sw1  = (uint32_t)((ch ^ (tr + 4)) << 4);  // rows tr + 4, tr + 12, ...
-        bool           dead = false;
-        const int      n_slices = (n_units + kMT - 1) / kMT;
-        int            g    = (u_begin / kMT) % G;
-        for (int it = 0; it < ((p.dev_mode & 32) ? 0 : n_slices + kXLag); ++it) {
-            if (it < n_slices) {
-                const int sx = it % kXST;
-                if (!dead && it >= kXST) {
-                    const bool ok = timed_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dbg_w0);
-                    if (!__all_sync(0xffffffffu, ok)) {
-                        if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
-                        dead = true;
-                    }
+        // slice [TT tokens][128 k] of a group -> two 64-wide K blocks, rows of 128 B with their 16-byte
+        // chunks XOR-swizzled by (row & 7): the layout the tensor core expects and the one a tensor-map
+        // copy with 128-byte swizzle writes.  One slice serves both feature tiles of the unit.
+        bool dead = false;
+        int  g    = u_begin % G;
+        for (int it = 0; it < n_units; ++it) {
+            const int sx = it % kXST;
+            if (it >= kXST) warp_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dead, p.status, kStatusGemmPipeWait);
+            if (!dead && lane == 0) {
+                const uint32_t xb = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
+                if (p.dev_mode & 16) {
+                    mbar_arrive(&bars->x_full[sx]);  // developer experiment: no activation copy
                 }
-                if (!dead && !(p.dev_mode & 4)) {
-                    const uint32_t       xb      = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
-                    const size_t         row_b   = (size_t)p.K * 2;
-                    const unsigned char* src_col = p.X + ((size_t)g * kGroup + ch * 8) * 2;
-#pragma unroll
-                    for (int kb = 0; kb < 2; ++kb) {
-                        const unsigned char* src = src_col + kb * 128 + (size_t)(t0 + tr) * row_b;
-                        uint32_t             dst = xb + kb * (TT * 128) + tr * 128;
-                        for (int t = tr; t < TT; t += 8) {
-                            const bool ok0 = t < t_rows, ok1 = t + 4 < t_rows;
-                            cp_async16_zfill(dst + sw0, ok0 ? src : p.X, ok0);
-                            cp_async16_zfill(dst + 512 + sw1, ok1 ? src + 4 * row_b : p.X, ok1);
-                            src += 8 * row_b;
-                            dst += 1024;
-                        }
-                    }
+                else {
+                    mbar_arrive_expect_tx(&bars->x_full[sx], (uint32_t)x_bytes);
+                    tma_load_2d(xb, &x_map, g * kGroup, t0, &bars->x_full[sx]);
+                    tma_load_2d(xb + TT * 128, &x_map, g * kGroup + 64, t0, &bars->x_full[sx]);
                 }
-                if (++g == G) g = 0;
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            // the slice issued kXLag iterations ago has landed: publish it to the tensor core
-            const int done = it - kXLag;
-            if (done >= 0) {
-                cp_async_wait_dyn(kXLag);
-                fence_proxy_async_smem();
-                if (!dead) mbar_arrive(&bars->x_full[done % kXST]);
-            }
+            __syncwarp();
+            if (++g == G) g = 0;
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
     }
-    else if (warp == 1) {
-        // ================================================================== MMA issuer
+    else if (warp <= kTeams) {
+        // ================================================================== MMA issuers, one per team
+        const int      m     = warp - 1;
         const uint32_t idesc = (1u << 4) | ((uint32_t)(TT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+        const uint32_t d_tmem = tmem + m * accS;
+        const uint32_t kb_step = (uint32_t)(TT * 128) >> 4;  // descriptor units (16 B) between the two K blocks
         bool dead    = false;
         int  seg_idx = 0;
         bool first   = true;  // first MMA of the current segment overwrites the accumulator
-        for (int it = 0; it < ((p.dev_mode & 32) ? 0 : n_units); ++it) {
-            const int u  = u_begin + it;
-            const int g  = u % G;
-            const int sa = it % kAST, sx = it % kXST;
-            if (first && seg_idx > 0 && !dead) {
-                // the epilogue of the previous segment must have drained the accumulator
-                const bool ok = timed_wait(&bars->acc_empty, (seg_idx - 1) & 1, dbg_w0);
-                if (!__all_sync(0xffffffffu, ok)) dead = true;
+        int  g       = u_begin % G;
+        int  sa = 0, sx = 0, pa = 0, px = 0;  // stage and phase parity of the weight / activation rings
+        for (int it = 0; it < n_units; ++it) {
+            if (first && seg_idx > 0) {
+                // the epilogue of the previous segment must have drained the accumulators
+                warp_wait(&bars->acc_empty, (seg_idx - 1) & 1, dead, p.status, kStatusGemmTmemWait);
             }
-            if (!dead) {
-                const bool ok = timed_wait(&bars->a_full[sa], (it / kAST) & 1, dbg_w0)
-                                && timed_wait(&bars->x_full[sx], (it / kXST) & 1, dbg_w0);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
-                    dead = true;
-                }
-            }
+            warp_wait(&bars->x_full[sx], px, dead, p.status, kStatusGemmPipeWait);
+            warp_wait(&bars->a_full[m][sa], pa, dead, p.status, kStatusGemmPipeWait);
             tc_fence_after();
-            if (lane == 0) TC_TRACE(1, it, 0);
             if (!dead && lane == 0) {
-                const long long ti0 = TC_CLOCK();
-                const uint32_t a_tmem = tmem + kAccCols + sa * kACols;
-                const uint32_t x_addr = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
+                const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols;
+                const uint64_t d0     = make_desc(base + (uint32_t)(x_ring - sm) + sx * x_bytes);
+                uint32_t       accum  = first ? 0u : 1u;
 #pragma unroll
-                for (int kb = 0; kb < 2; ++kb) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        if (p.dev_mode & 1) continue;  // developer experiment: no MMA
-                        const uint64_t db = make_desc(x_addr + kb * (TT * 128) + ks * 32);
-                        umma_f16_ts(tmem, a_tmem + (kb * 4 + ks) * 8, db, idesc, (first && kb == 0 && ks == 0) ? 0u : 1u);
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    if (p.dev_mode & 4) continue;
+                    // K block j / 4, 16-wide K step j % 4 (32 bytes inside the 128-byte rows)
+                    umma_f16_ts(d_tmem, a_tmem + j * 8, d0 + (uint64_t)((j >> 2) * kb_step + (j & 3) * 2), idesc, accum);
+                    accum = 1u;
                 }
-                const long long ti1 = TC_CLOCK();
-                umma_commit(&bars->a_empty[sa]);
+                umma_commit(&bars->a_empty[m][sa]);
                 umma_commit(&bars->x_empty[sx]);
-                dbg_w1 += ti1 - ti0;            // (developer counters: x_full waits are folded into w0 below)
-                dbg_w2 += TC_CLOCK() - ti1;
-                TC_TRACE(1, it, 1);
             }
             first = false;
             const bool seg_end = (it == n_units - 1) || (g == G - 1);
@@ -341,87 +297,62 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 ++seg_idx;
                 first = true;
             }
+            if (++g == G) g = 0;
+            if (++sa == kAST) { sa = 0; pa ^= 1; }
+            if (++sx == kXST) { sx = 0; px ^= 1; }
             __syncwarp();
-        }
-        if (p.debug != nullptr && blockIdx.x == 1 && lane == 0 && !dead) {
-            // developer probe: all MMAs have been issued; how long until a commit with nothing (new)
-            // in front of it reaches its barrier, and how long an empty commit takes right after
-            const long long c0 = clock64();
-            umma_commit(&bars->probe);
-            (void)mbar_wait(&bars->probe, 0);
-            const long long c1 = clock64();
-            umma_commit(&bars->probe);
-            (void)mbar_wait(&bars->probe, 1);
-            const long long c2 = clock64();
-            p.debug[19] = c1 - c0;
-            p.debug[20] = c2 - c1;
         }
     }
     else {
         // ================================================================== expand + epilogue
-        const int  dw   = warp - 2;       // 0..7
-        const int  tile = warp & 3;       // 32-feature column tile expanded by this warp = its TMEM lane quarter
-        const int  kh   = dw >> 2;        // which pair of 32-row slabs of the group
+        const int  dw   = warp - kDqWarp0; // 0..15
+        const int  m    = dw >> 3;         // team = 128-feature tile of the unit
+        const int  q    = warp & 3;        // TMEM lane quarter this warp may access = its 32-feature tile
+        const int  kh   = (dw >> 2) & 1;   // which pair of 32-row slabs of the group it expands,
+                                           // and which half of the token columns it drains
         const int  r    = lane >> 2;
-        const int  c    = lane & 3;
-        const int  q4   = warp & 3;       // TMEM lane quarter this warp may read
-        const int  chalf = dw >> 2;       // which half of the token columns it drains
         bool       dead = false;
         int        seg_idx = 0;
-        const int  dtid = tid - 64;
+        const int  dtid = tid - kDqWarp0 * 32;
 
-
-        // private ring of this warp: per unit its own 2 x 512 B of packed weight (column tile `tile`,
+        // private ring of this warp: per unit its own 2 x 512 B of packed weight (32-feature tile,
         // 32-row slabs 2 kh, 2 kh + 1 of the group) + the 128 B of {zero, scale} of its 32 features
-        const uint32_t my_ring = base + (uint32_t)(w_ring - sm) + dw * kWST * kWarpStage;
-        int            ijt = u_begin / G, ig = u_begin - ijt * G;  // unit the next copy is issued for
-        int  i_it = 0;  // index (CTA-local) of the unit the next copy is issued for
+        const uint32_t       my_ring = base + (uint32_t)(w_ring - sm) + dw * kWST * kWarpStage;
+        const unsigned char* my_ring_g = w_ring + dw * kWST * kWarpStage;
+        int                  i_js = u_begin / G, i_g = u_begin - i_js * G;  // unit the next copy is issued for
         auto issue_unit = [&](int stage) {
-            ++i_it;
-            const int tile0 = ijt * 4;
-            if (tile0 + tile < n_tiles32) {
+            const int tile = (i_js * kTeams + m) * 4 + q;
+            if (tile < n_tiles32 && !(p.dev_mode & 8)) {
                 const uint32_t       dst = my_ring + stage * kWarpStage + lane * 16;
-                const unsigned char* src = p.A + (((size_t)ig * 4 + kh * 2) * n_tiles32 + tile0 + tile) * kTileBytes + lane * 16;
-                cp_async16_zfill(dst, src, true);
-                cp_async16_zfill(dst + kTileBytes, src + (size_t)n_tiles32 * kTileBytes, true);
+                const unsigned char* src = p.A + (((size_t)i_g * 4 + kh * 2) * n_tiles32 + tile) * kTileBytes + lane * 16;
+                cp_async16(dst, src);
+                cp_async16(dst + kTileBytes, src + (size_t)n_tiles32 * kTileBytes);
                 if (lane < 8) {
-                    cp_async16_zfill(dst + 2 * kTileBytes, p.Q + ((size_t)ig * p.N + (size_t)(tile0 + tile) * 32) * 4 + lane * 16, true);
+                    cp_async16(dst + 2 * kTileBytes, p.Q + ((size_t)i_g * p.N + (size_t)tile * 32) * 4 + lane * 16);
                 }
             }
-            if (++ig == G) {
-                ig = 0;
-                ++ijt;
+            if (++i_g == G) {
+                i_g = 0;
+                ++i_js;
             }
         };
+#pragma unroll
         for (int sidx = 0; sidx < kWST - 1; ++sidx) {
             if (sidx < n_units) issue_unit(sidx);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
 
+        int js = u_begin / G, g = u_begin - js * G;
+        int sw = 0;
         for (int it = 0; it < n_units; ++it) {
-            const int u     = u_begin + it;
-            const int jt    = u / G;
-            const int g     = u - jt * G;
-            const int tile0 = jt * 4;
-            const int ntw   = min(4, n_tiles32 - tile0);
-            const int sw = it % kWST, sa = it % kAST;
-            cp_async_wait_dyn(kWST - 2);
+            const int  sa     = it % kAST;
+            const bool exists = (js * kTeams + m) * 4 + q < n_tiles32;
+            asm volatile("cp.async.wait_group %0;" ::"n"(kWST - 2) : "memory");
             __syncwarp();
-            if (warp == 2 && lane == 0) TC_TRACE(2, it, 0);
-
-            if (!dead) {
-                bool ok = true;
-                if (it >= kAST && !(p.dev_mode & 32)) ok = timed_wait(&bars->a_empty[sa], ((it / kAST) - 1) & 1, dbg_w0);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (lane == 0) atomicOr(p.status, kStatusGemmPipeWait);
-                    dead = true;
-                }
-            }
-            const long long te0 = TC_CLOCK();
-            if (warp == 2 && lane == 0) TC_TRACE(2, it, 1);
-            if (!dead && tile < ntw && !(p.dev_mode & 2)) {
+            if (it >= kAST) warp_wait(&bars->a_empty[m][sa], ((it / kAST) - 1) & 1, dead, p.status, kStatusGemmPipeWait);
+            if (!dead && exists) {
                 tc_fence_after();
-                const unsigned char* sb = w_ring + (dw * kWST + sw) * kWarpStage;
+                const unsigned char* sb = my_ring_g + sw * kWarpStage;
                 const __half2*       qs = reinterpret_cast<const __half2*>(sb + 2 * kTileBytes);
                 uint32_t z1024[2], nz64[2], s_lo[2], s_hi[2];
 #pragma unroll
@@ -437,74 +368,82 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                     s_lo[a]  = reinterpret_cast<const uint32_t&>(sl2);
                     s_hi[a]  = reinterpret_cast<const uint32_t&>(sh2);
                 }
-                const uint32_t a_tmem = tmem + kAccCols + sa * kACols + ((uint32_t)(tile * 32) << 16);
+                const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols + ((uint32_t)(q * 32) << 16);
+                // all fragments first (independent chains the scheduler can interleave), then the stores
+                uint32_t f[8][4];
 #pragma unroll
                 for (int kk = 0; kk < 2; ++kk) {
-                    const int   k32 = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
-                    const uint4 w   = reinterpret_cast<const uint4*>(sb)[kk * 32 + lane];
+                    const uint4    w     = reinterpret_cast<const uint4*>(sb)[kk * 32 + lane];
                     const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                     for (int wi = 0; wi < 4; ++wi) {
-                        const int k16 = wi >> 1;
-                        const int a   = wi & 1;
-                        uint32_t  f[4];
-                        unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], f);
-                        f[0] = hmul2_ftz(f[0], s_lo[a]);
-                        f[1] = hmul2_ftz(f[1], s_hi[a]);
-                        f[2] = hmul2_ftz(f[2], s_lo[a]);
-                        f[3] = hmul2_ftz(f[3], s_hi[a]);
-                        // rows tile*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
-                        tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), f[0], f[1], f[2],
-                                           f[3]);
+                        const int a = wi & 1;
+                        uint32_t (&fr)[4] = f[kk * 4 + wi];
+                        if (p.dev_mode & 2) {
+                            fr[0] = fr[1] = fr[2] = fr[3] = wv[wi];
+                        }
+                        else {
+                            unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], fr);
+                            fr[0] = hmul2_ftz(fr[0], s_lo[a]);
+                            fr[1] = hmul2_ftz(fr[1], s_hi[a]);
+                            fr[2] = hmul2_ftz(fr[2], s_lo[a]);
+                            fr[3] = hmul2_ftz(fr[3], s_hi[a]);
+                        }
+                    }
+                }
+                if (!(p.dev_mode & 1)) {
+#pragma unroll
+                    for (int kk = 0; kk < 2; ++kk) {
+                        const int k32 = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) {
+                            const int k16 = wi >> 1;
+                            const int a   = wi & 1;
+                            const uint32_t (&fr)[4] = f[kk * 4 + wi];
+                            // rows q*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
+                            tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), fr[0], fr[1], fr[2],
+                                               fr[3]);
+                        }
                     }
                 }
             }
             // expanded tile visible to the tensor core; packed stage free again
-            const long long te1 = TC_CLOCK();
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0 && !dead) {
-                mbar_arrive(&bars->a_full[sa]);
-            }
-            if (warp == 2 && lane == 0) TC_TRACE(2, it, 2);
+            if (lane == 0 && !dead) mbar_arrive(&bars->a_full[m][sa]);
             // refill the slot that was read one unit ago (everyone in the warp is past its reads)
-            if (it + kWST - 1 < n_units) issue_unit((it + kWST - 1) % kWST);
+            if (it + kWST - 1 < n_units) issue_unit(sw == 0 ? kWST - 1 : sw - 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
-            dbg_w1 += te1 - te0;
-            dbg_w2 += TC_CLOCK() - te1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_last_unit));
+            sw = (sw == kWST - 1) ? 0 : sw + 1;
 
+            const int  this_js = js;
             const bool seg_end = (it == n_units - 1) || (g == G - 1);
-            if (!seg_end || (p.dev_mode & 32)) continue;
-
-            // ---- column tile jt finished for this CTA: drain the accumulator ------------------
-            const int c_first = (jt * G) / upc;
-            const int c_last  = ((jt + 1) * G - 1) / upc;
-            const int n_split = c_last - c_first + 1;
-            const int col0    = jt * kTileN;
-            if (!dead) {
-                const bool ok = timed_wait(&bars->acc_full, seg_idx & 1, dbg_w0);
-                if (!__all_sync(0xffffffffu, ok)) {
-                    if (lane == 0) atomicOr(p.status, kStatusGemmTmemWait);
-                    dead = true;
-                }
+            if (++g == G) {
+                g = 0;
+                ++js;
             }
+            if (!seg_end) continue;
+
+            // ---- 256-feature tile this_js finished for this CTA: drain the accumulators ------------
+            const int c_first = (this_js * G) / upc;
+            const int c_last  = ((this_js + 1) * G - 1) / upc;
+            const int n_split = c_last - c_first + 1;
+            const int col0    = this_js * kSuperN;
+            warp_wait(&bars->acc_full, seg_idx & 1, dead, p.status, kStatusGemmTmemWait);
             tc_fence_after();
-            const long long tp0 = TC_CLOCK();
-            long long tp1 = tp0, tp2 = tp0, tp3 = tp0, tp4 = tp0;
-            const int n_row   = q4 * 32 + lane;         // feature row of the tile held by this thread
-            const int n_glob  = col0 + n_row;
-            const int ccount  = TT / 2;                 // token columns per warp
-            float*    slot    = p.workspace + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + jt) * (size_t)(128 * kTileN);
-            if (!dead && !(p.dev_mode & 8)) {
+            const int n_row  = m * kTileN + q * 32 + lane;  // feature row of the CTA tile held by this thread
+            const int n_glob = col0 + n_row;
+            const int ccount = TT / 2;                      // token columns per warp
+            float*    slot   = p.workspace + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + this_js) * (size_t)(128 * kSuperN);
+            if (!dead && !(p.dev_mode & 32)) {
                 for (int cb = 0; cb < ccount; cb += 8) {
-                    const int col = chalf * ccount + cb;
+                    const int col = kh * ccount + cb;
                     float     v[8];
-                    tmem_ld8(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)col, v);
+                    tmem_ld8(tmem + m * accS + ((uint32_t)(q * 32) << 16) + (uint32_t)col, v);
                     if (n_split > 1) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) __stcg(slot + (size_t)(col + i) * kTileN + n_row, v[i]);
+                        for (int i = 0; i < 8; ++i) __stcg(slot + (size_t)(col + i) * kSuperN + n_row, v[i]);
                     }
                     else {
 #pragma unroll
@@ -529,47 +468,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             __syncwarp();
             if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
             ++seg_idx;
-            tp1 = TC_CLOCK();
 
-            if (n_split > 1) {
+            if (n_split > 1 && !(p.dev_mode & 32)) {
                 __threadfence();
-                tp2 = TC_CLOCK();
-                named_bar_sync(1, kDqWarps * 32);
+                named_bar_sync(1, kDqThreads);
                 if (dtid == 0) {
-                    int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + jt;
+                    int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + this_js;
                     const int ticket  = atomicAdd(counter, 1);
                     const int is_last = ticket == n_split - 1;
                     if (is_last) *counter = 0;
                     bars->flag = is_last;
                 }
-                named_bar_sync(1, kDqWarps * 32);
-                tp3 = TC_CLOCK();
+                named_bar_sync(1, kDqThreads);
                 if (bars->flag && !dead) {
-                    gt_fin += 1;
                     __threadfence();
-                    // fixed-order reduction of every CTA's partial.  Each thread owns up to 8 groups of
-                    // 4 adjacent features at a time and walks the slots with all 8 loads in flight.
-                    const int n_cols = min(kTileN, p.N - col0);
-                    const int quads  = n_cols / 4;  // N % 32 == 0
-                    const int items  = t_rows * quads;
-                    for (int i0 = dtid; i0 < items; i0 += kDqWarps * 32 * 8) {
-                        float4 acc[8];
+                    // fixed-order reduction of every CTA's partial.  Each thread owns up to 4 groups of
+                    // 4 adjacent features at a time and walks the slots with all 4 loads in flight.
+                    const int    n_cols = min(kSuperN, p.N - col0);
+                    const int    quads  = n_cols / 4;  // N % 32 == 0
+                    const int    items  = t_rows * quads;
+                    const float* slot0  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
+                    for (int i0 = dtid; i0 < items; i0 += kDqThreads * 4) {
+                        float4 acc[4];
+                        int    off[4];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int j = 0; j < 4; ++j) {
+                            acc[j]       = make_float4(0.f, 0.f, 0.f, 0.f);
+                            const int i  = i0 + j * kDqThreads;
+                            const int ii = i < items ? i : i0;
+                            const int t  = ii / quads;
+                            off[j]       = t * kSuperN + (ii - t * quads) * 4;
+                        }
                         for (int cc = c_first; cc <= c_last; ++cc) {
-                            const float* sl = p.workspace
-                                              + ((size_t)blockIdx.y * p.slots_per_chunk + cc + jt) * (size_t)(128 * kTileN);
-                            float4 v[8];
+                            const float* sl = slot0 + (size_t)(cc + this_js) * (size_t)(128 * kSuperN);
+                            float4       v[4];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {  // all loads of the slot first: they overlap
-                                const int i  = i0 + j * kDqWarps * 32;
-                                const int ii = i < items ? i : i0;
-                                const int t  = ii / quads;
-                                const int n  = (ii - t * quads) * 4;
-                                v[j]         = __ldcg(reinterpret_cast<const float4*>(sl + (size_t)t * kTileN + n));
-                            }
+                            for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(sl + off[j]));
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
+                            for (int j = 0; j < 4; ++j) {
                                 acc[j].x += v[j].x;
                                 acc[j].y += v[j].y;
                                 acc[j].z += v[j].z;
@@ -577,11 +513,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                             }
                         }
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int i = i0 + j * kDqWarps * 32;
+                        for (int j = 0; j < 4; ++j) {
+                            const int i = i0 + j * kDqThreads;
                             if (i < items) {
-                                const int     t  = i / quads;
-                                const int     n  = (i - t * quads) * 4;
+                                const int     t  = off[j] / kSuperN;
+                                const int     n  = off[j] - t * kSuperN;
                                 const __half2 h0 = __floats2half2_rn(acc[j].x, acc[j].y);
                                 const __half2 h1 = __floats2half2_rn(acc[j].z, acc[j].w);
                                 if (p.fused_silu) {
@@ -599,49 +535,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                         }
                     }
                 }
-                named_bar_sync(1, kDqWarps * 32);
-            }
-            tp4 = TC_CLOCK();
-            dbg_epi += tp4 - tp0;
-            if (p.debug != nullptr && blockIdx.y == 0 && dtid == 0 && blockIdx.x < 8) {
-                long long* e = p.debug + 940 + blockIdx.x * 8;
-                e[0] = tp0 - (tp0 - 0);  // placeholder keeps layout simple
-                e[1] = tp1 - tp0;        // drain + stores
-                e[2] = tp2 - tp1;        // __threadfence
-                e[3] = tp3 - tp2;        // ticket + barriers
-                e[4] = tp4 - tp3;        // finalize (if last) + barrier
-                e[5] = (long long)gt_fin;
-                e[6] = n_split;
+                named_bar_sync(1, kDqThreads);
             }
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
     }
 
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    if (p.debug != nullptr && blockIdx.y == 0 && warp == 2 && lane == 0) {
-        // developer timeline of every CTA: start, last unit expanded, end (ns, global timer), finalizes, units, SM id
-        unsigned long long gt_end;
-        unsigned           smid;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_end));
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        long long* row = p.debug + 32 + blockIdx.x * 6;
-        row[0] = (long long)gt_start;
-        row[1] = (long long)gt_last_unit;
-        row[2] = (long long)gt_end;
-        row[3] = (long long)gt_fin;
-        row[4] = n_units;
-        row[5] = smid;
-    }
-    if (p.debug != nullptr && blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (warp <= 2 || warp == kXWarp)) {
-        // developer counters of CTA 1: per role {total cycles, wait 0, wait 1, wait 2}
-        const int role = warp == kXWarp ? 3 : warp;
-        p.debug[role * 4 + 0] = TC_CLOCK() - dbg_t0;
-        p.debug[role * 4 + 1] = dbg_w0;
-        p.debug[role * 4 + 2] = dbg_w1;
-        p.debug[role * 4 + 3] = dbg_w2;
-        if (warp == 0) p.debug[16] = n_units;
-        if (warp == 1) p.debug[17] = dbg_t1 - dbg_t0;
-        if (warp == 2) p.debug[18] = dbg_epi;
-    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -649,24 +548,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     }
 }
 
+using PFN_encodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// the driver's tensor-map encoder, found through the runtime so that the library does not link libcuda
+PFN_encodeTiled lookup_encode_tiled()
+{
+    void*                           fn = nullptr;
+    cudaDriverEntryPointQueryResult q{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess
+        || q != cudaDriverEntryPointSuccess) {
+        return nullptr;
+    }
+    return reinterpret_cast<PFN_encodeTiled>(fn);
+}
+
+int x_stages_for(int token_tile) { return token_tile > 64 ? 3 : kXSTMax; }
+int a_stages_for(int token_tile) { return token_tile > 64 ? 2 : kASTMax; }
+int acc_stride_for(int token_tile) { return token_tile > 64 ? 128 : 64; }
+
 }  // namespace
-
-int gemm_tc_x_stages(int token_tile)
-{
-    return token_tile > 64 ? 5 : 8;
-}
-
-int gemm_tc_w_stages(int token_tile)
-{
-    // unit it + w_stages - 1 is issued while unit it is expanded; its activation slot must have been
-    // released by the MMA of unit it + w_stages - 1 - x_stages: keep that at least 3 units back
-    return gemm_tc_x_stages(token_tile) - 2;
-}
 
 size_t gemm_tc_smem_bytes(int token_tile)
 {
-    return 1024 + (size_t)gemm_tc_x_stages(token_tile) * 2 * token_tile * 128
-           + (size_t)gemm_tc_w_stages(token_tile) * kDqWarps * kWarpStage + sizeof(Bars) + 64;
+    return 1024 + (size_t)x_stages_for(token_tile) * 2 * token_tile * 128 + (size_t)kWST * kDqWarps * kWarpStage + sizeof(Bars) + 64;
 }
 
 GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
@@ -674,7 +580,7 @@ GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
     GemmTcPlan pl{};
     pl.token_tile  = T >= 128 ? 128 : ((T + 15) / 16) * 16;
     pl.t_chunks    = (T + 127) / 128;
-    pl.n_col_tiles = (N + kTileN - 1) / kTileN;
+    pl.n_col_tiles = (N + kSuperN - 1) / kSuperN;
     const int G    = K / kGroup;
     pl.total_units = pl.n_col_tiles * G;
     int ctas       = sm_count < pl.total_units ? sm_count : pl.total_units;
@@ -682,7 +588,7 @@ GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
     pl.ctas            = (pl.total_units + pl.units_per_cta - 1) / pl.units_per_cta;
     pl.slots_per_chunk = pl.ctas + pl.n_col_tiles;
     pl.smem_bytes      = gemm_tc_smem_bytes(pl.token_tile);
-    pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * 128 * kTileN;
+    pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * 128 * kSuperN;
     pl.counter_ints     = (size_t)pl.t_chunks * pl.n_col_tiles;
     return pl;
 }
@@ -699,13 +605,26 @@ cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st
     p.slots_per_chunk = pl.slots_per_chunk;
     p.n_col_tiles     = pl.n_col_tiles;
     p.token_tile      = pl.token_tile;
-    p.x_stages        = gemm_tc_x_stages(pl.token_tile);
-    // loads in flight = x_lag slices; the ring is deeper than that so that issuing slice j + x_lag (and
-    // with it publishing slice j) only needs the MMA of slice j + x_lag - x_stages to have retired
-    p.x_lag           = pl.token_tile > 64 ? 2 : 3;
-    p.w_stages        = gemm_tc_w_stages(pl.token_tile);
+    p.x_stages        = x_stages_for(pl.token_tile);
+    p.a_stages        = a_stages_for(pl.token_tile);
+    p.acc_stride      = acc_stride_for(pl.token_tile);
+
+    // Activations as a 2-D tensor [T][K] of fp16; one box = 64 k (128 bytes, the swizzle span) x token tile.
+    static const PFN_encodeTiled encode = lookup_encode_tiled();
+    if (encode == nullptr) return cudaErrorNotSupported;
+    CUtensorMap       x_map;
+    const cuuint64_t  dims[2]    = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+    const cuuint64_t  strides[1] = {(cuuint64_t)p.K * 2};
+    const cuuint32_t  box[2]     = {64u, (cuuint32_t)pl.token_tile};
+    const cuuint32_t  estr[2]    = {1u, 1u};
+    if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<unsigned char*>(p.X), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+        != CUDA_SUCCESS) {
+        return cudaErrorInvalidValue;
+    }
     dim3 grid(pl.ctas, pl.t_chunks);
-    gemm_s4_f16_tc_kernel<<<grid, kThreads, pl.smem_bytes, st>>>(p);
+    gemm_s4_f16_tc_kernel<<<grid, kThreads, pl.smem_bytes, st>>>(p, x_map);
     return cudaGetLastError();
 }
 

@@ -20,10 +20,8 @@ struct tm_handle {
     unsigned*          status          = nullptr;  // device status word (bounded waits)
     int                last_cuda_error = 0;
     unsigned long long launches        = 0;
-    long long*         debug_buf       = nullptr;  // 64 KB of developer counters when debug_counters is set
-    int                tc_dev_mode     = 0;  // TM_B200_TC_DEV_MODE: timing experiments (results are then wrong)
-    int                debug_counters  = 0;  // TM_B200_DEBUG_COUNTERS=1: kernels of CTA 1 record wait cycles
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
+    int                tc_dev_mode     = 0;  // TM_B200_TC_DEV_MODE: timing experiments (results are then wrong)
     int                gemv_dev_mode   = 0;  // TM_B200_GEMV_DEV_MODE: timing experiments (results are then wrong)
 };

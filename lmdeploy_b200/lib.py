@@ -87,7 +87,6 @@ SIGNATURES = {
     "tm_last_cuda_error": (_i, [_vp]),
     "tm_check_device_status": (_i, [_vp, _vp, C.POINTER(C.c_uint)]),
     "tm_launch_count": (C.c_ulonglong, [_vp]),
-    "tm_debug_counters": (_i, [_vp, _vp, C.POINTER(C.c_longlong)]),
     "tm_gemm_s4_f16_workspace_bytes": (_sz, [_i, _i, _i]),
     "tm_gemm_s4_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "tm_gemm_s4_f16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
