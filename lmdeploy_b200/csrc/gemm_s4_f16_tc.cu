@@ -259,26 +259,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     }
     else if (warp <= kTeams) {
         // ================================================================== MMA issuers, one per team
-        const int      m     = warp - 1;
-        const uint32_t idesc = (1u << 4) | ((uint32_t)(TT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-        const uint32_t d_tmem = tmem + m * accS;
-        const uint32_t kb_step = (uint32_t)(TT * 128) >> 4;  // descriptor units (16 B) between the two K blocks
-        bool dead    = false;
-        int  seg_idx = 0;
-        bool first   = true;  // first MMA of the current segment overwrites the accumulator
-        int  g       = u_begin % G;
-        int  sa = 0, sx = 0, pa = 0, px = 0;  // stage and phase parity of the weight / activation rings
-        for (int it = 0; it < n_units; ++it) {
-            if (first && seg_idx > 0) {
-                // the epilogue of the previous segment must have drained the accumulators
-                warp_wait(&bars->acc_empty, (seg_idx - 1) & 1, dead, p.status, kStatusGemmTmemWait);
-            }
-            warp_wait(&bars->x_full[sx], px, dead, p.status, kStatusGemmPipeWait);
-            warp_wait(&bars->a_full[m][sa], pa, dead, p.status, kStatusGemmPipeWait);
-            tc_fence_after();
-            if (!dead && lane == 0) {
+        // A single lane runs the whole loop: waits, eight MMAs, commits.  Nothing here needs the warp.
+        if (lane == 0) {
+            const int      m       = warp - 1;
+            const uint32_t idesc   = (1u << 4) | ((uint32_t)(TT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+            const uint32_t d_tmem  = tmem + m * accS;
+            const uint32_t kb_step = (uint32_t)(TT * 128) >> 4;  // descriptor units (16 B) between the two K blocks
+            const uint64_t d_ring  = make_desc(base + (uint32_t)(x_ring - sm));
+            const uint32_t x_step  = (uint32_t)x_bytes >> 4;
+            int  seg_idx = 0;
+            bool first   = true;  // first MMA of the current segment overwrites the accumulator
+            int  g       = u_begin % G;
+            int  sa = 0, sx = 0;
+            uint32_t pa = 0, px = 0;  // phase parity of the weight / activation rings
+            for (int it = 0; it < n_units; ++it) {
+                bool ok = true;
+                if (first && seg_idx > 0) {
+                    // the epilogue of the previous segment must have drained the accumulators
+                    ok = mbar_spin(&bars->acc_empty, (seg_idx - 1) & 1);
+                }
+                ok = ok && mbar_spin(&bars->x_full[sx], px) && mbar_spin(&bars->a_full[m][sa], pa);
+                if (!ok) {
+                    atomicOr(p.status, kStatusGemmPipeWait);
+                    break;
+                }
+                tc_fence_after();
                 const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols;
-                const uint64_t d0     = make_desc(base + (uint32_t)(x_ring - sm) + sx * x_bytes);
+                const uint64_t d0     = d_ring + (uint64_t)(sx * x_step);
                 uint32_t       accum  = first ? 0u : 1u;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -289,19 +296,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
                 umma_commit(&bars->a_empty[m][sa]);
                 umma_commit(&bars->x_empty[sx]);
+                first = false;
+                if ((it == n_units - 1) || (g == G - 1)) {
+                    umma_commit(&bars->acc_full);
+                    ++seg_idx;
+                    first = true;
+                }
+                if (++g == G) g = 0;
+                if (++sa == kAST) { sa = 0; pa ^= 1; }
+                if (++sx == kXST) { sx = 0; px ^= 1; }
             }
-            first = false;
-            const bool seg_end = (it == n_units - 1) || (g == G - 1);
-            if (seg_end) {
-                if (!dead && lane == 0) umma_commit(&bars->acc_full);
-                ++seg_idx;
-                first = true;
-            }
-            if (++g == G) g = 0;
-            if (++sa == kAST) { sa = 0; pa ^= 1; }
-            if (++sx == kXST) { sx = 0; px ^= 1; }
-            __syncwarp();
         }
+        __syncwarp();
     }
     else {
         // ================================================================== expand + epilogue
@@ -435,40 +441,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int n_row  = m * kTileN + q * 32 + lane;  // feature row of the CTA tile held by this thread
             const int n_glob = col0 + n_row;
             const int ccount = TT / 2;                      // token columns per warp
-            float*    slot   = p.workspace + ((size_t)blockIdx.y * p.slots_per_chunk + blockIdx.x + this_js) * (size_t)(128 * kSuperN);
+            // split-K partials: [slot][128 tokens][256 feature rows] fp32 (a warp touches 128 contiguous bytes per token)
+            float* const slots = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
+            const uint32_t my_acc = tmem + m * accS + ((uint32_t)(q * 32) << 16);
+            // eight token columns of this thread's feature row -> C
+            auto store_c = [&](const float (&v)[8], int col) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int t = t0 + col + i;
+                    if (p.fused_silu) {
+                        // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pair (gate, up) = rows (n, n + 1)
+                        const float mine  = __half2float(__float2half_rn(v[i]));
+                        const float other = __shfl_down_sync(0xffffffffu, mine, 1);
+                        if ((lane & 1) == 0 && t < p.T && n_glob < p.N) {
+                            const float silu = mine / (1.f + __expf(-mine));
+                            p.C[(size_t)t * (p.N / 2) + n_glob / 2] = __float2half_rn(silu * other);
+                        }
+                    }
+                    else if (t < p.T && n_glob < p.N) {
+                        p.C[(size_t)t * p.N + n_glob] = __float2half_rn(v[i]);
+                    }
+                }
+            };
             if (!dead && !(p.dev_mode & 32)) {
+                float* mine = slots + (size_t)(blockIdx.x + this_js) * (size_t)(128 * kSuperN) + n_row;
                 for (int cb = 0; cb < ccount; cb += 8) {
                     const int col = kh * ccount + cb;
                     float     v[8];
-                    tmem_ld8(tmem + m * accS + ((uint32_t)(q * 32) << 16) + (uint32_t)col, v);
+                    tmem_ld8(my_acc + (uint32_t)col, v);
                     if (n_split > 1) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) __stcg(slot + (size_t)(col + i) * kSuperN + n_row, v[i]);
+                        for (int i = 0; i < 8; ++i) __stcg(mine + (size_t)(col + i) * kSuperN, v[i]);
                     }
                     else {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int t = t0 + col + i;
-                            if (p.fused_silu) {
-                                const float mine  = __half2float(__float2half_rn(v[i]));
-                                const float other = __shfl_down_sync(0xffffffffu, mine, 1);
-                                if ((lane & 1) == 0 && t < p.T && n_glob < p.N) {
-                                    const float silu = mine / (1.f + __expf(-mine));
-                                    p.C[(size_t)t * (p.N / 2) + n_glob / 2] = __float2half_rn(silu * other);
-                                }
-                            }
-                            else if (t < p.T && n_glob < p.N) {
-                                p.C[(size_t)t * p.N + n_glob] = __float2half_rn(v[i]);
-                            }
-                        }
+                        store_c(v, col);
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
             ++seg_idx;
-
             if (n_split > 1 && !(p.dev_mode & 32)) {
                 __threadfence();
                 named_bar_sync(1, kDqThreads);
@@ -482,61 +492,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 named_bar_sync(1, kDqThreads);
                 if (bars->flag && !dead) {
                     __threadfence();
-                    // fixed-order reduction of every CTA's partial.  Each thread owns up to 4 groups of
-                    // 4 adjacent features at a time and walks the slots with all 4 loads in flight.
-                    const int    n_cols = min(kSuperN, p.N - col0);
-                    const int    quads  = n_cols / 4;  // N % 32 == 0
-                    const int    items  = t_rows * quads;
-                    const float* slot0  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
-                    for (int i0 = dtid; i0 < items; i0 += kDqThreads * 4) {
-                        float4 acc[4];
-                        int    off[4];
+                    // Last CTA of the tile: sum the partials in CTA order.  Its own term comes from the
+                    // accumulator, which is still in TMEM; the others are read with up to four slots in flight.
+                    const int me = blockIdx.x;
+                    for (int cb = 0; cb < ccount; cb += 8) {
+                        const int col = kh * ccount + cb;
+                        float     own[8], acc[8];
+                        tmem_ld8(my_acc + (uint32_t)col, own);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            acc[j]       = make_float4(0.f, 0.f, 0.f, 0.f);
-                            const int i  = i0 + j * kDqThreads;
-                            const int ii = i < items ? i : i0;
-                            const int t  = ii / quads;
-                            off[j]       = t * kSuperN + (ii - t * quads) * 4;
-                        }
-                        for (int cc = c_first; cc <= c_last; ++cc) {
-                            const float* sl = slot0 + (size_t)(cc + this_js) * (size_t)(128 * kSuperN);
-                            float4       v[4];
+                        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                        for (int cc = c_first; cc <= c_last; cc += 4) {
+                            float part[4][8];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(sl + off[j]));
+                            for (int e = 0; e < 4; ++e) {
+                                const bool   live = cc + e <= c_last && cc + e != me;
+                                const float* src  = slots + (size_t)(cc + e + this_js) * (size_t)(128 * kSuperN) + (size_t)col * kSuperN + n_row;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                acc[j].x += v[j].x;
-                                acc[j].y += v[j].y;
-                                acc[j].z += v[j].z;
-                                acc[j].w += v[j].w;
+                                for (int i = 0; i < 8; ++i) part[e][i] = live ? __ldcg(src + (size_t)i * kSuperN) : 0.f;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) acc[i] += (cc + e == me) ? own[i] : part[e][i];  // absent slots add +0
                             }
                         }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int i = i0 + j * kDqThreads;
-                            if (i < items) {
-                                const int     t  = off[j] / kSuperN;
-                                const int     n  = off[j] - t * kSuperN;
-                                const __half2 h0 = __floats2half2_rn(acc[j].x, acc[j].y);
-                                const __half2 h1 = __floats2half2_rn(acc[j].z, acc[j].w);
-                                if (p.fused_silu) {
-                                    const float2 u0 = __half22float2(h0), u1 = __half22float2(h1);
-                                    const float  s0 = u0.x / (1.f + __expf(-u0.x)), s1 = u1.x / (1.f + __expf(-u1.x));
-                                    *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2) =
-                                        __floats2half2_rn(s0 * u0.y, s1 * u1.y);
-                                }
-                                else {
-                                    __half2* dst = reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n);
-                                    dst[0]       = h0;
-                                    dst[1]       = h1;
-                                }
-                            }
-                        }
+                        store_c(acc, col);
                     }
                 }
-                named_bar_sync(1, kDqThreads);
             }
+            // the accumulators may be overwritten now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
+            if (n_split > 1 && !(p.dev_mode & 32)) named_bar_sync(1, kDqThreads);  // the flag is reused by the next segment
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     }
