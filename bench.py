@@ -355,10 +355,12 @@ def run_decode_workload(args, rank, world, device, name):
         sampler = ClockSampler(device)
         sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.cudart().cudaProfilerStart()           # a profiler started with capture off sees the timed steps only
         e0.record(stream)
         model.decode(st, K, use_graph=True)
         e1.record(stream)
         torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
         barrier(world)
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop()

@@ -133,40 +133,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-// Non-suspending probe of an mbarrier phase
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded spin on an mbarrier phase (the waits of this kernel are short and on its critical path)
-__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity)
-{
-    if (mbar_test_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_test_wait(bar, parity)) {
-        if (clock64() - t0 > kMaxWaitCycles) return false;
-    }
-    return true;
-}
-
 // Bounded wait of a whole warp; on a time-out the warp records `bit` and plays dead from then on.
 __device__ __forceinline__ void warp_wait(uint64_t* bar, uint32_t parity, bool& dead, unsigned* status, unsigned bit)
 {
     if (dead) return;
     // one lane polls; the shuffle hands the outcome (and, as a warp-level sync, the ordering) to the rest
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_spin(bar, parity) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;  // suspending wait: leaves the issue slots to the busy warps
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) {
         if ((threadIdx.x & 31) == 0) atomicOr(status, bit);
@@ -276,9 +249,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 bool ok = true;
                 if (first && seg_idx > 0) {
                     // the epilogue of the previous segment must have drained the accumulators
-                    ok = mbar_spin(&bars->acc_empty, (seg_idx - 1) & 1);
+                    ok = mbar_wait(&bars->acc_empty, (seg_idx - 1) & 1);
                 }
-                ok = ok && mbar_spin(&bars->x_full[sx], px) && mbar_spin(&bars->a_full[m][sa], pa);
+                ok = ok && mbar_wait(&bars->x_full[sx], px) && mbar_wait(&bars->a_full[m][sa], pa);
                 if (!ok) {
                     atomicOr(p.status, kStatusGemmPipeWait);
                     break;
