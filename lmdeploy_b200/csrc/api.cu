@@ -68,7 +68,6 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->gemv_dev_mode = env_int("TM_B200_GEMV_DEV_MODE", 0);
-    h->tc_dev_mode   = env_int("TM_B200_TC_DEV_MODE", 0);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     cudaSetDevice(prev);
@@ -188,7 +187,6 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
-            p.dev_mode   = h->tc_dev_mode;
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
             h->launches += 1;
             if (e != cudaSuccess) {

@@ -54,7 +54,6 @@ struct GemmTcParams {
     unsigned*            status;
     int                  N, T, K;
     int                  fused_silu;
-    int                  dev_mode;  // developer experiments (TM_B200_TC_DEV_MODE): 1 no TMEM store, 2 no expand math, 4 no MMA, 8 no weight copies
     // filled in by gemm_tc_launch from the plan
     int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, a_stages, acc_stride;
 };

@@ -217,14 +217,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             if (it >= kXST) warp_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dead, p.status, kStatusGemmPipeWait);
             if (!dead && lane == 0) {
                 const uint32_t xb = base + (uint32_t)(x_ring - sm) + sx * x_bytes;
-                if (p.dev_mode & 16) {
-                    mbar_arrive(&bars->x_full[sx]);  // developer experiment: no activation copy
-                }
-                else {
-                    mbar_arrive_expect_tx(&bars->x_full[sx], (uint32_t)x_bytes);
-                    tma_load_2d(xb, &x_map, g * kGroup, t0, &bars->x_full[sx]);
-                    tma_load_2d(xb + TT * 128, &x_map, g * kGroup + 64, t0, &bars->x_full[sx]);
-                }
+                mbar_arrive_expect_tx(&bars->x_full[sx], (uint32_t)x_bytes);
+                tma_load_2d(xb, &x_map, g * kGroup, t0, &bars->x_full[sx]);
+                tma_load_2d(xb + TT * 128, &x_map, g * kGroup + 64, t0, &bars->x_full[sx]);
             }
             __syncwarp();
             if (++g == G) g = 0;
@@ -262,7 +257,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 uint32_t       accum  = first ? 0u : 1u;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    if (p.dev_mode & 4) continue;
                     // K block j / 4, 16-wide K step j % 4 (32 bytes inside the 128-byte rows)
                     umma_f16_ts(d_tmem, a_tmem + j * 8, d0 + (uint64_t)((j >> 2) * kb_step + (j & 3) * 2), idesc, accum);
                     accum = 1u;
@@ -298,39 +292,53 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         // 32-row slabs 2 kh, 2 kh + 1 of the group) + the 128 B of {zero, scale} of its 32 features
         const uint32_t       my_ring = base + (uint32_t)(w_ring - sm) + dw * kWST * kWarpStage;
         const unsigned char* my_ring_g = w_ring + dw * kWST * kWarpStage;
-        int                  i_js = u_begin / G, i_g = u_begin - i_js * G;  // unit the next copy is issued for
+        // state of the copy front (runs kWST - 1 units ahead of the expansion): this lane's 16 bytes of
+        // the warp's first slab and of the {zero, scale} row.  A warp whose tile lies beyond N re-reads
+        // the last tile; what it produces is never stored.
+        int                  i_js = u_begin / G, i_g = u_begin - i_js * G;
+        const unsigned char* i_w  = nullptr;
+        const unsigned char* i_q  = nullptr;
+        const size_t         slab_b  = (size_t)n_tiles32 * kTileBytes;  // bytes between 32-row slabs
+        const size_t         q_row_b = (size_t)p.N * 4;                 // bytes between {zero, scale} rows
+        auto i_seek = [&]() {
+            const int tile = min((i_js * kTeams + m) * 4 + q, n_tiles32 - 1);
+            i_w = p.A + (((size_t)i_g * 4 + kh * 2) * n_tiles32 + tile) * kTileBytes + lane * 16;
+            i_q = p.Q + ((size_t)i_g * p.N + (size_t)tile * 32) * 4 + (lane & 7) * 16;
+        };
+        i_seek();
+        int to_issue = n_units;
         auto issue_unit = [&](int stage) {
-            const int tile = (i_js * kTeams + m) * 4 + q;
-            if (tile < n_tiles32 && !(p.dev_mode & 8)) {
-                const uint32_t       dst = my_ring + stage * kWarpStage + lane * 16;
-                const unsigned char* src = p.A + (((size_t)i_g * 4 + kh * 2) * n_tiles32 + tile) * kTileBytes + lane * 16;
-                cp_async16(dst, src);
-                cp_async16(dst + kTileBytes, src + (size_t)n_tiles32 * kTileBytes);
-                if (lane < 8) {
-                    cp_async16(dst + 2 * kTileBytes, p.Q + ((size_t)i_g * p.N + (size_t)tile * 32) * 4 + lane * 16);
-                }
-            }
+            const uint32_t dst = my_ring + stage * kWarpStage + lane * 16;
+            cp_async16(dst, i_w);
+            cp_async16(dst + kTileBytes, i_w + slab_b);
+            if (lane < 8) cp_async16(dst + 2 * kTileBytes, i_q);
+            i_w += 4 * slab_b;
+            i_q += q_row_b;
             if (++i_g == G) {
                 i_g = 0;
                 ++i_js;
+                i_seek();
             }
         };
 #pragma unroll
         for (int sidx = 0; sidx < kWST - 1; ++sidx) {
-            if (sidx < n_units) issue_unit(sidx);
+            if (to_issue > 0) issue_unit(sidx);
+            --to_issue;
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
 
-        int js = u_begin / G, g = u_begin - js * G;
-        int sw = 0;
+        int      js = u_begin / G, g = u_begin - js * G;
+        int      sw = 0, sw_fill = kWST - 1;  // ring slot read now / refilled now (the one read one unit ago)
+        int      sa = 0;
+        uint32_t pa = 0;                      // phase parity of the team's expanded-weight ring
         for (int it = 0; it < n_units; ++it) {
-            const int  sa     = it % kAST;
-            const bool exists = (js * kTeams + m) * 4 + q < n_tiles32;
             asm volatile("cp.async.wait_group %0;" ::"n"(kWST - 2) : "memory");
             __syncwarp();
-            if (it >= kAST) warp_wait(&bars->a_empty[m][sa], ((it / kAST) - 1) & 1, dead, p.status, kStatusGemmPipeWait);
-            if (!dead && exists) {
-                tc_fence_after();
+            // the tensor core must be done with what this TMEM stage held kAST units ago (the first
+            // round passes at once: a fresh barrier counts as having completed the phase before)
+            warp_wait(&bars->a_empty[m][sa], pa ^ 1u, dead, p.status, kStatusGemmPipeWait);
+            tc_fence_after();
+            {
                 const unsigned char* sb = my_ring_g + sw * kWarpStage;
                 const __half2*       qs = reinterpret_cast<const __half2*>(sb + 2 * kTileBytes);
                 uint32_t z1024[2], nz64[2], s_lo[2], s_hi[2];
@@ -358,31 +366,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                     for (int wi = 0; wi < 4; ++wi) {
                         const int a = wi & 1;
                         uint32_t (&fr)[4] = f[kk * 4 + wi];
-                        if (p.dev_mode & 2) {
-                            fr[0] = fr[1] = fr[2] = fr[3] = wv[wi];
-                        }
-                        else {
-                            unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], fr);
-                            fr[0] = hmul2_ftz(fr[0], s_lo[a]);
-                            fr[1] = hmul2_ftz(fr[1], s_hi[a]);
-                            fr[2] = hmul2_ftz(fr[2], s_lo[a]);
-                            fr[3] = hmul2_ftz(fr[3], s_hi[a]);
-                        }
+                        unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], fr);
+                        fr[0] = hmul2_ftz(fr[0], s_lo[a]);
+                        fr[1] = hmul2_ftz(fr[1], s_hi[a]);
+                        fr[2] = hmul2_ftz(fr[2], s_lo[a]);
+                        fr[3] = hmul2_ftz(fr[3], s_hi[a]);
                     }
                 }
-                if (!(p.dev_mode & 1)) {
 #pragma unroll
-                    for (int kk = 0; kk < 2; ++kk) {
-                        const int k32 = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
+                for (int kk = 0; kk < 2; ++kk) {
+                    const int k32 = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
 #pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) {
-                            const int k16 = wi >> 1;
-                            const int a   = wi & 1;
-                            const uint32_t (&fr)[4] = f[kk * 4 + wi];
-                            // rows q*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
-                            tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), fr[0], fr[1], fr[2],
-                                               fr[3]);
-                        }
+                    for (int wi = 0; wi < 4; ++wi) {
+                        const int k16 = wi >> 1;
+                        const int a   = wi & 1;
+                        const uint32_t (&fr)[4] = f[kk * 4 + wi];
+                        // rows q*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
+                        tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), fr[0], fr[1], fr[2],
+                                           fr[3]);
                     }
                 }
             }
@@ -390,11 +391,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0 && !dead) mbar_arrive(&bars->a_full[m][sa]);
+            if (lane == 0) mbar_arrive(&bars->a_full[m][sa]);
             // refill the slot that was read one unit ago (everyone in the warp is past its reads)
-            if (it + kWST - 1 < n_units) issue_unit(sw == 0 ? kWST - 1 : sw - 1);
+            if (to_issue > 0) issue_unit(sw_fill);
+            --to_issue;
             asm volatile("cp.async.commit_group;" ::: "memory");
-            sw = (sw == kWST - 1) ? 0 : sw + 1;
+            sw      = (sw == kWST - 1) ? 0 : sw + 1;
+            sw_fill = (sw_fill == kWST - 1) ? 0 : sw_fill + 1;
+            if (++sa == kAST) {
+                sa = 0;
+                pa ^= 1u;
+            }
 
             const int  this_js = js;
             const bool seg_end = (it == n_units - 1) || (g == G - 1);
@@ -436,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                     }
                 }
             };
-            if (!dead && !(p.dev_mode & 32)) {
+            if (!dead) {
                 float* mine = slots + (size_t)(blockIdx.x + this_js) * (size_t)(128 * kSuperN) + n_row;
                 for (int cb = 0; cb < ccount; cb += 8) {
                     const int col = kh * ccount + cb;
@@ -452,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
             }
             ++seg_idx;
-            if (n_split > 1 && !(p.dev_mode & 32)) {
+            if (n_split > 1) {
                 __threadfence();
                 named_bar_sync(1, kDqThreads);
                 if (dtid == 0) {
@@ -497,7 +504,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             tc_fence_before();
             __syncwarp();
             if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
-            if (n_split > 1 && !(p.dev_mode & 32)) named_bar_sync(1, kDqThreads);  // the flag is reused by the next segment
+            if (n_split > 1) named_bar_sync(1, kDqThreads);  // the flag is reused by the next segment
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     }

@@ -22,6 +22,5 @@ struct tm_handle {
     unsigned long long launches        = 0;
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
-    int                tc_dev_mode     = 0;  // TM_B200_TC_DEV_MODE: timing experiments (results are then wrong)
     int                gemv_dev_mode   = 0;  // TM_B200_GEMV_DEV_MODE: timing experiments (results are then wrong)
 };
