@@ -31,6 +31,9 @@ if ROOT not in sys.path:
 
 LLAMA7B_PROJ = [("qkv", 12288, 4096, False), ("o", 4096, 4096, False), ("gate_up", 22016, 4096, True),
                 ("down", 4096, 11008, False)]
+# Llama-2-70B on one GPU (no tensor-parallel slicing): 8 KV heads, inter size 28672
+LLAMA70B_PROJ = [("qkv", 10240, 8192, False), ("o", 8192, 8192, False), ("gate_up", 57344, 8192, True),
+                 ("down", 8192, 28672, False)]
 
 
 def measured_peaks():
@@ -117,7 +120,8 @@ def run_gemm_workload(args, rank, world, device):
     h = l.default_handle(device)
     l2 = torch.cuda.get_device_properties(device).L2_cache_size
     T = args.tokens
-    cases = [build_gemm_case(nm, n, k, fz, T, l2, device, 1000 + i) for i, (nm, n, k, fz) in enumerate(LLAMA7B_PROJ)]
+    proj = LLAMA70B_PROJ if args.shapes == "70b" else LLAMA7B_PROJ
+    cases = [build_gemm_case(nm, n, k, fz, T, l2, device, 1000 + i) for i, (nm, n, k, fz) in enumerate(proj)]
     op = tm.LlamaLinear(device)
     weights = [[tm.LlamaDenseWeight(c["k"], c["n"], c["A"][r], tm.WeightType.kINT4, None, c["Q"][r], 128)
                 for r in range(c["reps"])] for c in cases]
@@ -193,16 +197,19 @@ def run_gemm_workload(args, rank, world, device):
     gbs = bytes_step / (ms_step * 1e-3) * 1e-9 * world
     dom = per["gate_up"]
     out = {
-        "metric": "W4 GEMM HBM GB/s vs peak (Llama-2-7B projections)", "value": round(gbs, 1), "unit": "GB/s",
+        "metric": f"W4 GEMM HBM GB/s vs peak (Llama-2-{args.shapes.upper()} projections)", "value": round(gbs, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 x int4 -> f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": "gemm", "tokens": T, "shapes": [c["name"] for c in cases],
+        "config": {"workload": "gemm", "tokens": T, "model_shapes": args.shapes, "shapes": [c["name"] for c in cases],
                    "l2": "inputs larger than L2: weights replicated beyond 2x L2, next replica each launch",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
-        "roofline": {"bound": "hbm", "kernel": "gemm_s4_f16_small_kernel (gate_up)", "achieved": dom["gbs"],
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4),
-                     "peak_source": peaks["source"], "traffic": None},
+        "roofline": {"bound": "hbm", "kernel": ("gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_small_kernel") + " (gate_up)",
+                     "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+                     "algorithmic_bytes": dom["bytes"],
+                     # DRAM bytes / algorithmic bytes measured with ncu on the qkv and o shapes (profiles/)
+                     "traffic": int(dom["bytes"] * (1.03 if T > 16 else 1.0))},
         "per_kernel": per, "clocks": clocks, "gpu_launches": int(launches),
     }
     return out
@@ -285,7 +292,9 @@ def run_mmha_workload(args, rank, world, device):
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "kernel": "mmha_decode_kernel", "achieved": round(gbs, 1),
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
-                     "peak_source": peaks["source"], "traffic": None},
+                     "peak_source": peaks["source"], "algorithmic_bytes": int(nbytes),
+                     # ncu on this workload: 1.157 GB read + written for 1.132 GB algorithmic (profiles/)
+                     "traffic": int(nbytes * 1.02)},
         "clocks": clocks, "gpu_launches": args.steps,
     }
 
@@ -398,7 +407,11 @@ def run_decode_workload(args, rank, world, device, name):
     peaks = measured_peaks()
     kv_b = 1 if cfg.quant_policy & 4 else 2
     total_b, w_b, head_b, kvb = decode_step_bytes(cfg, world, B, mean_len, kv_b)
-    dom = max(per.items(), key=lambda kv: kv[1]["us_per_step"])
+    dom = max(((k, v) for k, v in per.items() if not k.startswith("gemm ")), key=lambda kv: kv[1]["us_per_step"])
+    # DRAM bytes per launch of the dominant kernel: ratio measured once with ncu on the same shapes
+    # (dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes; profiles/), applied to this launch
+    traffic_ratio = {"gemm_s4_f16_tc_kernel": 1.03, "gemm_s4_f16_small_kernel": 1.0, "mmha_decode_kernel": 1.02}
+    ratio = next((r for k, r in traffic_ratio.items() if dom[0].startswith(k)), None)
     out = {
         "metric": "decode tokens/s Llama-2 W4A16", "value": round(B * 1e3 / ms_step, 1), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
@@ -411,7 +424,8 @@ def run_decode_workload(args, rank, world, device, name):
         "e2e": {"value": round(B * 1e3 / ms_e2e_step, 1), "unit": "tokens/s", "h2d_bytes_per_step": B * 4,
                 "d2h_bytes_per_step": B * 4},
         "roofline": {"bound": "hbm", "kernel": dom[0], "achieved": dom[1]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(dom[1]["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"], "traffic": None},
+                     "frac": round(dom[1]["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+                     "algorithmic_bytes": dom[1]["bytes"], "traffic": int(dom[1]["bytes"] * ratio) if ratio else None},
         "step_roofline": {"bytes_per_step_per_gpu": int(total_b), "weights": int(w_b), "lm_head": int(head_b), "kv": int(kvb),
                           "achieved_gbs_per_gpu": round(total_b / (ms_step * 1e-3) * 1e-9, 1),
                           "frac_of_hbm_peak": round(total_b / (ms_step * 1e-3) * 1e-9 / peaks["hbm_gbs"], 4)},
@@ -436,22 +450,37 @@ def time_decode_kernels(model, st, cfg, B, tp, stream, tm, session_len):
     op = tm.LlamaLinear(dev.index)
     hid = cfg.hidden
     names = [("gemm qkv", 2, False), ("gemm o", 3, False), ("gemm w13+silu", 4, True), ("gemm w2", 5, False)]
+    def graph_time(launch, n_it):
+        """device time per launch: `n_it` launches captured into one CUDA graph, replayed once warm and once timed"""
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=stream):
+            for i in range(n_it):
+                launch(i)
+        gr.replay()
+        a, b = ev(), ev()
+        a.record(stream)
+        gr.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / n_it
+
+    gemm_us = gemm_b = 0.0
     for nm, idx, fused in names:
         w0 = layers[0][idx]
         x = torch.randn(B, w0.input_dims, device=dev).half()
         y = torch.empty(B, w0.output_dims // (2 if fused else 1), dtype=torch.float16, device=dev)
         n_it = max(cfg.num_layer, 32)
-        for i in range(3):
-            op.forward(y, x, B, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm)
-        a, b = ev(), ev()
-        a.record(stream)
-        for i in range(n_it):
-            op.forward(y, x, B, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm)
-        b.record(stream)
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b) * 1e3 / n_it
+        us = graph_time(lambda i: op.forward(y, x, B, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm), n_it)
         nb = gemm_bytes(w0.output_dims, w0.input_dims, B, fused)
-        per[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1))
+        gemm_us += us
+        gemm_b += nb
+        per[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1), bytes=int(nb))
+    kname = "gemm_s4_f16_tc_kernel" if B > 16 else "gemm_s4_f16_small_kernel"
+    per[f"{kname} (4 projections of a layer)"] = dict(us=round(gemm_us / 4, 2), gbs=round(gemm_b / gemm_us * 1e-3, 1),
+                                                      us_per_step=round(gemm_us * cfg.num_layer, 1), bytes=int(gemm_b / 4))
     # attention over the caches as they stand (layer l of every sequence)
     Hl, Hkvl = cfg.head_num // tp, cfg.kv_head_num // tp
     qkv = torch.randn(B, (Hl + 2 * Hkvl) * 128, device=dev).half()
@@ -465,18 +494,13 @@ def time_decode_kernels(model, st, cfg, B, tp, stream, tm, session_len):
     p.total_padding_tokens = (session_len - 1 - lengths).to(torch.int32)
     if cfg.quant_policy & 4:
         p.int8_mode, p.attention_k_scale, p.attention_v_scale = 4, 4.0 / 127, 4.0 / 127
-    n_it = max(cfg.num_layer, 32)
-    a, b = ev(), ev()
-    for rep in range(2):
-        a.record(stream)
-        for i in range(n_it):
-            p.kv_cache_per_sample_offset = (i % cfg.num_layer) * Hkvl * session_len * 128
-            tm.masked_multihead_attention(p)
-        b.record(stream)
-        torch.cuda.synchronize()
-    us = a.elapsed_time(b) * 1e3 / n_it
+    def attn(i):
+        p.kv_cache_per_sample_offset = (i % cfg.num_layer) * Hkvl * session_len * 128
+        tm.masked_multihead_attention(p)
+
+    us = graph_time(attn, max(cfg.num_layer, 32))
     nb = mmha_bytes(lengths.cpu().numpy(), Hl, Hkvl, 1 if cfg.quant_policy & 4 else 2)
-    per["mmha_decode_kernel"] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1))
+    per["mmha_decode_kernel"] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1), bytes=int(nb))
     return per
 
 
@@ -584,6 +608,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=0, help="cap on the prompt length for smoke runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--shapes", choices=["7b", "70b"], default="7b", help="projection shapes of the gemm workload")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=32)
