@@ -8,6 +8,10 @@
 
 using namespace tmb;
 
+namespace tmb {
+thread_local int g_pdl = 0;
+}
+
 namespace {
 
 int env_int(const char* name, int dflt)
@@ -68,6 +72,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->gemv_dev_mode = env_int("TM_B200_GEMV_DEV_MODE", 0);
+    h->pdl           = env_int("TM_B200_PDL", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     cudaSetDevice(prev);
@@ -187,7 +192,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
-            cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream);
+            cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
             h->launches += 1;
             if (e != cudaSuccess) {
                 h->last_cuda_error = (int)e;
@@ -241,7 +246,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
         p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
         p.dev_mode   = h->gemv_dev_mode;
 
-        cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream);
+        cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
         h->launches += 1;
         if (e != cudaSuccess) {
             h->last_cuda_error = (int)e;
@@ -331,7 +336,7 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     p.counters        = h->attn_counters;
     p.status          = h->status;
 
-    cudaError_t e = mmha_launch(pl, p, int8, (cudaStream_t)stream);
+    cudaError_t e = mmha_launch(pl, p, int8, (cudaStream_t)stream, g_pdl != 0);
     h->launches += 1;
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -346,7 +351,7 @@ extern "C" int tm_rmsnorm(void* out, const void* in, const void* scale, float ep
     if (n % 8 || n > 16384) return TM_ERR_UNSUPPORTED;
     if (((uintptr_t)out | (uintptr_t)in | (uintptr_t)scale) & 15u) return TM_ERR_INVALID_ARG;
     if (m == 0) return TM_OK;
-    return rmsnorm_launch((__half*)out, (const __half*)in, (const __half*)scale, eps, m, n, (cudaStream_t)stream)
+    return rmsnorm_launch((__half*)out, (const __half*)in, (const __half*)scale, eps, m, n, (cudaStream_t)stream, g_pdl != 0)
                    == cudaSuccess ?
                TM_OK :
                TM_ERR_CUDA;
@@ -360,7 +365,7 @@ extern "C" int tm_add_residual_rmsnorm(
     if (((uintptr_t)residual | (uintptr_t)in_out | (uintptr_t)scale | (uintptr_t)bias) & 15u) return TM_ERR_INVALID_ARG;
     if (m == 0) return TM_OK;
     return add_residual_rmsnorm_launch((__half*)residual, (__half*)in_out, (const __half*)bias, (const __half*)scale, eps,
-                                       m, n, (cudaStream_t)stream)
+                                       m, n, (cudaStream_t)stream, g_pdl != 0)
                    == cudaSuccess ?
                TM_OK :
                TM_ERR_CUDA;

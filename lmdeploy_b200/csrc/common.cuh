@@ -121,6 +121,20 @@ __device__ __forceinline__ uint64_t policy_evict_last()
     return p;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream is still running; pdl_wait() returns once that predecessor
+// has completed and its writes are visible (a no-op for a normal launch).  Everything before it may
+// only read data that no kernel writes (weights).  pdl_launch_dependents() lets the successor start;
+// the kernels here call it after their own wait, so at most two kernels overlap.
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -166,6 +180,23 @@ __device__ __forceinline__ void unpack_s4_minus_zero(uint32_t w, uint32_t z1024_
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[1]) : "r"(t1), "r"(kSixteenth), "r"(nz64_hi));
     asm("sub.f16x2 %0, %1, %2;" : "=r"(out[2]) : "r"(t2), "r"(z1024_lo));
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[3]) : "r"(t3), "r"(kSixteenth), "r"(nz64_hi));
+}
+
+// Kernel launch with or without the programmatic-serialization attribute
+template<typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = grid;
+    cfg.blockDim         = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs                                          = attr;
+    cfg.numAttrs                                       = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace tmb

@@ -41,7 +41,7 @@ struct GemmSmallPlan {
 size_t        gemm_small_smem_bytes(int nt);
 GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem);
 cudaError_t   gemm_small_prepare(int max_smem);
-cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st);
+cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st, bool pdl = false);
 
 // ---- tensor-core (tcgen05) kernel for more than 16 tokens ---------------------------------
 struct GemmTcParams {
@@ -74,6 +74,6 @@ struct GemmTcPlan {
 size_t      gemm_tc_smem_bytes(int token_tile);
 GemmTcPlan  gemm_tc_plan(int N, int T, int K, int sm_count);
 cudaError_t gemm_tc_prepare(int max_smem);
-cudaError_t gemm_tc_launch(const GemmTcPlan& plan, GemmTcParams p, cudaStream_t st);
+cudaError_t gemm_tc_launch(const GemmTcPlan& plan, GemmTcParams p, cudaStream_t st, bool pdl = false);
 
 }  // namespace tmb

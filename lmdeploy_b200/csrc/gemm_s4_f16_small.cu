@@ -152,7 +152,8 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
         i_qok  = lane < 16 && i_tile * kColsPerTile + lane * 4 < p.N;
     };
     i_seek();
-    auto issue_unit = [&](int stage) {
+    // `with_x`: also the unit's activations (not before pdl_wait(): they come from the kernel before this one)
+    auto issue_unit = [&](int stage, bool with_x) {
         const uint32_t dst = ring_s + stage * kWarpStage + lane * 16;
         // the warp's two tiles are adjacent in memory: 1 KB contiguous per slab
         cp_async16(dst, i_w);
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
             if (i_qok) cp_async16(dst + 2 * kSlabBytes, i_q);
             i_q += (size_t)p.N * 4;
         }
-        if (x_loader) cp_async16(x_dst + stage * kXUnit, x_base + (size_t)i_k * (kUnitRows * 2));
+        if (with_x && x_loader) cp_async16(x_dst + stage * kXUnit, x_base + (size_t)i_k * (kUnitRows * 2));
         i_w += 2 * slab_stride;
         if (++i_k == G) {
             i_k = 0;
@@ -172,11 +173,26 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
             i_seek();
         }
     };
+    // The weights of the first ST - 1 units are requested before the kernel ahead of this one in the
+    // stream is known to be complete (nothing writes them); their activations follow after the wait,
+    // in one more group, and the first unit waits for all of it.
+    const int x_k0 = i_k;
 #pragma unroll
     for (int sidx = 0; sidx < ST - 1; ++sidx) {
-        if (sidx < n_units) issue_unit(sidx);
+        if (sidx < n_units) issue_unit(sidx, false);
         cp_async_commit();
     }
+    pdl_wait();
+    pdl_launch_dependents();
+    if (x_loader) {
+        int xk = x_k0;
+#pragma unroll
+        for (int sidx = 0; sidx < ST - 1; ++sidx) {
+            if (sidx < n_units) cp_async16(x_dst + sidx * kXUnit, x_base + (size_t)xk * (kUnitRows * 2));
+            if (++xk == G) xk = 0;
+        }
+    }
+    cp_async_commit();
 
     // per (tile, 16-row half): Z = offset + zero (rows r / r + 8) and the scale (s, s / 16)
     float zl[kTilesPerWarp][2], zh[kTilesPerWarp][2], sl[kTilesPerWarp][2], sh[kTilesPerWarp][2];
@@ -212,10 +228,15 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
     for (int it = 0; it < n_units; it += 2) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            cp_async_wait<ST - 2>();
+            if (it == 0 && u == 0) {
+                cp_async_wait<0>();  // everything requested so far: the first units and their activations
+            }
+            else {
+                cp_async_wait<ST - 2>();
+            }
             // every thread's copies for this unit have landed, and every warp is done with the unit before
             __syncthreads();
-            if (to_issue > 0) issue_unit(s_fill);
+            if (to_issue > 0) issue_unit(s_fill, true);
             --to_issue;
             cp_async_commit();
 
@@ -470,7 +491,7 @@ cudaError_t gemm_small_prepare(int max_smem)
     return cudaFuncSetAttribute(gemm_s4_f16_small_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
 
-cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaStream_t st)
+cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaStream_t st, bool pdl)
 {
     p.units_per_cta   = pl.units_per_cta;
     p.total_units     = pl.total_units;
@@ -480,11 +501,10 @@ cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaSt
     dim3 grid(pl.ctas, pl.t_chunks);
     dim3 block(kThreads);
     switch (pl.nt) {
-        case 1: gemm_s4_f16_small_kernel<1><<<grid, block, pl.smem_bytes, st>>>(p); break;
-        case 2: gemm_s4_f16_small_kernel<2><<<grid, block, pl.smem_bytes, st>>>(p); break;
-        default: gemm_s4_f16_small_kernel<4><<<grid, block, pl.smem_bytes, st>>>(p); break;
+        case 1: return launch_kernel(gemm_s4_f16_small_kernel<1>, grid, block, pl.smem_bytes, st, pdl, p);
+        case 2: return launch_kernel(gemm_s4_f16_small_kernel<2>, grid, block, pl.smem_bytes, st, pdl, p);
+        default: return launch_kernel(gemm_s4_f16_small_kernel<4>, grid, block, pl.smem_bytes, st, pdl, p);
     }
-    return cudaGetLastError();
 }
 
 }  // namespace tmb

@@ -212,6 +212,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         // copy with 128-byte swizzle writes.  One slice serves both feature tiles of the unit.
         bool dead = false;
         int  g    = u_begin % G;
+        pdl_wait();  // the activations come from the kernel before this one
+        pdl_launch_dependents();
         for (int it = 0; it < n_units; ++it) {
             const int sx = it % kXST;
             if (it >= kXST) warp_wait(&bars->x_empty[sx], ((it / kXST) - 1) & 1, dead, p.status, kStatusGemmPipeWait);
@@ -326,6 +328,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             --to_issue;
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
+
+        // The packed weights requested above are written by no kernel.  What follows reads and writes
+        // scratch, tickets and the output, which the kernel before this one may still be using.
+        pdl_wait();
 
         int      js = u_begin / G, g = u_begin - js * G;
         int      sw = 0, sw_fill = kWST - 1;  // ring slot read now / refilled now (the one read one unit ago)
@@ -566,7 +572,7 @@ cudaError_t gemm_tc_prepare(int max_smem)
     return cudaFuncSetAttribute(gemm_s4_f16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
 
-cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st)
+cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st, bool pdl)
 {
     p.units_per_cta   = pl.units_per_cta;
     p.total_units     = pl.total_units;
@@ -592,8 +598,7 @@ cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st
         return cudaErrorInvalidValue;
     }
     dim3 grid(pl.ctas, pl.t_chunks);
-    gemm_s4_f16_tc_kernel<<<grid, kThreads, pl.smem_bytes, st>>>(p, x_map);
-    return cudaGetLastError();
+    return launch_kernel(gemm_s4_f16_tc_kernel, grid, dim3(kThreads), pl.smem_bytes, st, pdl, p, x_map);
 }
 
 }  // namespace tmb

@@ -22,5 +22,14 @@ struct tm_handle {
     unsigned long long launches        = 0;
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
+    int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
     int                gemv_dev_mode   = 0;  // TM_B200_GEMV_DEV_MODE: timing experiments (results are then wrong)
 };
+
+namespace tmb {
+// Set by the decode driver around its launches (per host thread): the kernel launches made through
+// the C ABI on this thread carry the programmatic-dependent-launch attribute.  Off for direct callers,
+// who may put any kernel in front of ours.
+extern thread_local int g_pdl;
+}  // namespace tmb
+

@@ -160,6 +160,11 @@ int run_step(StepCtx& c)
     cudaStream_t                 s   = c.stream;
     LlamaLinear                  linear(m.h);
     const unsigned long long     l0 = m.h->launches;
+    // kernels of this step overlap their prologues with the tail of the kernel before them
+    struct PdlScope {
+        explicit PdlScope(int on) { g_pdl = on; }
+        ~PdlScope() { g_pdl = 0; }
+    } pdl_scope(m.h->pdl);
 
     prepare_step_kernel<<<(B + 127) / 128, 128, 0, s>>>(
         st.step, st.start_step, st.forced_ids, m.picked, m.ids_in, m.inactive, B, st.max_steps, cfg.vocab_size);

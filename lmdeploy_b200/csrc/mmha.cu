@@ -194,6 +194,11 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         cp_async_commit();
     }
 
+    // The cache rows requested above were written by earlier steps; q, k, v of the new token come
+    // from the kernel before this one.
+    pdl_wait();
+    pdl_launch_dependents();
+
     // ---------------------------------------------------------------- q (+k, v of the new token)
     {
         float base = p.rope_base;
@@ -655,19 +660,16 @@ MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_ch
     return pl;
 }
 
-cudaError_t mmha_launch(const MmhaPlan& pl, MmhaParams p, bool int8, cudaStream_t st)
+cudaError_t mmha_launch(const MmhaPlan& pl, MmhaParams p, bool int8, cudaStream_t st, bool pdl)
 {
     p.chunk      = pl.chunk;
     p.max_splits = pl.max_splits;
     dim3 grid(pl.max_splits, p.Hkv * pl.head_blocks, p.B);
     dim3 block(kWarps * 32);
     if (int8) {
-        mmha_decode_kernel<true><<<grid, block, mmha_smem_bytes<true>(), st>>>(p);
+        return launch_kernel(mmha_decode_kernel<true>, grid, block, mmha_smem_bytes<true>(), st, pdl, p);
     }
-    else {
-        mmha_decode_kernel<false><<<grid, block, mmha_smem_bytes<false>(), st>>>(p);
-    }
-    return cudaGetLastError();
+    return launch_kernel(mmha_decode_kernel<false>, grid, block, mmha_smem_bytes<false>(), st, pdl, p);
 }
 
 }  // namespace tmb

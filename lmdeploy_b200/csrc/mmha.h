@@ -36,11 +36,12 @@ struct MmhaPlan {
 
 cudaError_t mmha_prepare();
 MmhaPlan    mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk);
-cudaError_t mmha_launch(const MmhaPlan& plan, MmhaParams p, bool int8, cudaStream_t st);
+cudaError_t mmha_launch(const MmhaPlan& plan, MmhaParams p, bool int8, cudaStream_t st, bool pdl = false);
 
 // RMSNorm kernels (norm.cu)
-cudaError_t rmsnorm_launch(__half* out, const __half* in, const __half* scale, float eps, int m, int n, cudaStream_t st);
+cudaError_t rmsnorm_launch(__half* out, const __half* in, const __half* scale, float eps, int m, int n, cudaStream_t st, bool pdl = false);
 cudaError_t add_residual_rmsnorm_launch(
-    __half* residual, __half* in_out, const __half* bias, const __half* scale, float eps, int m, int n, cudaStream_t st);
+    __half* residual, __half* in_out, const __half* bias, const __half* scale, float eps, int m, int n, cudaStream_t st,
+    bool pdl = false);
 
 }  // namespace tmb

@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(__half* residual, __half* in_out, const __half* in, const __half* bias, const __half* scale, float eps, int n)
 {
     __shared__ float red[kNormThreads / 32];
+    pdl_wait();  // the rows come from the kernel before this one
+    pdl_launch_dependents();
     const size_t     row  = (size_t)blockIdx.x * n;
     const int        nvec = n / 8;
     uint4            keep[kMaxVec];
@@ -94,17 +96,15 @@ rmsnorm_kernel(__half* residual, __half* in_out, const __half* in, const __half*
 
 }  // namespace
 
-cudaError_t rmsnorm_launch(__half* out, const __half* in, const __half* scale, float eps, int m, int n, cudaStream_t st)
+cudaError_t rmsnorm_launch(__half* out, const __half* in, const __half* scale, float eps, int m, int n, cudaStream_t st, bool pdl)
 {
-    rmsnorm_kernel<false><<<m, kNormThreads, 0, st>>>(nullptr, out, in, nullptr, scale, eps, n);
-    return cudaGetLastError();
+    return launch_kernel(rmsnorm_kernel<false>, dim3(m), dim3(kNormThreads), 0, st, pdl, nullptr, out, in, nullptr, scale, eps, n);
 }
 
 cudaError_t add_residual_rmsnorm_launch(
-    __half* residual, __half* in_out, const __half* bias, const __half* scale, float eps, int m, int n, cudaStream_t st)
+    __half* residual, __half* in_out, const __half* bias, const __half* scale, float eps, int m, int n, cudaStream_t st, bool pdl)
 {
-    rmsnorm_kernel<true><<<m, kNormThreads, 0, st>>>(residual, in_out, nullptr, bias, scale, eps, n);
-    return cudaGetLastError();
+    return launch_kernel(rmsnorm_kernel<true>, dim3(m), dim3(kNormThreads), 0, st, pdl, residual, in_out, nullptr, bias, scale, eps, n);
 }
 
 }  // namespace tmb
