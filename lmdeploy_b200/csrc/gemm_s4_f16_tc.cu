@@ -333,6 +333,86 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         // scratch, tickets and the output, which the kernel before this one may still be using.
         pdl_wait();
 
+        // split-K: [slot][128 tokens][256 feature rows] fp32 partial tiles (a warp touches 128 contiguous
+        // bytes per token), per tile a count of CTAs whose partial is complete and a count of CTAs that
+        // are done reading.  Tiles this CTA shares with others are reduced after its last unit.
+        float* const slots  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
+        int* const   arrive = p.counters + (size_t)blockIdx.y * p.n_col_tiles;
+        int* const   done   = p.counters + (size_t)(gridDim.y + blockIdx.y) * p.n_col_tiles;
+        constexpr int kMaxPending = 4;
+        int           pend[kMaxPending];
+        int           n_pend = 0;
+        // Every CTA of a split tile reduces its own share of the feature rows, once all partials of the
+        // tile are in scratch: nobody reads more than one tile's worth, and the sum runs in CTA order.
+        auto reduce_share = [&](int tjs) {
+            const int c_first = (tjs * G) / upc;
+            const int c_last  = ((tjs + 1) * G - 1) / upc;
+            const int n_split = c_last - c_first + 1;
+            const int col0    = tjs * kSuperN;
+            if (dtid == 0) {
+                // bounded wait for the other CTAs of the tile (all of them are resident: the grid has
+                // at most one CTA per SM)
+                int             seen = 0;
+                const long long t_begin = clock64();
+                for (;;) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrive + tjs) : "memory");
+                    if (seen >= n_split || clock64() - t_begin > kMaxWaitCycles) break;
+                }
+                if (seen < n_split) atomicOr(p.status, kStatusGemmTmemWait);
+                bars->flag = seen >= n_split;
+            }
+            named_bar_sync(1, kDqThreads);
+            if (bars->flag) {
+                const int j      = blockIdx.x - c_first;
+                const int n_cols = min(kSuperN, p.N - col0);  // N % 32 == 0
+                const int f0     = (n_cols * j / n_split) & ~3;
+                const int f1     = j == n_split - 1 ? n_cols : ((n_cols * (j + 1) / n_split) & ~3);
+                const int quads  = (f1 - f0) / 4;
+                const int items  = t_rows * quads;
+                for (int i = dtid; i < items; i += kDqThreads) {
+                    const int    t    = i / quads;
+                    const int    n    = f0 + (i - t * quads) * 4;
+                    const float* src  = slots + (size_t)t * kSuperN + n;
+                    float4       acc  = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int cc = c_first; cc <= c_last; cc += 4) {
+                        float4 part[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            part[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (cc + e <= c_last) {
+                                part[e] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(cc + e + tjs) * (size_t)(128 * kSuperN)));
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {  // absent slots add +0
+                            acc.x += part[e].x, acc.y += part[e].y, acc.z += part[e].z, acc.w += part[e].w;
+                        }
+                    }
+                    const __half2 h0 = __floats2half2_rn(acc.x, acc.y), h1 = __floats2half2_rn(acc.z, acc.w);
+                    if (p.fused_silu) {
+                        // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pairs (gate, up)
+                        const float2 u0 = __half22float2(h0), u1 = __half22float2(h1);
+                        const float  s0 = u0.x / (1.f + __expf(-u0.x)), s1 = u1.x / (1.f + __expf(-u1.x));
+                        *reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * (p.N / 2) + (col0 + n) / 2) =
+                            __floats2half2_rn(s0 * u0.y, s1 * u1.y);
+                    }
+                    else {
+                        __half2* dst = reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n);
+                        dst[0]       = h0;
+                        dst[1]       = h1;
+                    }
+                }
+            }
+            named_bar_sync(1, kDqThreads);  // everyone is done reading; the flag may be reused
+            if (dtid == 0) {
+                // the last reader of the tile resets both counts for the next launch
+                if (atomicAdd(done + tjs, 1) == n_split - 1) {
+                    arrive[tjs] = 0;
+                    done[tjs]   = 0;
+                }
+            }
+        };
+
         int      js = u_begin / G, g = u_begin - js * G;
         int      sw = 0, sw_fill = kWST - 1;  // ring slot read now / refilled now (the one read one unit ago)
         int      sa = 0;
@@ -427,8 +507,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             const int n_row  = m * kTileN + q * 32 + lane;  // feature row of the CTA tile held by this thread
             const int n_glob = col0 + n_row;
             const int ccount = TT / 2;                      // token columns per warp
-            // split-K partials: [slot][128 tokens][256 feature rows] fp32 (a warp touches 128 contiguous bytes per token)
-            float* const slots = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
             const uint32_t my_acc = tmem + m * accS + ((uint32_t)(q * 32) << 16);
             // eight token columns of this thread's feature row -> C
             auto store_c = [&](const float (&v)[8], int col) {
@@ -465,53 +543,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
             }
             ++seg_idx;
-            if (n_split > 1) {
-                __threadfence();
-                named_bar_sync(1, kDqThreads);
-                if (dtid == 0) {
-                    int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + this_js;
-                    const int ticket  = atomicAdd(counter, 1);
-                    const int is_last = ticket == n_split - 1;
-                    if (is_last) *counter = 0;
-                    bars->flag = is_last;
-                }
-                named_bar_sync(1, kDqThreads);
-                if (bars->flag && !dead) {
-                    __threadfence();
-                    // Last CTA of the tile: sum the partials in CTA order.  Its own term comes from the
-                    // accumulator, which is still in TMEM; the others are read with up to four slots in flight.
-                    const int me = blockIdx.x;
-                    for (int cb = 0; cb < ccount; cb += 8) {
-                        const int col = kh * ccount + cb;
-                        float     own[8], acc[8];
-                        tmem_ld8(my_acc + (uint32_t)col, own);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-                        for (int cc = c_first; cc <= c_last; cc += 4) {
-                            float part[4][8];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const bool   live = cc + e <= c_last && cc + e != me;
-                                const float* src  = slots + (size_t)(cc + e + this_js) * (size_t)(128 * kSuperN) + (size_t)col * kSuperN + n_row;
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) part[e][i] = live ? __ldcg(src + (size_t)i * kSuperN) : 0.f;
-                            }
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) acc[i] += (cc + e == me) ? own[i] : part[e][i];  // absent slots add +0
-                            }
-                        }
-                        store_c(acc, col);
-                    }
-                }
-            }
             // the accumulators may be overwritten now
             tc_fence_before();
             __syncwarp();
             if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty);
-            if (n_split > 1) named_bar_sync(1, kDqThreads);  // the flag is reused by the next segment
+            if (n_split > 1) {
+                // publish the partial; its reduction waits until this CTA has no units left
+                __threadfence();
+                named_bar_sync(1, kDqThreads);
+                if (dtid == 0) {
+                    __threadfence();  // release: the partial of every thread, ordered before by the barrier
+                    atomicAdd(arrive + this_js, 1);
+                }
+                if (n_pend == kMaxPending) {
+                    reduce_share(pend[0]);
+                    for (int i = 1; i < kMaxPending; ++i) pend[i - 1] = pend[i];
+                    --n_pend;
+                }
+                pend[n_pend++] = this_js;
+            }
         }
+        for (int i = 0; i < n_pend; ++i) reduce_share(pend[i]);
         asm volatile("cp.async.wait_all;" ::: "memory");
     }
 
@@ -563,7 +615,7 @@ GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
     pl.slots_per_chunk = pl.ctas + pl.n_col_tiles;
     pl.smem_bytes      = gemm_tc_smem_bytes(pl.token_tile);
     pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * 128 * kSuperN;
-    pl.counter_ints     = (size_t)pl.t_chunks * pl.n_col_tiles;
+    pl.counter_ints     = (size_t)2 * pl.t_chunks * pl.n_col_tiles;  // arrivals and finished readers per tile
     return pl;
 }
 
