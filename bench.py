@@ -233,7 +233,9 @@ def run_mmha_workload(args, rank, world, device):
     B, H, Hkv, D, S_max = args.batch, args.heads, args.kv_heads, 128, 4224
     int8 = args.kv == "int8"
     rng = np.random.default_rng(1234 + rank)
-    lengths = rng.integers(128, 4097, size=B).astype(np.int32)
+    lo, hi = (int(v) for v in args.kv_len.split(","))
+    S_max = max(S_max, hi + 128)
+    lengths = rng.integers(lo, hi + 1, size=B).astype(np.int32)
     g = torch.Generator(device=device).manual_seed(7 + rank)
     if int8:
         kc = torch.randint(-127, 128, (B, Hkv, S_max, D), dtype=torch.int8, device=device, generator=g)
@@ -288,7 +290,7 @@ def run_mmha_workload(args, rank, world, device):
         "scaling": "weak", "vs_baseline": None, "dtype": f"f16 q, {args.kv} KV, f32 softmax/accumulate",
         "data": "synthetic",
         "config": {"workload": "mmha", "batch": B, "heads": H, "kv_heads": Hkv, "kv": args.kv,
-                   "kv_len": "uniform 128..4096", "l2": "inputs larger than L2 (one call reads > 1 GB of KV cache)",
+                   "kv_len": f"uniform {lo}..{hi}", "l2": "inputs larger than L2 (one call reads > 1 GB of KV cache)",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "kernel": "mmha_decode_kernel", "achieved": round(gbs, 1),
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
@@ -609,6 +611,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--shapes", choices=["7b", "70b"], default="7b", help="projection shapes of the gemm workload")
+    ap.add_argument("--kv-len", default="128,4096", help="lo,hi of the uniform KV lengths of the mmha workload")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--heads", type=int, default=32)

@@ -489,6 +489,19 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
             }
         }
 
+        if (INT8 && (blk & 7) == 7) {
+            // Take the +1152 offsets out every 128 tokens of this warp: left in, the accumulators grow to
+            // 1152 x (number of tokens) and the fp32 sums lose the bits that carry sum p v.
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                acc[a][0] = fmaf(-kOffset, psum[0], acc[a][0]);
+                acc[a][1] = fmaf(-kOffset, psum[1], acc[a][1]);
+                acc[a][2] = fmaf(-kOffset, psum[0], acc[a][2]);
+                acc[a][3] = fmaf(-kOffset, psum[1], acc[a][3]);
+            }
+            psum[0] = psum[1] = psum[2] = psum[3] = 0.f;
+        }
+
         __syncwarp();
         if (blk + NSTAGE - 1 < my_blocks) {
             issue_block(blk + NSTAGE - 1, (blk + NSTAGE - 1) % NSTAGE);
@@ -643,13 +656,24 @@ MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_ch
     const long long items = (long long)B * Hkv * pl.head_blocks;
     int             chunk = want_chunk;
     if (chunk <= 0) {
-        // A CTA pays a fixed start-up (q load, RoPE, pipeline fill) worth a few hundred tokens, so
-        // splits are kept long: about 16 CTAs per SM over the whole grid (4 resident at a time),
-        // 128..4096 tokens per split.
-        long long c = ((long long)max_len * items) / ((long long)sm_count * 16);
-        chunk       = (int)((c + 63) / 64 * 64);
-        if (chunk < 128) chunk = 128;
-        if (chunk > 4096) chunk = 4096;
+        // Splitting a sequence costs a partial record per split, a ticket and a merge, and every CTA
+        // pays a fixed start-up (q load, RoPE, pipeline fill) worth a few hundred tokens: measured on
+        // B200, one CTA per (sequence, KV head) beats any split as soon as there is about one CTA per
+        // two SMs.  So: no split up to 2048 tokens when there are that many items; 2048-token splits
+        // beyond (they even out the tail of long sequences); with fewer items, just enough splits of at
+        // least 256 tokens to put two CTAs on every SM.
+        if (items * 2 >= sm_count) {
+            chunk = max_len < 2048 ? max_len : 2048;
+        }
+        else {
+            long long splits = (2ll * sm_count + items - 1) / items;
+            long long most   = (max_len + 255) / 256;
+            if (splits > most) splits = most;
+            if (splits < 1) splits = 1;
+            chunk = (int)((max_len + splits - 1) / splits);
+            if (chunk < 256) chunk = 256;
+        }
+        if (chunk < 64) chunk = 64;
     }
     chunk         = (chunk + 63) / 64 * 64;
     pl.chunk      = chunk;
