@@ -54,6 +54,12 @@ TM_API int tm_last_cuda_error(const tm_handle* h);
 TM_API int tm_check_device_status(tm_handle* h, void* stream, unsigned* word);
 /* Number of kernel launches issued through this handle since creation. */
 TM_API unsigned long long tm_launch_count(const tm_handle* h);
+/* Tuning knobs of this handle (no reference counterpart; the same knobs are read from the environment
+ * at tm_create).  `name`: "gemm_tc_min_n" (token count from which the tcgen05 GEMM is used),
+ * "mmha_chunk" (cached tokens per KV split, 0 = automatic), "mmha_warps" (warps per attention CTA: 1, 2,
+ * 4 or 0 = automatic), "pdl" (1 = tm_llama_decode launches with programmatic dependent launch).
+ * Returns TM_ERR_INVALID_ARG for an unknown name or value. */
+TM_API int tm_set_option(tm_handle* h, const char* name, int value);
 
 /* ------------------------------------------------------------------------------------------
  * AWQ W4A16 GEMM.  Replaces GemmS4F16::Run

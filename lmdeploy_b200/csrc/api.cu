@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <string>
 
 using namespace tmb;
 
@@ -75,6 +76,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     h->pdl           = env_int("TM_B200_PDL", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
+    h->mmha_warps  = env_int("TM_B200_MMHA_WARPS", 0);
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;
@@ -104,6 +106,28 @@ extern "C" int tm_destroy(tm_handle* h)
 extern "C" int tm_last_cuda_error(const tm_handle* h)
 {
     return h ? h->last_cuda_error : 0;
+}
+
+extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
+{
+    if (!h || !name) return TM_ERR_INVALID_ARG;
+    const std::string n(name);
+    if (n == "gemm_tc_min_n" && value >= 1) {
+        h->gemm_tc_min_n = value;
+    }
+    else if (n == "mmha_chunk" && value >= 0) {
+        h->mmha_chunk = value;
+    }
+    else if (n == "mmha_warps" && (value == 0 || value == 1 || value == 2 || value == 4)) {
+        h->mmha_warps = value;
+    }
+    else if (n == "pdl" && (value == 0 || value == 1)) {
+        h->pdl = value;
+    }
+    else {
+        return TM_ERR_INVALID_ARG;
+    }
+    return TM_OK;
 }
 
 extern "C" unsigned long long tm_launch_count(const tm_handle* h)
@@ -297,9 +321,9 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     }
 
     const int max_len = a->timestep < a->memory_max_len ? a->timestep : a->memory_max_len;
-    MmhaPlan  pl      = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, h->mmha_chunk);
+    MmhaPlan  pl      = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, h->mmha_chunk, h->mmha_warps);
     while (pl.ws_floats * sizeof(float) > h->attn_scratch_bytes && pl.chunk < (1 << 20)) {
-        pl = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, pl.chunk * 2);
+        pl = mmha_plan(a->batch_size, a->num_heads, a->num_kv_heads, max_len, h->sm_count, pl.chunk * 2, h->mmha_warps);
     }
     if (pl.ws_floats * sizeof(float) > h->attn_scratch_bytes || pl.counter_ints > h->attn_counter_ints) {
         return TM_ERR_WORKSPACE;

@@ -25,7 +25,7 @@ namespace tmb {
 namespace {
 
 constexpr int kD          = 128;  // head dim
-constexpr int kWarps      = 4;
+constexpr int kMaxWarps   = 4;  // warps per CTA: 4, 2 or 1 (template parameter W of the kernel)
 constexpr int kBlockTok   = 16;   // tokens per warp block
 constexpr int kHeadsPerCta = 8;
 constexpr float kLog2e    = 1.4426950408889634f;
@@ -102,9 +102,11 @@ __device__ __forceinline__ int qk_d0(int c, int j)
     return INT8 ? 32 * c + 4 * j : 16 * c + 64 * (j >> 2) + 4 * (j & 3);
 }
 
-template<bool INT8>
-__global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
+template<bool INT8, int W>
+__global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kernel(MmhaParams p)
 {
+    constexpr int kWarps   = W;
+    constexpr int kThreads = W * 32;
     constexpr int ROWB   = INT8 ? kD : 2 * kD;        // bytes per cached token row
     constexpr int CPR    = ROWB / 16;                 // 16-byte chunks per row
     constexpr int NSTAGE = 3;
@@ -216,8 +218,10 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         }
         const int   pad  = p.padding ? p.padding[bi] : 0;
         const float pos  = p.pos_from_length ? (float)tlength : (float)(p.timestep - pad);  // template.cuh:1391-1395
-        const int   pr   = tid & 63;                    // pair index: elements 2pr, 2pr+1
-        const int   part = tid >> 6;                    // 0 / 1: which rows this thread handles
+        constexpr int kPairThreads = kThreads < 64 ? kThreads : 64;
+        constexpr int kParts       = kThreads / kPairThreads;  // 1 or 2 threads share a pair index
+        const int     part         = tid / kPairThreads;       // which rows this thread handles
+        for (int pr = tid % kPairThreads; pr < 64; pr += kPairThreads) {  // pair index: elements 2pr, 2pr+1
         float       cs = 1.f, sn = 0.f;
         const bool  rot = 2 * pr < p.rot_dim;
         if (rot) {
@@ -226,7 +230,7 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         }
         const __half* xrow = p.qkv + (size_t)bi * p.stride;
         // rows 0..7: query heads (zero beyond nheads); row 8: k; row 9: v
-        for (int row = part; row < kHeadsPerCta + 2; row += 2) {
+        for (int row = part; row < kHeadsPerCta + 2; row += kParts) {
             const bool is_q = row < kHeadsPerCta;
             if (!is_q && !last_split) {
                 continue;
@@ -260,6 +264,7 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
             __half* dstp = is_q ? q_s + row * kD : (row == kHeadsPerCta ? knew_s : vnew_s);
             *reinterpret_cast<__half2*>(dstp + 2 * pr) = h;
         }
+        }
     }
     __syncthreads();
 
@@ -291,9 +296,9 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         unsigned char* kd   = const_cast<unsigned char*>(kc) + slot;
         unsigned char* vd   = const_cast<unsigned char*>(vc) + slot;
         if (INT8) {
-            if (tid < 64) {
-                const bool          is_v = tid >= 32;
-                const int           d    = (tid & 31) * 4;
+            for (int t2 = tid; t2 < 64; t2 += kThreads) {
+                const bool          is_v = t2 >= 32;
+                const int           d    = (t2 & 31) * 4;
                 const __half*       src  = is_v ? vnew_s : knew_s;
                 const float         sc   = is_v ? p.v_scale : p.k_scale;
                 const float         zp   = is_v ? p.v_zp : p.k_zp;
@@ -548,56 +553,47 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
     }
     __syncthreads();
 
-    // thread = head-dim index; loop over heads
-    const int d = tid;
-    float     M[kHeadsPerCta], L[kHeadsPerCta], O[kHeadsPerCta];
-#pragma unroll
-    for (int h = 0; h < kHeadsPerCta; ++h) {
-        float mm = last_split ? snew_s[h] : -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * kPartFloats + h]);
-        float ll = 0.f, oo = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float f = exp2f(part[w * kPartFloats + h] - mm);  // exp2(-inf) = 0 for idle warps
-            ll += part[w * kPartFloats + 8 + h] * f;
-            oo += part[w * kPartFloats + 16 + h * kD + d] * f;
-        }
-        if (last_split) {
-            const float f = exp2f(snew_s[h] - mm);
-            ll += f;
-            // the reference multiplies the fp16-rounded probability with the un-quantised v
-            oo += f * __half2float(vnew_s[d]);
-        }
-        M[h] = mm;
-        L[h] = ll;
-        O[h] = oo;
-    }
-
-    if (n_split == 1) {
+    // thread = head-dim index (a CTA of fewer than 128 threads takes several); loop over heads
+    constexpr int kRec = 2 + kD;  // split record: m | l | o[128]
+    for (int d = tid; d < kD; d += kThreads) {
 #pragma unroll
         for (int h = 0; h < kHeadsPerCta; ++h) {
-            if (h < nheads) {
+            if (h >= nheads) continue;
+            float mm = last_split ? snew_s[h] : -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, part[w * kPartFloats + h]);
+            float ll = 0.f, oo = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float f = exp2f(part[w * kPartFloats + h] - mm);  // exp2(-inf) = 0 for idle warps
+                ll += part[w * kPartFloats + 8 + h] * f;
+                oo += part[w * kPartFloats + 16 + h * kD + d] * f;
+            }
+            if (last_split) {
+                const float f = exp2f(snew_s[h] - mm);
+                ll += f;
+                // the reference multiplies the fp16-rounded probability with the un-quantised v
+                oo += f * __half2float(vnew_s[d]);
+            }
+            if (n_split == 1) {
                 // template.cuh:1662: 1 / (sum + 1e-6)
-                p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(O[h] / (L[h] + 1.e-6f));
+                p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(oo / (ll + 1.e-6f));
+            }
+            else {
+                float* rec = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits + split) * kRec;
+                if (d == 0) {
+                    __stcg(rec, mm);
+                    __stcg(rec + 1, ll);
+                }
+                __stcg(rec + 2 + d, oo);
             }
         }
+    }
+    if (n_split == 1) {
         return;
     }
 
     // ---------------------------------------------------------------- merge the splits
-    constexpr int kRec = 2 + kD;  // m | l | o[128]
-#pragma unroll
-    for (int h = 0; h < kHeadsPerCta; ++h) {
-        if (h < nheads) {
-            float* rec = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits + split) * kRec;
-            if (d == 0) {
-                __stcg(rec, M[h]);
-                __stcg(rec + 1, L[h]);
-            }
-            __stcg(rec + 2 + d, O[h]);
-        }
-    }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -614,41 +610,57 @@ __global__ void __launch_bounds__(kWarps * 32) mmha_decode_kernel(MmhaParams p)
         return;
     }
     __threadfence();
-    for (int h = 0; h < nheads; ++h) {
-        const float* rec0 = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits) * kRec;
-        float        mm   = -INFINITY;
-        for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(rec0 + (size_t)s * kRec));
-        float ll = 0.f, oo = 0.f;
-        for (int s = 0; s < n_split; ++s) {
-            const float* rec = rec0 + (size_t)s * kRec;
-            const float  f   = exp2f(__ldcg(rec) - mm);
-            ll += __ldcg(rec + 1) * f;
-            oo += __ldcg(rec + 2 + d) * f;
+    for (int d = tid; d < kD; d += kThreads) {
+        for (int h = 0; h < nheads; ++h) {
+            const float* rec0 = p.ws + (((size_t)bi * p.H + head0 + h) * p.max_splits) * kRec;
+            float        mm   = -INFINITY;
+            for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(rec0 + (size_t)s * kRec));
+            float ll = 0.f, oo = 0.f;
+            for (int s = 0; s < n_split; ++s) {
+                const float* rec = rec0 + (size_t)s * kRec;
+                const float  f   = exp2f(__ldcg(rec) - mm);
+                ll += __ldcg(rec + 1) * f;
+                oo += __ldcg(rec + 2 + d) * f;
+            }
+            p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(oo / (ll + 1.e-6f));
         }
-        p.out[((size_t)bi * p.H + head0 + h) * kD + d] = __float2half_rn(oo / (ll + 1.e-6f));
     }
 }
 
-template<bool INT8>
+template<bool INT8, int W>
 constexpr size_t mmha_smem_bytes()
 {
     constexpr int ROWB   = INT8 ? kD : 2 * kD;
     constexpr int NSTAGE = 3;
-    return (size_t)kWarps * NSTAGE * 2 * kBlockTok * ROWB + (kHeadsPerCta + 2) * kD * 2 + 2 * kHeadsPerCta * 4 + 16;
+    return (size_t)W * NSTAGE * 2 * kBlockTok * ROWB + (kHeadsPerCta + 2) * kD * 2 + 2 * kHeadsPerCta * 4 + 16;
+}
+
+template<bool INT8, int W>
+cudaError_t mmha_prepare_one()
+{
+    return cudaFuncSetAttribute(mmha_decode_kernel<INT8, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmha_smem_bytes<INT8, W>());
+}
+
+template<bool INT8, int W>
+cudaError_t mmha_launch_one(dim3 grid, const MmhaParams& p, cudaStream_t st, bool pdl)
+{
+    return launch_kernel(mmha_decode_kernel<INT8, W>, grid, dim3(W * 32), mmha_smem_bytes<INT8, W>(), st, pdl, p);
 }
 
 }  // namespace
 
 cudaError_t mmha_prepare()
 {
-    cudaError_t e = cudaFuncSetAttribute(
-        mmha_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmha_smem_bytes<true>());
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(
-        mmha_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmha_smem_bytes<false>());
+    cudaError_t e = mmha_prepare_one<true, 4>();
+    if (e == cudaSuccess) e = mmha_prepare_one<true, 2>();
+    if (e == cudaSuccess) e = mmha_prepare_one<true, 1>();
+    if (e == cudaSuccess) e = mmha_prepare_one<false, 4>();
+    if (e == cudaSuccess) e = mmha_prepare_one<false, 2>();
+    if (e == cudaSuccess) e = mmha_prepare_one<false, 1>();
+    return e;
 }
 
-MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk)
+MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk, int want_warps)
 {
     MmhaPlan  pl{};
     const int rep = H / Hkv;
@@ -681,6 +693,11 @@ MmhaPlan mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_ch
     if (pl.max_splits < 1) pl.max_splits = 1;
     pl.ws_floats    = (size_t)B * H * pl.max_splits * (2 + kD);
     pl.counter_ints = (size_t)B * Hkv * pl.head_blocks;
+    // Warps per CTA (16 warps are resident per SM in every variant).
+    const long long ctas = items * pl.max_splits;
+    (void)ctas;  // measured on B200: four warps per CTA win at every batch and length tried; 2 and 1 stay available as options
+    pl.warps = 4;
+    if (want_warps == 1 || want_warps == 2 || want_warps == 4) pl.warps = want_warps;
     return pl;
 }
 
@@ -689,11 +706,18 @@ cudaError_t mmha_launch(const MmhaPlan& pl, MmhaParams p, bool int8, cudaStream_
     p.chunk      = pl.chunk;
     p.max_splits = pl.max_splits;
     dim3 grid(pl.max_splits, p.Hkv * pl.head_blocks, p.B);
-    dim3 block(kWarps * 32);
     if (int8) {
-        return launch_kernel(mmha_decode_kernel<true>, grid, block, mmha_smem_bytes<true>(), st, pdl, p);
+        switch (pl.warps) {
+            case 1: return mmha_launch_one<true, 1>(grid, p, st, pdl);
+            case 2: return mmha_launch_one<true, 2>(grid, p, st, pdl);
+            default: return mmha_launch_one<true, 4>(grid, p, st, pdl);
+        }
     }
-    return launch_kernel(mmha_decode_kernel<false>, grid, block, mmha_smem_bytes<false>(), st, pdl, p);
+    switch (pl.warps) {
+        case 1: return mmha_launch_one<false, 1>(grid, p, st, pdl);
+        case 2: return mmha_launch_one<false, 2>(grid, p, st, pdl);
+        default: return mmha_launch_one<false, 4>(grid, p, st, pdl);
+    }
 }
 
 }  // namespace tmb

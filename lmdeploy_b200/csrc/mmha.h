@@ -30,12 +30,13 @@ struct MmhaPlan {
     int    head_blocks;   // CTAs per KV head along the query-head axis (8 heads each)
     int    chunk;         // cached tokens per split (multiple of 64)
     int    max_splits;
+    int    warps;         // warps per CTA: 4, 2 or 1
     size_t ws_floats;
     size_t counter_ints;
 };
 
 cudaError_t mmha_prepare();
-MmhaPlan    mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk);
+MmhaPlan    mmha_plan(int B, int H, int Hkv, int max_len, int sm_count, int want_chunk, int want_warps = 0);
 cudaError_t mmha_launch(const MmhaPlan& plan, MmhaParams p, bool int8, cudaStream_t st, bool pdl = false);
 
 // RMSNorm kernels (norm.cu)

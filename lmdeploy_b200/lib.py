@@ -87,6 +87,7 @@ SIGNATURES = {
     "tm_last_cuda_error": (_i, [_vp]),
     "tm_check_device_status": (_i, [_vp, _vp, C.POINTER(C.c_uint)]),
     "tm_launch_count": (C.c_ulonglong, [_vp]),
+    "tm_set_option": (_i, [_vp, C.c_char_p, _i]),
     "tm_gemm_s4_f16_workspace_bytes": (_sz, [_i, _i, _i]),
     "tm_gemm_s4_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "tm_gemm_s4_f16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -145,6 +146,10 @@ class Handle:
 
     def launch_count(self) -> int:
         return int(lib.tm_launch_count(self._h))
+
+    def set_option(self, name: str, value: int) -> None:
+        """tuning knob of this handle (see tm_set_option in include/tm_b200.h)"""
+        check(lib.tm_set_option(self._h, name.encode(), int(value)), f"tm_set_option({name})")
 
     def check_device_status(self, stream: int = 0) -> None:
         w = C.c_uint(0)

@@ -152,6 +152,29 @@ def test_benchmark_shape_long_sequences(int8):
     check_cache(kc, kw, int8, case["lengths"], 4224)
 
 
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("warps", [1, 2, 4])
+@pytest.mark.parametrize("chunk", [0, 64, 192])
+def test_every_cta_shape_and_split_size(int8, warps, chunk):
+    """The kernel exists with 1, 2 and 4 warps per CTA and splits a sequence into chunks; which one
+    runs is a tuning decision, so every combination is forced here (MHA, GQA, bias, ragged lengths)."""
+    from lmdeploy_b200 import lib as l
+    h = l.default_handle(torch.cuda.current_device())
+    lengths = [0, 1, 17, 64, 65, 200, 511, 600]
+    case = make_case(len(lengths), 16, 2, 640, lengths, 11, int8, bias=True)
+    try:
+        h.set_option("mmha_warps", warps)
+        h.set_option("mmha_chunk", chunk)
+        out, kc, vc = run_gpu(case)
+    finally:
+        h.set_option("mmha_warps", 0)
+        h.set_option("mmha_chunk", 0)
+    want, kw, vw = run_oracle(case)
+    assert_close(out, want, f"mmha warps={warps} chunk={chunk} int8={int8}")
+    check_cache(kc, kw, int8, case["lengths"], 640)
+    check_cache(vc, vw, int8, case["lengths"], 640)
+
+
 def test_split_merge_is_deterministic_and_tickets_reset():
     case = make_case(3, 8, 8, 2048, [2000, 700, 64], 5, True)
     a, _, _ = run_gpu(case)
