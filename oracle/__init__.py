@@ -13,9 +13,15 @@ Pin status
   ``lmdeploy/lite/quantization/weight/quantizer.py``,
   ``lmdeploy/pytorch/modules/linear.py``) imported by file path; the vectors live in
   ``tests/golden/awq_reference_vectors.npz`` next to the script that wrote them.
-* ``oracle.s4_format`` (layout conversion), ``oracle.gemm`` , ``oracle.attention`` and
-  ``oracle.norm`` restate CUDA code for which the reference holds no CPU
-  implementation, golden vector or known-answer test: **parity unpinned** by the
-  reference's own tests.  They are cross-checked on a GPU against the reference's CUDA
-  sources compiled unmodified into ``oracle/_ref`` (see ``oracle/build_ref.py``).
+* ``oracle.s4_format`` (layout conversion), ``oracle.gemm``, ``oracle.attention`` and the fused
+  residual-add of ``oracle.norm`` restate CUDA code for which the reference holds no CPU
+  implementation, golden vector or test of its own.  They are pinned against the reference's
+  CUDA kernels themselves: ``oracle/build_ref.py`` compiles the reference sources, unmodified and
+  where they lie, into ``oracle/_ref/libtm_ref.so`` (``ref_kernels.cu`` is the flat C entry layer);
+  ``tests/golden/make_ref_kernel_vectors.py`` ran them on a B200 and wrote
+  ``tests/golden/ref_kernel_vectors.npz``, which ``tests/test_oracle_ref_vectors.py`` checks on the
+  CPU (format bit for bit, the rest within the fp16 tolerances), and
+  ``tests/test_gpu_reference_kernels.py`` runs reference kernel, library and oracle side by side
+  on a GPU.  Not pinned: the plain ``rmsnorm`` (its reference file needs the reference's
+  flash-attention sources to link) and ``oracle.decoder`` (the sequencing of the above).
 """

@@ -21,7 +21,8 @@ decoder_masked_multihead_attention_template.cuh:1218-1913) as LLaMA drives it
 
 The reference multiplies q.k in fp16 FMA chains; this oracle uses fp32 dot products
 (the reference's "own fp32-accumulated torch implementation" the tolerance is stated
-against).  parity unpinned by the reference's own tests.
+against).  Pinned against the reference kernel's outputs on a B200
+(tests/golden/ref_kernel_vectors.npz, tests/test_gpu_reference_kernels.py).
 
 Cache layout per sequence (one layer): ``[Hkv, S_max, D]`` for K and for V, element
 fp16 or int8 (LlamaCacheManager.h:32, template.cuh:1425-1426).

@@ -9,7 +9,10 @@ fp32 matmul) plus the two epilogues of the CUDA GEMM:
 * fused SiLU      gemm_s4_f16.cu:31-43 — works on the fp16-rounded pair
   ``(gate, up) = (Y[:, 2j], Y[:, 2j+1])``: ``fp16(silu(gate) * up)`` in fp32.
 
-Argument names follow BASELINE usage: T tokens, N output features, K input features.
+Pinned against GemmS4F16::Run of the reference on a B200 (tests/golden/ref_kernel_vectors.npz,
+tests/test_gpu_reference_kernels.py).
+
+Argument names: T tokens, N output features, K input features.
 """
 from __future__ import annotations
 

@@ -7,7 +7,10 @@ TEST INFRASTRUCTURE.  Follows
   (sum of squares taken from the un-rounded fp32 sum, the residual stored as fp16, the
   normalisation applied to the stored fp16 residual; ops at :41-63)
 
-parity unpinned by the reference's own tests.
+The fused residual-add form is pinned against the reference kernel's outputs on a B200
+(tests/golden/ref_kernel_vectors.npz, tests/test_gpu_reference_kernels.py); the plain form is a
+restatement only (parity unpinned: its reference file does not link without the reference's
+flash-attention sources).
 """
 from __future__ import annotations
 

@@ -17,8 +17,8 @@ A "flat nibble array" is the word array read nibble by nibble, least significant
 nibble of word 0 first (``read_u4`` format.cu:19-22).
 
 Naming follows the reference: ``m`` = output features (N of the linear), ``k`` = input
-features.  parity unpinned by the reference's own tests (it has none for this file);
-cross-checked against the reference CUDA build in ``oracle/_ref`` on a GPU.
+features.  Pinned bit for bit against the reference's CUDA kernels run on a B200
+(tests/golden/ref_kernel_vectors.npz, tests/test_gpu_reference_kernels.py).
 """
 from __future__ import annotations
 
