@@ -70,20 +70,33 @@ __global__ void embedding_lookup_kernel(__half* x, const __half* table, const in
 __global__ void argmax_kernel(const float* logits, int* picked, int* output_ids, const int* step,
                               const unsigned char* inactive, int B, int local_vocab, int tp, int max_steps)
 {
-    __shared__ float s_val[256];
-    __shared__ int   s_idx[256];
+    __shared__ float s_val[1024];
+    __shared__ int   s_idx[1024];
     const int b    = blockIdx.x;
     float     best = -INFINITY;
     int       idx  = 0x7fffffff;
+    auto take = [&](float x, int i) {
+        if (x > best || (x == best && i < idx)) {
+            best = x;
+            idx  = i;
+        }
+    };
     for (int r = 0; r < tp; ++r) {
         const float* row = logits + ((size_t)r * B + b) * local_vocab;
-        for (int v = threadIdx.x; v < local_vocab; v += blockDim.x) {
-            const float x = row[v];
-            const int   i = r * local_vocab + v;
-            if (x > best || (x == best && i < idx)) {
-                best = x;
-                idx  = i;
+        if ((local_vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+            // four logits per load, several loads in flight per thread
+            const float4* row4 = reinterpret_cast<const float4*>(row);
+            for (int v = threadIdx.x; v < local_vocab / 4; v += blockDim.x) {
+                const float4 x = row4[v];
+                const int    i = r * local_vocab + 4 * v;
+                take(x.x, i);
+                take(x.y, i + 1);
+                take(x.z, i + 2);
+                take(x.w, i + 3);
             }
+        }
+        else {
+            for (int v = threadIdx.x; v < local_vocab; v += blockDim.x) take(row[v], r * local_vocab + v);
         }
     }
     s_val[threadIdx.x] = best;
@@ -257,7 +270,7 @@ int run_step(StepCtx& c)
         gather_logits_kernel<<<148 * 4, 256, 0, s>>>(st.logits_out, m.logits, B, m.local_vocab, tp);
         if (!c.ok_cuda()) return c.rc;
     }
-    argmax_kernel<<<B, 256, 0, s>>>(m.logits, m.picked, st.output_ids, st.step, m.inactive, B, m.local_vocab, tp, st.max_steps);
+    argmax_kernel<<<B, 1024, 0, s>>>(m.logits, m.picked, st.output_ids, st.step, m.inactive, B, m.local_vocab, tp, st.max_steps);
     if (!c.ok_cuda()) return c.rc;
     advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(st.step, st.sequence_lengths, m.inactive, B);
     if (!c.ok_cuda()) return c.rc;
