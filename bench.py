@@ -93,6 +93,24 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def load_reference_kernels():
+    """The reference's own CUDA kernels for this path, built unmodified from its sources by
+    oracle/build_ref.py (oracle/_ref/libtm_ref.so).  Only the `--impl reference` arm of the per-kernel
+    workloads uses it; None when it has not been built."""
+    import ctypes as C
+    path = os.path.join(ROOT, "oracle", "_ref", "libtm_ref.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    vp, i, f32 = C.c_void_p, C.c_int, C.c_float
+    lib.ref_gemm_s4_f16.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp]
+    lib.ref_mmha_decode.argtypes = [vp] * 7 + [i] * 5 + [i, f32, i, vp, vp, vp, vp, vp, C.c_size_t, i, f32, f32, f32, f32, i, i, i,
+                                                          vp]
+    lib.ref_set_sync.argtypes = [i]
+    lib.ref_set_sync(0)      # launches only: the timing below synchronises itself
+    return lib
+
+
 def gemm_bytes(n, k, t, fused):
     """algorithmic bytes of one W4A16 GEMM: int4 weight + {zero, scale} + activations in + out."""
     n_out = n // 2 if fused else n
@@ -126,14 +144,24 @@ def run_gemm_workload(args, rank, world, device):
     weights = [[tm.LlamaDenseWeight(c["k"], c["n"], c["A"][r], tm.WeightType.kINT4, None, c["Q"][r], 128)
                 for r in range(c["reps"])] for c in cases]
 
-    def step(i):
-        for c, ws in zip(cases, weights):
-            r = i % c["reps"]
-            op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
+    reflib = load_reference_kernels() if args.impl == "reference" else None
+    if args.impl == "reference" and reflib is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libtm_ref.so not built (python oracle/build_ref.py needs the reference tree)"}
 
     def one(c, ws, i):
         r = i % c["reps"]
-        op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
+        if reflib is not None:
+            import ctypes as C
+            rc = reflib.ref_gemm_s4_f16(C.c_void_p(c["Y"][r].data_ptr()), C.c_void_p(c["A"][r].data_ptr()),
+                                        C.c_void_p(c["X"][r].data_ptr()), C.c_void_p(c["Q"][r].data_ptr()), c["n"], T, c["k"], 128,
+                                        int(c["fused"]), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0, f"reference GEMM returned {rc}"
+        else:
+            op.forward(c["Y"][r], c["X"][r], T, ws[r], op.kFusedSiluFfn if c["fused"] else op.kGemm)
+
+    def step(i):
+        for c, ws in zip(cases, weights):
+            one(c, ws, i)
 
     # The launches are replayed from CUDA graphs so that the device, not the Python caller,
     # sets the pace.  One graph = `ring` consecutive steps (every step takes the next replica).
@@ -204,7 +232,8 @@ def run_gemm_workload(args, rank, world, device):
         "config": {"workload": "gemm", "tokens": T, "model_shapes": args.shapes, "shapes": [c["name"] for c in cases],
                    "l2": "inputs larger than L2: weights replicated beyond 2x L2, next replica each launch",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
-        "roofline": {"bound": "hbm", "kernel": ("gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_small_kernel") + " (gate_up)",
+        "roofline": {"bound": "hbm", "kernel": ("reference gemm_s4_f16_nn" if reflib is not None else
+                                                "gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_small_kernel") + " (gate_up)",
                      "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
                      "algorithmic_bytes": dom["bytes"],
@@ -212,7 +241,19 @@ def run_gemm_workload(args, rank, world, device):
                      "traffic": int(dom["bytes"] * (1.03 if T > 16 else 1.0))},
         "per_kernel": per, "clocks": clocks, "gpu_launches": int(launches),
     }
+    if reflib is not None:
+        mark_reference_kernel_arm(out)
     return out
+
+
+def mark_reference_kernel_arm(out):
+    """fields of a line measured on the reference's own CUDA kernels (per-kernel workloads)"""
+    out["impl"] = "reference"
+    out["roofline"]["traffic"] = None
+    out["cpu_baseline"] = {"value": out["value"], "unit": out["unit"], "cores": 0, "kind": "reference",
+                           "sample": "the reference's CUDA kernels for this workload, built unmodified for sm_100a (oracle/_ref), "
+                                     "same inputs, same timer, on the GPU"}
+    out["e2e"] = {"value": out["value"], "unit": out["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 
 def mmha_bytes(lengths, H, Hkv, e):
@@ -244,7 +285,7 @@ def run_mmha_workload(args, rank, world, device):
         kc = torch.randn(B, Hkv, S_max, D, device=device, generator=g).half()
         vc = torch.randn(B, Hkv, S_max, D, device=device, generator=g).half()
     kp = torch.tensor([kc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
-    vp = torch.tensor([vc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
+    vp_ = torch.tensor([vc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
     qkv = torch.randn(B, (H + 2 * Hkv) * D, device=device, generator=g).half()
     out = torch.empty(B, H * D, dtype=torch.float16, device=device)
     ld = torch.from_numpy(lengths).to(device)
@@ -253,18 +294,34 @@ def run_mmha_workload(args, rank, world, device):
     p = tm.Masked_multihead_attention_params(
         out=out, q=qkv, k=qkv[:, H * D:], v=qkv[:, (H + Hkv) * D:], stride=(H + 2 * Hkv) * D, batch_size=B,
         memory_max_len=S_max, num_heads=H, num_kv_heads=Hkv, timestep=ts, inv_sqrt_dh=1.0 / math.sqrt(D),
-        total_padding_tokens=pad, length_per_sample=ld, k_cache_per_sample=kp, v_cache_per_sample=vp)
+        total_padding_tokens=pad, length_per_sample=ld, k_cache_per_sample=kp, v_cache_per_sample=vp_)
     if int8:
         p.int8_mode = tm.QUANT_POLICY_CACHE_KV_INT8
         p.attention_k_scale = p.attention_v_scale = 4.0 / 127.0
+    reflib = load_reference_kernels() if args.impl == "reference" else None
+    if args.impl == "reference" and reflib is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libtm_ref.so not built (python oracle/build_ref.py needs the reference tree)"}
+
+    def attention():
+        if reflib is None:
+            tm.masked_multihead_attention(p)
+            return
+        import ctypes as C
+        vp = lambda t: C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p()
+        rc = reflib.ref_mmha_decode(vp(out), vp(qkv), vp(qkv[:, H * D:]), vp(qkv[:, (H + Hkv) * D:]), None, None, None,
+                                    (H + 2 * Hkv) * D, B, S_max, H, Hkv, D, 10000.0, ts, vp(pad), None, vp(ld), vp(kp), vp(vp_),
+                                    0, 4 if int8 else 0, float(getattr(p, "attention_k_scale", 0.0) or 0.0), 0.0, float(getattr(p, "attention_v_scale", 0.0) or 0.0), 0.0, 2048, 0, 0,
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, f"reference attention returned {rc}"
+
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
-            tm.masked_multihead_attention(p)
+            attention()
         h.check_device_status(stream.cuda_stream)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            tm.masked_multihead_attention(p)
+            attention()
         graph.replay()
         barrier(world)
         torch.cuda.synchronize()
@@ -284,7 +341,7 @@ def run_mmha_workload(args, rank, world, device):
     nbytes = mmha_bytes(lengths, H, Hkv, 1 if int8 else 2)
     peaks = measured_peaks()
     gbs = nbytes / (ms * 1e-3) * 1e-9
-    return {
+    res = {
         "metric": "decode MMHA HBM GB/s vs peak", "value": round(gbs * world, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": f"f16 q, {args.kv} KV, f32 softmax/accumulate",
@@ -292,13 +349,17 @@ def run_mmha_workload(args, rank, world, device):
         "config": {"workload": "mmha", "batch": B, "heads": H, "kv_heads": Hkv, "kv": args.kv,
                    "kv_len": f"uniform {lo}..{hi}", "l2": "inputs larger than L2 (one call reads > 1 GB of KV cache)",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
-        "roofline": {"bound": "hbm", "kernel": "mmha_decode_kernel", "achieved": round(gbs, 1),
+        "roofline": {"bound": "hbm", "kernel": "reference masked_multihead_attention_kernel" if reflib is not None else "mmha_decode_kernel",
+                     "achieved": round(gbs, 1),
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                      "peak_source": peaks["source"], "algorithmic_bytes": int(nbytes),
                      # ncu on this workload: 1.157 GB read + written for 1.132 GB algorithmic (profiles/)
                      "traffic": int(nbytes * 1.02)},
         "clocks": clocks, "gpu_launches": args.steps,
     }
+    if reflib is not None:
+        mark_reference_kernel_arm(res)
+    return res
 
 
 DECODE_WORKLOADS = {
@@ -623,11 +684,16 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.impl == "reference" and args.workload not in ("gemm", "mmha"):
+        # whole-model workloads: the reference's CPU path (the engine around its kernels is out of scope)
         out = run_reference_arm(args, rank, world)
         if rank == 0:
             print(json.dumps(out), flush=True)
         return
+    if args.impl == "reference" and rank != 0:
+        return   # per-kernel workloads: rank 0 alone times the reference's CUDA kernels
+    if args.impl == "reference":
+        world = 1
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
 

@@ -21,13 +21,20 @@
 #define REF_API extern "C" __attribute__((visibility("default")))
 
 namespace {
-int finish(cudaStream_t st)
+bool g_sync = true;
+int  finish(cudaStream_t st)
 {
-    cudaError_t e = cudaStreamSynchronize(st);
+    cudaError_t e = g_sync ? cudaStreamSynchronize(st) : cudaSuccess;
     if (e == cudaSuccess) e = cudaGetLastError();
     return (int)e;
 }
 }  // namespace
+
+// 1 (default): every entry point waits for its kernels; 0: launches only (timing loops, graph capture)
+REF_API void ref_set_sync(int on)
+{
+    g_sync = on != 0;
+}
 
 // src/turbomind/kernels/gemm_s_f16/format.h:11-30
 REF_API int ref_reformat_s4_k_m8(void* dst, const void* src, int m, int k, void* stream)
