@@ -45,6 +45,8 @@ constexpr int kWarpStage    = 2 * kSlabBytes + 256;          // two slabs + {zer
 
 // stages of the cp.async rings per token-tile count
 __host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 4 : 6; }
+// co-resident CTAs per SM
+__host__ __device__ constexpr int ctas_per_sm_for(int nt) { return nt == 1 ? 2 : 1; }
 
 // dynamic shared memory: [warps][stages][kWarpStage] | [stages][2 slabs][TP x 64 B] | flag
 
@@ -87,7 +89,7 @@ __device__ __forceinline__ void load_x_frag(uint32_t (&bf)[4], uint32_t addr)
 }
 
 template<int NT>
-__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_kernel(GemmSmallParams p)
+__global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_small_kernel(GemmSmallParams p)
 {
     constexpr int TP     = NT * 8;
     constexpr int ST     = stages_for(NT);
@@ -274,23 +276,31 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) gemm_s4_f16_small_k
                         }
                         mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
                     }
+                    // all eight fragments of the slab first (independent chains the scheduler can
+                    // interleave), then the MMAs, k halves outermost so that back-to-back MMAs hit
+                    // different accumulators
+                    uint32_t af[kTilesPerWarp][4][4];
 #pragma unroll
                     for (int w = 0; w < kTilesPerWarp; ++w) {
                         const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes);
                         const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) {
-                            const int k16 = wi >> 1;
-                            const int a   = wi & 1;
-                            uint32_t  af[4];
-                            unpack_s4_biased(wv[wi], af);
+                        for (int wi = 0; wi < 4; ++wi) unpack_s4_biased(wv[wi], af[w][wi]);
+                    }
 #pragma unroll
-                            for (int j = 0; j < NT; ++j) {
-                                if (fresh && k16 == 0) {
-                                    mma_m16n8k16_init(acc[w][a][j], af, bf[j][0], bf[j][1]);
-                                }
-                                else {
-                                    mma_m16n8k16(acc[w][a][j], af, bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                    for (int k16 = 0; k16 < 2; ++k16) {
+#pragma unroll
+                        for (int w = 0; w < kTilesPerWarp; ++w) {
+#pragma unroll
+                            for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                                for (int j = 0; j < NT; ++j) {
+                                    if (fresh && k16 == 0) {
+                                        mma_m16n8k16_init(acc[w][a][j], af[w][2 * k16 + a], bf[j][0], bf[j][1]);
+                                    }
+                                    else {
+                                        mma_m16n8k16(acc[w][a][j], af[w][2 * k16 + a], bf[j][2 * k16], bf[j][2 * k16 + 1]);
+                                    }
                                 }
                             }
                         }
@@ -468,7 +478,7 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem)
     pl.n_col_tiles = (N / kColsPerTile + kTilesPerUnit - 1) / kTilesPerUnit;
     const int G    = K / kUnitRows;
     pl.total_units = pl.n_col_tiles * G;
-    const int slots = sm_count * (pl.nt == 1 ? 2 : 1);  // co-resident CTAs
+    const int slots = sm_count * ctas_per_sm_for(pl.nt);  // co-resident CTAs
     int       ctas  = slots < pl.total_units ? slots : pl.total_units;
     pl.units_per_cta    = (pl.total_units + ctas - 1) / ctas;
     pl.units_per_cta += pl.units_per_cta & 1;  // whole 128-row groups: two units
