@@ -280,16 +280,16 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     return TM_OK;
 }
 
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length);
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order);
 
 extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* stream)
 {
-    return tm_mmha_decode_impl(h, a, stream, 0);
+    return tm_mmha_decode_impl(h, a, stream, 0, nullptr);
 }
 
 // pos_from_length: the RoPE position of sequence b is length_per_sample[b] (what the engine's
 // timestep - padding evaluates to), so that nothing in the launch depends on the step number.
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length)
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order)
 {
     if (!h || !a) return TM_ERR_INVALID_ARG;
     if (!a->out || !a->q || !a->k || !a->v || !a->length_per_sample || !a->k_cache_per_sample || !a->v_cache_per_sample) {
@@ -339,6 +339,7 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     p.lengths         = a->length_per_sample;
     p.finished        = a->finished;
     p.padding         = a->total_padding_tokens;
+    p.order           = order;
     p.B               = a->batch_size;
     p.H               = a->num_heads;
     p.Hkv             = a->num_kv_heads;

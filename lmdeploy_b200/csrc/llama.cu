@@ -9,7 +9,7 @@
 #include <cstring>
 #include <new>
 
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length);
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order);
 
 namespace tmb {
 
@@ -43,10 +43,21 @@ namespace {
 
 // input token and activity of every sequence for this step
 __global__ void prepare_step_kernel(const int* step, const int* start_step, const int* forced_ids, const int* picked,
-                                    int* ids_in, unsigned char* inactive, int B, int max_steps, int vocab)
+                                    int* ids_in, unsigned char* inactive, int B, int max_steps, int vocab, const int* lengths,
+                                    int* order)
 {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
+    {
+        // attention launch order: longest cached sequence first (rank by length, ties by index)
+        const int mine = lengths[b];
+        int       rank = 0;
+        for (int j = 0; j < B; ++j) {
+            const int l = lengths[j];
+            rank += (l > mine || (l == mine && j < b)) ? 1 : 0;
+        }
+        order[rank] = b;
+    }
     const int s   = *step;
     const bool off = s >= max_steps || (start_step != nullptr && s < start_step[b]);
     inactive[b]   = off ? 1 : 0;
@@ -180,7 +191,8 @@ int run_step(StepCtx& c)
     } pdl_scope(m.h->pdl);
 
     prepare_step_kernel<<<(B + 127) / 128, 128, 0, s>>>(
-        st.step, st.start_step, st.forced_ids, m.picked, m.ids_in, m.inactive, B, st.max_steps, cfg.vocab_size);
+        st.step, st.start_step, st.forced_ids, m.picked, m.ids_in, m.inactive, B, st.max_steps, cfg.vocab_size,
+        st.sequence_lengths, m.order);
     if (!c.ok_cuda()) return c.rc;
     embedding_lookup_kernel<<<B, 128, 0, s>>>(m.x, (const __half*)m.tok_embeddings, m.ids_in, m.hidden);
     if (!c.ok_cuda()) return c.rc;
@@ -224,7 +236,7 @@ int run_step(StepCtx& c)
         a.attention_k_zp             = w.past_kv_scale[1];
         a.attention_v_scale          = w.past_kv_scale[2];
         a.attention_v_zp             = w.past_kv_scale[3];
-        if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1))) return c.rc;
+        if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order))) return c.rc;
         if (!c.ok(linear.forward(m.hbuf, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
         if (m.comm && m.comm->world > 1) {
             if (!c.ok(tm_allreduce_sum_f16(m.comm, m.hbuf, (size_t)B * m.hidden, s))) return c.rc;  // :292-297
@@ -332,6 +344,7 @@ extern "C" int tm_llama_create(tm_llama** out, tm_handle* h, tm_comm* comm, cons
     alloc((void**)&m->ids_in, B * 4);
     alloc((void**)&m->picked, B * 4);
     alloc((void**)&m->inactive, B);
+    alloc((void**)&m->order, (size_t)B * sizeof(int));
     alloc(&m->cublas_ws, 32u << 20);
     if (e == cudaSuccess) e = cudaMemset(m->picked, 0, B * 4);
     bool ok = e == cudaSuccess;
@@ -353,7 +366,7 @@ extern "C" int tm_llama_destroy(tm_llama* m)
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
     if (m->cublas) cublasDestroy(m->cublas);
     for (void* p : {(void*)m->x, (void*)m->hbuf, (void*)m->qkv, (void*)m->ctx, (void*)m->ffn, (void*)m->logits_local,
-                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, m->cublas_ws}) {
+                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, m->cublas_ws}) {
         if (p) cudaFree(p);
     }
     delete m;

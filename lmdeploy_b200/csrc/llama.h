@@ -62,6 +62,7 @@ struct tm_llama {
     __half *x = nullptr, *hbuf = nullptr, *qkv = nullptr, *ctx = nullptr, *ffn = nullptr;
     float * logits_local = nullptr, *logits = nullptr;
     int *   ids_in = nullptr, *picked = nullptr;
+    int*    order = nullptr;  // sequences by cached length, longest first (attention launch order)
     unsigned char* inactive = nullptr;
 
     cublasHandle_t cublas    = nullptr;

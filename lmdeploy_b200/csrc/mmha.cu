@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int g    = lane >> 2;
     const int c    = lane & 3;
 
-    const int bi = blockIdx.z;
+    const int bi = p.order != nullptr ? p.order[blockIdx.z] : blockIdx.z;
     if (p.finished != nullptr && p.finished[bi]) {
         return;  // template.cuh:1298-1300: neither out nor the cache is touched
     }

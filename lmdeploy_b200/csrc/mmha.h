@@ -17,6 +17,7 @@ struct MmhaParams {
     const int*           lengths;   // [B] tokens already cached
     const unsigned char* finished;  // [B] or null
     const int*           padding;   // [B] or null (total_padding_tokens)
+    const int*           order;     // [B] or null: sequence handled by grid row z (longest first evens out the tail)
     int                  B, H, Hkv, stride, S_max, timestep, rot_dim, max_pos, use_dynamic_ntk, use_logn;
     int                  pos_from_length;  // RoPE position = cached length (the decode driver; lets a CUDA graph be replayed)
     float                rope_base, inv_sqrt_dh, k_scale, k_zp, v_scale, v_zp;
