@@ -83,12 +83,14 @@ def test_llama7b_projections(name, n, k, t):
     assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"{name} t={t}")
 
 
-@pytest.mark.parametrize("n,k", [(1280, 8192), (8192, 1024), (8192, 3584)])
-def test_llama70b_tp8_shapes(n, k):
+@pytest.mark.parametrize("t", [5, 128])
+@pytest.mark.parametrize("n,k", [(1280, 8192), (8192, 1024), (8192, 3584), (2560, 8192), (8192, 2048)])
+def test_llama70b_tp8_and_tp4_shapes(n, k, t):
+    """per-rank projection shapes of Llama-2-70B at tp=8 (qkv, o, w2) and tp=4 (qkv, o), both GEMM kernels"""
     lin = _linear(n, k, 1)
-    x = _x(5, k, 5)
+    x = _x(t, k, 5)
     y = _run(lin, x, n, k)
-    assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"70b/tp8 n={n} k={k}")
+    assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"70b/tp n={n} k={k} t={t}")
 
 
 @pytest.mark.parametrize("t", [129, 200, 512])
