@@ -35,7 +35,8 @@ typedef enum tm_status {
     TM_ERR_CUDA           = -4, /* a CUDA runtime call failed (see tm_last_cuda_error)        */
     TM_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (status word non-zero)  */
     TM_ERR_NCCL           = -6,
-    TM_ERR_NOT_BUILT      = -7  /* feature compiled out (e.g. NCCL missing)                   */
+    TM_ERR_NOT_BUILT      = -7, /* feature compiled out (e.g. NCCL missing)                   */
+    TM_ERR_IO             = -8  /* a weight file is missing or has the wrong size            */
 } tm_status;
 
 typedef struct tm_handle tm_handle;
@@ -245,6 +246,15 @@ TM_API int tm_llama_set_layer(tm_llama* m, int layer, const tm_llama_layer_weigh
 /* tok_embeddings half [vocab, hidden]; output_norm half [hidden]; output_weight half
  * [vocab / tp (this rank's rows), hidden]. */
 TM_API int tm_llama_set_globals(tm_llama* m, const void* tok_embeddings, const void* output_norm, const void* output_weight);
+/* Loads every weight of this rank from a TurboMind workspace directory: the binary files that
+ * LlamaWeight::loadModel (src/turbomind/models/llama/LlamaWeight.cc:86-106) and
+ * LlamaDecoderLayerWeight::loadModel (LlamaDecoderLayerWeight.cc:261-307; int4 branch of loadWeights,
+ * :206-220) read, i.e. what lmdeploy's deploy.py exports for W4A16: tok_embeddings.weight, norm.weight,
+ * output.weight, layers.<l>.{attention_norm,ffn_norm}.weight, layers.<l>.{attention.w_qkv,attention.wo,
+ * feed_forward.w13,feed_forward.w2}.<rank>.{qweight,scales_zeros}, optional ...w_qkv.<rank>.bias and
+ * layers.<l>.past_kv_scale.<rank>.weight.  The model owns the device copies.  TM_ERR_IO when a file is
+ * missing or its size does not match the configuration. */
+TM_API int tm_llama_load_workspace(tm_llama* m, const char* dir);
 
 /* Decode state, all device memory owned by the caller:
  *   k_cache_ptrs/v_cache_ptrs  [batch] base pointers; sequence b's cache is

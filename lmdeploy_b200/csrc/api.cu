@@ -34,6 +34,7 @@ extern "C" const char* tm_status_string(int status)
         case TM_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
         case TM_ERR_NCCL: return "NCCL error";
         case TM_ERR_NOT_BUILT: return "feature not built";
+        case TM_ERR_IO: return "weight file missing or of the wrong size";
         default: return "unknown status";
     }
 }

@@ -369,6 +369,7 @@ extern "C" int tm_llama_destroy(tm_llama* m)
                     (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, m->cublas_ws}) {
         if (p) cudaFree(p);
     }
+    for (void* p : m->owned) cudaFree(p);
     delete m;
     return TM_OK;
 }

@@ -57,6 +57,7 @@ struct tm_llama {
     const void* tok_embeddings = nullptr;
     const void* output_norm    = nullptr;
     const void* output_weight  = nullptr;
+    std::vector<void*> owned;  // device copies made by tm_llama_load_workspace
 
     // activations, sized for max_batch_size
     __half *x = nullptr, *hbuf = nullptr, *qkv = nullptr, *ctx = nullptr, *ffn = nullptr;

@@ -19,6 +19,7 @@ TM_ERR_CUDA = -4
 TM_ERR_DEVICE_TIMEOUT = -5
 TM_ERR_NCCL = -6
 TM_ERR_NOT_BUILT = -7
+TM_ERR_IO = -8
 
 
 class TmError(RuntimeError):
@@ -106,6 +107,7 @@ SIGNATURES = {
     "tm_llama_destroy": (_i, [_vp]),
     "tm_llama_set_layer": (_i, [_vp, _i, C.POINTER(TmLlamaLayerWeights)]),
     "tm_llama_set_globals": (_i, [_vp, _vp, _vp, _vp]),
+    "tm_llama_load_workspace": (_i, [_vp, C.c_char_p]),
     "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
     "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),

@@ -88,6 +88,8 @@ class LlamaModel:
         _l.check(_l.lib.tm_llama_create(C.byref(self._m), self.handle.ptr, comm.ptr if comm else None, C.byref(c)),
                  "tm_llama_create")
         self._keep: List[object] = []   # tensors the C side points to
+        self._layers = {}               # layer -> (tensors..., kv_scale), for save_workspace
+        self._globals = None
 
     # -- weights -----------------------------------------------------------------------------
     def set_layer(self, l, attn_norm, ffn_norm, qkv: tm.LlamaDenseWeight, o: tm.LlamaDenseWeight,
@@ -101,10 +103,12 @@ class LlamaModel:
         w.w2_qweight, w.w2_scales_zeros = w2.kernel.data_ptr(), w2.scales_and_zeros.data_ptr()
         w.past_kv_scale = (C.c_float * 4)(*kv_scale)
         self._keep += [attn_norm, ffn_norm, qkv, o, w13, w2]
+        self._layers[l] = (attn_norm, ffn_norm, qkv, o, w13, w2, tuple(kv_scale))
         _l.check(_l.lib.tm_llama_set_layer(self._m, l, C.byref(w)), "tm_llama_set_layer")
 
     def set_globals(self, tok_embeddings, output_norm, output_weight):
         self._keep += [tok_embeddings, output_norm, output_weight]
+        self._globals = (tok_embeddings, output_norm, output_weight)
         _l.check(_l.lib.tm_llama_set_globals(self._m, tok_embeddings.data_ptr(), output_norm.data_ptr(),
                                              output_weight.data_ptr()), "tm_llama_set_globals")
 
@@ -127,6 +131,39 @@ class LlamaModel:
         head = (torch.randn(cfg.vocab_size, hid, device=dev, generator=g) * 0.02).half()
         lo = cfg.vocab_size // tp * self.rank
         self.set_globals(emb, ones, head[lo: lo + cfg.vocab_size // tp].contiguous())
+
+    # -- TurboMind workspace files -----------------------------------------------------------
+    def save_workspace(self, path: str):
+        """Write this rank's weights in the file layout of a TurboMind workspace (what
+        lmdeploy/serve/turbomind/deploy.py exports for W4A16 and LlamaWeight::loadModel reads):
+        raw little-endian tensors, one file each.  ``output.weight`` holds the whole vocabulary, so
+        this helper is for tp == 1."""
+        import os
+        import numpy as np
+        assert self.tp == 1, "save_workspace writes the un-sliced lm-head: tp == 1 only"
+        os.makedirs(path, exist_ok=True)
+
+        def dump(name, t):
+            t.detach().contiguous().cpu().numpy().tofile(os.path.join(path, name))
+
+        emb, norm, head = self._globals
+        dump("tok_embeddings.weight", emb)
+        dump("norm.weight", norm)
+        dump("output.weight", head)
+        for l, (an, fn, qkv, o, w13, w2, kv) in self._layers.items():
+            dump(f"layers.{l}.attention_norm.weight", an)
+            dump(f"layers.{l}.ffn_norm.weight", fn)
+            for name, w in (("attention.w_qkv", qkv), ("attention.wo", o), ("feed_forward.w13", w13), ("feed_forward.w2", w2)):
+                dump(f"layers.{l}.{name}.{self.rank}.qweight", w.kernel)
+                dump(f"layers.{l}.{name}.{self.rank}.scales_zeros", w.scales_and_zeros)
+            if qkv.bias is not None:
+                dump(f"layers.{l}.attention.w_qkv.{self.rank}.bias", qkv.bias)
+            np.asarray(kv, np.float32).tofile(os.path.join(path, f"layers.{l}.past_kv_scale.{self.rank}.weight"))
+
+    def load_workspace(self, path: str):
+        """Load every weight of this rank from a TurboMind workspace directory (tm_llama_load_workspace:
+        the library reads the files and owns the device copies)."""
+        _l.check(_l.lib.tm_llama_load_workspace(self._m, path.encode()), f"tm_llama_load_workspace({path})")
 
     # -- decode state ------------------------------------------------------------------------
     def new_state(self, batch: int, max_steps: int, start_step=None, forced_ids=None, keep_hidden=False,

@@ -116,3 +116,61 @@ def test_decode_steps_match_oracle(int8, use_graph):
         assert agree >= total - 1, f"greedy picks agree on {agree}/{total}"
         assert model.last_launches() > 0
     model.close()
+
+
+def _free_run(model, prompts, n_gen):
+    B = len(prompts)
+    pmax = max(len(p) for p in prompts)
+    steps = pmax + n_gen
+    start = np.array([pmax - len(p) for p in prompts], np.int32)
+    forced = np.full((steps, B), -1, np.int32)
+    for b, p in enumerate(prompts):
+        forced[start[b]:pmax, b] = p
+    stream = torch.cuda.Stream()          # a captured step needs a stream of its own
+    with torch.cuda.stream(stream):
+        st = model.new_state(B, steps, start, forced, keep_hidden=True, keep_logits=True)
+        model.decode(st, steps, use_graph=True)
+        model.handle.check_device_status(stream.cuda_stream)
+        return st.output_ids.cpu().numpy(), st.logits.cpu().numpy(), st.k_cache.cpu().numpy()
+
+
+@pytest.mark.parametrize("int8", [True, False])
+def test_workspace_files_round_trip(int8, tmp_path):
+    """A model written in the TurboMind workspace file layout and loaded back by the library
+    (tm_llama_load_workspace) decodes bit for bit like the model it was written from; a missing or
+    truncated file is reported as an I/O error."""
+    import os
+    from lmdeploy_b200 import lib as l, llama
+    model, _, _ = build(int8)
+    prompts = [[5, 17, 900], [1, 2, 3, 4, 999], [7, 8]]
+    want = _free_run(model, prompts, 4)
+    ws = str(tmp_path / "workspace")
+    model.save_workspace(ws)
+    names = set(os.listdir(ws))
+    assert {"tok_embeddings.weight", "norm.weight", "output.weight", "layers.0.attention_norm.weight",
+            "layers.1.feed_forward.w13.0.qweight", "layers.1.feed_forward.w2.0.scales_zeros",
+            "layers.0.past_kv_scale.0.weight"} <= names
+    hid = CFG["head_num"] * 128
+    assert os.path.getsize(os.path.join(ws, "layers.0.attention.w_qkv.0.qweight")) == hid * (CFG["head_num"] + 2 * CFG["kv_head_num"]) * 128 // 2
+
+    loaded = llama.LlamaModel(model.cfg, max_batch_size=4, session_len=CFG["session_len"], device=0)
+    loaded.load_workspace(ws)
+    got = _free_run(loaded, prompts, 4)
+    for a, b in zip(want, got):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), "loaded model decodes differently"
+    loaded.close()
+
+    # a truncated file and a missing file
+    p = os.path.join(ws, "layers.1.feed_forward.w2.0.qweight")
+    data = open(p, "rb").read()
+    open(p, "wb").write(data[:-4])
+    broken = llama.LlamaModel(model.cfg, max_batch_size=4, session_len=CFG["session_len"], device=0)
+    with pytest.raises(l.TmError) as e:
+        broken.load_workspace(ws)
+    assert e.value.status == l.TM_ERR_IO
+    os.remove(p)
+    with pytest.raises(l.TmError) as e:
+        broken.load_workspace(ws)
+    assert e.value.status == l.TM_ERR_IO
+    broken.close()
+    model.close()
