@@ -180,6 +180,43 @@ TM_API int tm_add_residual_rmsnorm(void* residual, void* in_out, const void* bia
                             int n, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Prefill-side writers around the KV cache (half data, size_per_head == 128).  Replace, with the
+ * same argument order and meaning,
+ *   invokeAddFusedQKVBiasTranspose  (src/turbomind/kernels/unfused_attention_kernels.h:66-86, definition
+ *                                    unfused_attention_kernels.cu:999-1027; caller
+ *                                    src/turbomind/models/llama/LlamaContextAttentionLayer.cc:163-182)
+ *   invokeExtendKVCache             (src/turbomind/models/llama/llama_kernels.h:36-51, llama_kernels.cu:400-464;
+ *                                    caller LlamaContextAttentionLayer.cc:195-209)
+ *   invokeTransposeKVCache          (llama_kernels.h:53-68, llama_kernels.cu:586-660; caller
+ *                                    LlamaContextAttentionLayer.cc:332-346)
+ *
+ * tm_add_fused_qkv_bias_transpose: QKV [token_num, (head_num + 2 kv_head_num) * 128] (+ bias), interleaved-pair
+ *   RoPE of q and k at position history_length[b] + s, optional log-n scaling of q, written to
+ *   q_buf [B, head_num, seq_len, 128], k_buf / v_buf [B, kv_head_num, seq_len, 128].  padding_offset
+ *   (may be NULL) maps a packed token to its padded index b * seq_len + s.  QKV itself is not modified.
+ * tm_extend_kv_cache: k_src / v_src [B, heads, max_q_len, 128] rows [0, query_length[b]) -> cache rows
+ *   history_length[b] + s of k_dst[b] / v_dst[b] (device arrays of device pointers) at element offset
+ *   dst_offset, cache layout [heads, max_seq_len, 128]; quant & 4: int8 cache,
+ *   q = sat_s8(rint((x - zp) / scale)), kv_scale = HOST pointer to {k_scale, k_zp, v_scale, v_zp}.
+ * tm_transpose_kv_cache: cache rows [0, key_length[b]) -> [B, head_num, max_kv_len, 128], query head h
+ *   reading cached head h / head_n_rep; int8 rows dequantised as half(q * scale + zp).
+ * K and V are moved by one launch each call; all launches are asynchronous on `stream`.
+ */
+TM_API int tm_add_fused_qkv_bias_transpose(void* q_buf, void* k_buf, void* v_buf, const void* QKV, const void* qkv_bias,
+                                           const int* padding_offset, const int* history_length, const int* input_length,
+                                           int batch_size, int seq_len, int token_num, int head_num, int kv_head_num,
+                                           int size_per_head, int rotary_embedding_dim, float rotary_embedding_base,
+                                           int max_position_embeddings, int use_dynamic_ntk, int use_logn_attn, void* stream);
+TM_API int tm_extend_kv_cache(void** k_dst, void** v_dst, size_t dst_offset, const void* k_src, const void* v_src,
+                              int local_batch_size, const int* query_length, int max_q_len, const int* history_length,
+                              int max_seq_len, int size_per_head, int local_head_num, void* stream, int quant,
+                              const float* kv_scale);
+TM_API int tm_transpose_kv_cache(void* key_cache_trans, void* val_cache_trans, const void** key_cache, const void** val_cache,
+                                 size_t src_offset, int batch_size, const int* key_length, int max_kv_len, int max_seq_len,
+                                 int size_per_head, int head_num, int head_n_rep, void* stream, int quant,
+                                 const float* kv_scale);
+
+/* ------------------------------------------------------------------------------------------
  * Tensor-parallel communicator (one process per GPU; NCCL over NVLink).  Replaces
  *   ftNcclAllReduceSum<half> / ftNcclAllGather (src/turbomind/utils/nccl_utils.h:94-99) and the
  *   NcclParam set-up of src/turbomind/triton_backend/transformer_triton_backend.cpp:24-82.

@@ -112,6 +112,10 @@ SIGNATURES = {
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
     "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
+    "tm_add_fused_qkv_bias_transpose": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
+                                             C.c_float, _i, _i, _i, _vp]),
+    "tm_extend_kv_cache": (_i, [_vp, _vp, _sz, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _i, C.POINTER(C.c_float)]),
+    "tm_transpose_kv_cache": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, C.POINTER(C.c_float)]),
 }
 
 

@@ -210,3 +210,49 @@ def invokeFusedAddBiasResidualRMSNorm(residual, in_out, bias, scale, eps, batch_
     st = _stream() if stream is None else C.c_void_p(stream)
     _l.check(_l.lib.tm_add_residual_rmsnorm(_ptr(residual), _ptr(in_out), _ptr(bias), _ptr(scale), eps, batch_size,
                                             n_dims, st), "invokeFusedAddBiasResidualRMSNorm")
+
+
+# ----------------------------------------------------------------------------------------------
+# prefill-side writers around the KV cache (src/turbomind/kernels/unfused_attention_kernels.h:66-86,
+# src/turbomind/models/llama/llama_kernels.h:36-68): same names and argument order as the reference
+
+def _kv_scale(kv_scale):
+    if kv_scale is None:
+        return None
+    vals = [float(v) for v in kv_scale]
+    if len(vals) != 4:
+        raise ValueError("kv_scale holds k_scale, k_zp, v_scale, v_zp")
+    return (C.c_float * 4)(*vals)
+
+
+def invokeAddFusedQKVBiasTranspose(q_buf, k_buf, v_buf, QKV, qkv_bias, padding_offset, history_length, input_length,
+                                   batch_size, seq_len, token_num, head_num, kv_head_num, size_per_head,
+                                   rotary_embedding_dim, rotary_embedding_base, max_position_embeddings, use_dynamic_ntk,
+                                   use_logn_attn, stream=None):
+    _need_cuda(q_buf, k_buf, v_buf, QKV, qkv_bias, padding_offset, history_length, input_length)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_add_fused_qkv_bias_transpose(
+        _ptr(q_buf), _ptr(k_buf), _ptr(v_buf), _ptr(QKV), _ptr(qkv_bias), _ptr(padding_offset), _ptr(history_length),
+        _ptr(input_length), batch_size, seq_len, token_num, head_num, kv_head_num, size_per_head, rotary_embedding_dim,
+        rotary_embedding_base, max_position_embeddings, int(use_dynamic_ntk), int(use_logn_attn), st),
+        "invokeAddFusedQKVBiasTranspose")
+
+
+def invokeExtendKVCache(k_dst, v_dst, dst_offset, k_src, v_src, local_batch_size, query_length, max_q_len, history_length,
+                        max_seq_len, size_per_head, local_head_num, stream=None, quant=0, kv_scale=None):
+    """k_dst / v_dst: int64 device tensors holding one cache base pointer per sequence."""
+    _need_cuda(k_dst, v_dst, k_src, v_src, query_length, history_length)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_extend_kv_cache(_ptr(k_dst), _ptr(v_dst), dst_offset, _ptr(k_src), _ptr(v_src), local_batch_size,
+                                       _ptr(query_length), max_q_len, _ptr(history_length), max_seq_len, size_per_head,
+                                       local_head_num, st, quant, _kv_scale(kv_scale)), "invokeExtendKVCache")
+
+
+def invokeTransposeKVCache(key_cache_trans, val_cache_trans, key_cache, val_cache, src_offset, batch_size, key_length,
+                           max_kv_len, max_seq_len, size_per_head, head_num, head_n_rep, stream=None, quant=0,
+                           kv_scale=None):
+    _need_cuda(key_cache_trans, val_cache_trans, key_cache, val_cache, key_length)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_transpose_kv_cache(_ptr(key_cache_trans), _ptr(val_cache_trans), _ptr(key_cache), _ptr(val_cache),
+                                          src_offset, batch_size, _ptr(key_length), max_kv_len, max_seq_len, size_per_head,
+                                          head_num, head_n_rep, st, quant, _kv_scale(kv_scale)), "invokeTransposeKVCache")

@@ -24,6 +24,10 @@ REFERENCE_SOURCES = [
     "src/turbomind/kernels/decoder_masked_multihead_attention.cu",
     "src/turbomind/kernels/decoder_masked_multihead_attention/decoder_masked_multihead_attention_128.cu",
     "src/turbomind/models/llama/llama_decoder_kernels.cu",
+    "src/turbomind/models/llama/llama_kernels.cu",
+    "src/turbomind/kernels/unfused_attention_kernels.cu",
+    "src/turbomind/utils/logger.cc",
+    "src/turbomind/utils/Tensor.cc",
 ]
 
 

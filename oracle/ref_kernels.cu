@@ -8,17 +8,54 @@
 //   src/turbomind/kernels/decoder_masked_multihead_attention.cu     dispatcher
 //   src/turbomind/kernels/decoder_masked_multihead_attention/decoder_masked_multihead_attention_128.cu
 //   src/turbomind/models/llama/llama_decoder_kernels.cu             invokeFusedAddBiasResidualRMSNorm
-// They build for sm_100a as they are (mma.sync / ldmatrix / cp.async).
+//   src/turbomind/models/llama/llama_kernels.cu                     invokeRootMeanSquareNorm, invokeExtendKVCache,
+//                                                                   invokeTransposeKVCache
+//   src/turbomind/kernels/unfused_attention_kernels.cu              invokeAddFusedQKVBiasTranspose
+//   src/turbomind/utils/logger.cc, src/turbomind/utils/Tensor.cc    (needed by the file above)
+// They build for sm_100a as they are (mma.sync / ldmatrix / cp.async).  llama_kernels.cu also holds the
+// FlashAttentionOp front end, whose implementation needs CUTLASS and is not built: the empty
+// FlashAttentionOpImpl below only satisfies the linker and aborts if it is ever called.
 #include "src/turbomind/kernels/decoder_masked_multihead_attention.h"
 #include "src/turbomind/kernels/gemm_s_f16/format.h"
 #include "src/turbomind/kernels/gemm_s_f16/gemm_s4_f16.h"
+#include "src/turbomind/kernels/unfused_attention_kernels.h"
 #include "src/turbomind/models/llama/llama_decoder_kernels.h"
+#include "src/turbomind/models/llama/llama_kernels.h"
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <exception>
 
 #define REF_API extern "C" __attribute__((visibility("default")))
+
+namespace turbomind {
+template<typename T, int V>
+class FlashAttentionOpImpl<T, V>::impl {};
+template<typename T, int V>
+FlashAttentionOpImpl<T, V>::FlashAttentionOpImpl(int, int, int, int, int)
+{
+}
+template<typename T, int V>
+FlashAttentionOpImpl<T, V>::~FlashAttentionOpImpl()
+{
+}
+template<typename T, int V>
+int FlashAttentionOpImpl<T, V>::get_workspace_size() const
+{
+    return 0;
+}
+template<typename T, int V>
+void FlashAttentionOpImpl<T, V>::operator()(Params&, cudaStream_t) const
+{
+    std::fprintf(stderr, "FlashAttentionOpImpl is not built in this test library\n");
+    std::abort();
+}
+template class FlashAttentionOpImpl<half, 1>;
+template class FlashAttentionOpImpl<half, 2>;
+template class FlashAttentionOpImpl<float, 1>;
+template class FlashAttentionOpImpl<float, 2>;
+}  // namespace turbomind
 
 namespace {
 bool g_sync = true;
@@ -133,12 +170,57 @@ REF_API int ref_mmha_decode(void* out, const void* q, const void* k, const void*
     return finish((cudaStream_t)stream);
 }
 
-// llama_decoder_kernels.h:8-9 (llama_kernels.cu, which holds the plain RMSNorm, drags in the
-// reference's flash-attention sources and is left out)
+// llama_decoder_kernels.h:8-9
 REF_API int ref_add_residual_rmsnorm(void* residual, void* in_out, const void* bias, const void* scale, float eps, int batch_size,
                                      int n_dims, void* stream)
 {
     turbomind::invokeFusedAddBiasResidualRMSNorm((half*)residual, (half*)in_out, (const half*)bias, (const half*)scale, eps,
                                                  batch_size, n_dims, (cudaStream_t)stream);
+    return finish((cudaStream_t)stream);
+}
+
+// llama_kernels.h:15-16
+REF_API int ref_rmsnorm(void* out, const void* input, const void* scale, float eps, int m, int n, void* stream)
+{
+    turbomind::invokeRootMeanSquareNorm((half*)out, (const half*)input, (const half*)scale, eps, m, n, (cudaStream_t)stream);
+    return finish((cudaStream_t)stream);
+}
+
+// unfused_attention_kernels.h:66-86
+REF_API int ref_add_fused_qkv_bias_transpose(void* q_buf, void* k_buf, void* v_buf, void* QKV, const void* qkv_bias,
+                                             const int* padding_offset, const int* history_length, const int* input_length,
+                                             int batch_size, int seq_len, int token_num, int head_num, int kv_head_num,
+                                             int size_per_head, int rotary_embedding_dim, float rotary_embedding_base,
+                                             int max_position_embeddings, int use_dynamic_ntk, int use_logn_attn, void* stream)
+{
+    turbomind::invokeAddFusedQKVBiasTranspose((half*)q_buf, (half*)k_buf, (half*)v_buf, (half*)QKV, (const half*)qkv_bias,
+                                              padding_offset, history_length, input_length, batch_size, seq_len, token_num,
+                                              head_num, kv_head_num, size_per_head, rotary_embedding_dim, rotary_embedding_base,
+                                              max_position_embeddings, use_dynamic_ntk != 0, use_logn_attn != 0,
+                                              (cudaStream_t)stream);
+    return finish((cudaStream_t)stream);
+}
+
+// llama_kernels.h:36-51
+REF_API int ref_extend_kv_cache(void** k_dst, void** v_dst, size_t dst_offset, const void* k_src, const void* v_src,
+                                int local_batch_size, const int* query_length, int max_q_len, const int* history_length,
+                                int max_seq_len, int size_per_head, int local_head_num, void* stream, int quant,
+                                const float* kv_scale)
+{
+    turbomind::invokeExtendKVCache((half**)k_dst, (half**)v_dst, dst_offset, (const half*)k_src, (const half*)v_src,
+                                   local_batch_size, query_length, max_q_len, history_length, max_seq_len, size_per_head,
+                                   local_head_num, (cudaStream_t)stream, quant, kv_scale);
+    return finish((cudaStream_t)stream);
+}
+
+// llama_kernels.h:53-68
+REF_API int ref_transpose_kv_cache(void* key_cache_trans, void* val_cache_trans, const void** key_cache, const void** val_cache,
+                                   size_t src_offset, int batch_size, const int* key_length, int max_kv_len, int max_seq_len,
+                                   int size_per_head, int head_num, int head_n_rep, void* stream, int quant,
+                                   const float* kv_scale)
+{
+    turbomind::invokeTransposeKVCache((half*)key_cache_trans, (half*)val_cache_trans, (const half**)key_cache,
+                                      (const half**)val_cache, src_offset, batch_size, key_length, max_kv_len, max_seq_len,
+                                      size_per_head, head_num, head_n_rep, (cudaStream_t)stream, quant, kv_scale);
     return finish((cudaStream_t)stream);
 }

@@ -36,6 +36,8 @@ def ref():
     lib.ref_mmha_decode.argtypes = [vp] * 7 + [i] * 5 + [i, f32, i, vp, vp, vp, vp, vp, C.c_size_t, i, f32, f32, f32, f32, i, i,
                                                           i, vp]
     lib.ref_add_residual_rmsnorm.argtypes = [vp, vp, vp, vp, f32, i, i, vp]
+    lib.ref_rmsnorm.argtypes = [vp, vp, vp, f32, i, i, vp]
+    lib.ref_rmsnorm.restype = i
     for name in ("ref_reformat_s4_k_m8", "ref_convert_s4_k_m8", "ref_transpose_qk_s4_k_m8_hf", "ref_fuse_w1_w3_s4_k_m8",
                  "ref_dequantize_s4", "ref_gemm_s4_f16", "ref_mmha_decode", "ref_add_residual_rmsnorm"):
         getattr(lib, name).restype = i
@@ -185,6 +187,24 @@ def test_fused_add_rmsnorm_matches_reference_kernel(ref, m, n, bias):
     assert np.array_equal(outs[0][0].view(np.uint16), np.asarray(r_cpu).view(np.uint16)), "residual: CPU oracle != reference"
     assert_close(outs[1][1], outs[0][1], "norm output: library vs reference kernel", max_abs=4e-3)
     assert_close(outs[0][1], o_cpu, "norm output: reference kernel vs CPU oracle", max_abs=4e-3)
+
+
+@pytest.mark.parametrize("m,n", [(1, 4096), (64, 4096), (3, 8192)])
+def test_rmsnorm_matches_reference_kernel(ref, m, n):
+    """invokeRootMeanSquareNorm of the reference against tm_rmsnorm and the CPU oracle."""
+    from lmdeploy_b200 import turbomind as tm
+    from oracle import norm as on
+    rng = np.random.default_rng(19)
+    x = (rng.standard_normal((m, n)) * 1.5).astype(np.float16)
+    w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float16)
+    xd, wd = dev(x), dev(w)
+    o_ref = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    o_lib = torch.zeros_like(o_ref)
+    assert ref.ref_rmsnorm(_p(o_ref), _p(xd), _p(wd), 1e-6, m, n, None) == 0
+    tm.invokeRootMeanSquareNorm(o_lib, xd, wd, 1e-6, m, n)
+    torch.cuda.synchronize()
+    assert_close(o_lib.cpu().numpy(), o_ref.cpu().numpy(), "rmsnorm: library vs reference kernel", max_abs=4e-3)
+    assert_close(on.rmsnorm(x, w, 1e-6), o_ref.cpu().numpy(), "rmsnorm: CPU oracle vs reference kernel", max_abs=4e-3)
 
 
 # ------------------------------------------------------------------------------------- attention
