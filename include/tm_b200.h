@@ -217,6 +217,38 @@ TM_API int tm_transpose_kv_cache(void* key_cache_trans, void* val_cache_trans, c
                                  const float* kv_scale);
 
 /* ------------------------------------------------------------------------------------------
+ * Prefill (context) attention over the KV cache: causal softmax(q k^T / sqrt(128)) v for the new tokens of
+ * every sequence, keys / values read in place from the per-sequence cache (fp16, or int8 dequantised as
+ * half(q * scale + zp) on the fly), grouped-query heads.  Replaces what
+ *   LlamaContextAttentionLayer<T>::fusedMultiHeadAttention  (src/turbomind/models/llama/
+ *   LlamaContextAttentionLayer.cc:257-313) asks of FlashAttentionOp<T>::operator()
+ *   (src/turbomind/models/llama/llama_kernels.h:129-150): query = q_buf_2_, key / val = the cache pointers
+ *   with the layer offset, cu_seqlens for the packed output, actual_seqlen_k = context_lengths,
+ * and, for an int8 cache, the unfused route (:316-420) without its dequantised copy of the cache.
+ * Query i of sequence b sits at position context_lengths[b] - q_len[b] + i and sees keys [0, position];
+ * q_len[b] = cu_seqlens[b + 1] - cu_seqlens[b]; its output row is cu_seqlens[b] + i.
+ * The new tokens' keys / values must already be in the cache (tm_extend_kv_cache).
+ */
+typedef struct tm_context_attention_params {
+    void*        attn_out;           /* half [token_num, head_num * 128]                           */
+    const void*  query;              /* half [batch, head_num, max_q_len, 128]                     */
+    void**       key_cache;          /* device array [batch] of per-sequence cache base pointers   */
+    void**       val_cache;
+    size_t       cache_layer_offset; /* elements: layer * kv_head_num * max_seq_len * 128          */
+    const int*   cu_seqlens;         /* device int [batch + 1], prefix sums of the query lengths   */
+    const int*   context_lengths;    /* device int [batch], history + query length                 */
+    int          batch_size;
+    int          head_num;
+    int          kv_head_num;
+    int          size_per_head;      /* 128 */
+    int          max_q_len;
+    int          max_seq_len;        /* rows per head of the cache                                 */
+    int          quant_policy;       /* & 4: int8 cache                                            */
+    float        kv_scale[4];        /* k_scale, k_zp, v_scale, v_zp                               */
+} tm_context_attention_params;
+TM_API int tm_context_attention(const tm_context_attention_params* params, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Tensor-parallel communicator (one process per GPU; NCCL over NVLink).  Replaces
  *   ftNcclAllReduceSum<half> / ftNcclAllGather (src/turbomind/utils/nccl_utils.h:94-99) and the
  *   NcclParam set-up of src/turbomind/triton_backend/transformer_triton_backend.cpp:24-82.

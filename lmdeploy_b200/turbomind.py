@@ -256,3 +256,22 @@ def invokeTransposeKVCache(key_cache_trans, val_cache_trans, key_cache, val_cach
     _l.check(_l.lib.tm_transpose_kv_cache(_ptr(key_cache_trans), _ptr(val_cache_trans), _ptr(key_cache), _ptr(val_cache),
                                           src_offset, batch_size, _ptr(key_length), max_kv_len, max_seq_len, size_per_head,
                                           head_num, head_n_rep, st, quant, _kv_scale(kv_scale)), "invokeTransposeKVCache")
+
+
+def fusedMultiHeadAttention(attn_out, query, key_cache_ptrs, val_cache_ptrs, cache_layer_offset, cu_seqlens, context_lengths,
+                            batch_size, max_q_len, max_seq_len, head_num, kv_head_num, size_per_head=128, quant_policy=0,
+                            kv_scale=None, stream=None):
+    """LlamaContextAttentionLayer<T>::fusedMultiHeadAttention (src/turbomind/models/llama/LlamaContextAttentionLayer.cc:
+    257-313) with the layer's members passed explicitly: causal attention of the new tokens over the cache in place,
+    attn_out [token_num, head_num * size_per_head] packed by cu_seqlens."""
+    _need_cuda(attn_out, query, key_cache_ptrs, val_cache_ptrs, cu_seqlens, context_lengths)
+    a = _l.TmContextAttentionParams()
+    a.attn_out, a.query = attn_out.data_ptr(), query.data_ptr()
+    a.key_cache, a.val_cache, a.cache_layer_offset = key_cache_ptrs.data_ptr(), val_cache_ptrs.data_ptr(), cache_layer_offset
+    a.cu_seqlens, a.context_lengths = cu_seqlens.data_ptr(), context_lengths.data_ptr()
+    a.batch_size, a.head_num, a.kv_head_num, a.size_per_head = batch_size, head_num, kv_head_num, size_per_head
+    a.max_q_len, a.max_seq_len, a.quant_policy = max_q_len, max_seq_len, quant_policy
+    if kv_scale is not None:
+        a.kv_scale = _kv_scale(kv_scale)
+    st = _stream() if stream is None else C.c_void_p(stream)
+    _l.check(_l.lib.tm_context_attention(C.byref(a), st), "fusedMultiHeadAttention")

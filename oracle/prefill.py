@@ -107,3 +107,32 @@ def transpose_kv_cache(k_cache, v_cache, layer_offset_rows_head, key_length, max
             out[b, :, :n] = np.repeat(rows, head_n_rep, axis=0)  # query head h reads cached head h / n_rep (:526)
         outs.append(out)
     return outs[0], outs[1]
+
+
+def context_attention(q, k_cache, v_cache, layer_offset_rows_head, cu_seqlens, context_lengths, head_num, kv_head_num,
+                      kv_scale=None):
+    """Causal attention of the new tokens over the cache, as the reference's unfused route defines it
+    (src/turbomind/models/llama/LlamaContextAttentionLayer.cc:316-420: transposed cache -> q k^T (fp32 accumulate) ->
+    invokeMaskedSoftmax with scale 1/sqrt(d), probabilities stored as fp16 -> p v (fp32 accumulate) -> fp16) and as its
+    flash-attention route computes up to rounding (:257-313).  The mask is invokeCreateCausalMasks
+    (src/turbomind/models/llama/llama_kernels.cu:179-201): query i sees key j iff j <= i + (k_len - q_len).
+
+    q fp16 [B, H, max_q_len, D]; caches as in extend_kv_cache; -> fp16 [token_num, H * D] (packed by cu_seqlens)."""
+    B = len(k_cache)
+    n_rep = head_num // kv_head_num
+    out = np.zeros((int(cu_seqlens[B]), head_num * D), np.float16)
+    scale = np.float32(1.0 / np.sqrt(np.float32(D)))
+    for b in range(B):
+        tok0, q_len, ctx = int(cu_seqlens[b]), int(cu_seqlens[b + 1] - cu_seqlens[b]), int(context_lengths[b])
+        hist = ctx - q_len
+        for h in range(head_num):
+            row = layer_offset_rows_head + h // n_rep
+            k, v = k_cache[b][row, :ctx], v_cache[b][row, :ctx]
+            if k.dtype == np.int8:
+                k, v = dequant_int8(k, kv_scale[0], kv_scale[1]), dequant_int8(v, kv_scale[2], kv_scale[3])
+            s = (q[b, h, :q_len].astype(np.float32) @ k.astype(np.float32).T) * scale
+            s[np.arange(ctx)[None, :] > (hist + np.arange(q_len))[:, None]] = -np.inf
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            p = (p / p.sum(axis=1, keepdims=True)).astype(np.float16)
+            out[tok0:tok0 + q_len, h * D:(h + 1) * D] = (p.astype(np.float32) @ v.astype(np.float32)).astype(np.float16)
+    return out

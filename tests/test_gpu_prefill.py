@@ -255,3 +255,86 @@ def test_argument_checks():
     assert e(ip, ip, 0, p, p, 0, ip, 1, ip, 16, D, 1, None, 0, None) == l.TM_OK
     t = l.lib.tm_transpose_kv_cache
     assert t(p, p, ip, ip, 0, 1, ip, 1, 16, D, 3, 2, None, 0, None) == l.TM_ERR_INVALID_ARG                      # 3 heads, groups of 2
+
+
+# ------------------------------------------------------------------------------- context attention
+
+def attention_case(q_lens, hist, H, Hkv, S_max, layers, layer, seed, int8):
+    rng = np.random.default_rng(seed)
+    B = len(q_lens)
+    max_q = max(q_lens)
+    q = rng.standard_normal((B, H, max_q, D)).astype(np.float16)
+    if int8:
+        kc = [rng.integers(-128, 128, size=(layers * Hkv, S_max, D)).astype(np.int8) for _ in range(B)]
+        vc = [rng.integers(-128, 128, size=(layers * Hkv, S_max, D)).astype(np.int8) for _ in range(B)]
+        scale = np.asarray([0.011, 0.05, 0.013, -0.1], np.float32)
+    else:
+        kc = [rng.standard_normal((layers * Hkv, S_max, D)).astype(np.float16) for _ in range(B)]
+        vc = [rng.standard_normal((layers * Hkv, S_max, D)).astype(np.float16) for _ in range(B)]
+        scale = None
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    ctx = (np.asarray(q_lens) + np.asarray(hist)).astype(np.int32)
+    return dict(q=q, kc=kc, vc=vc, scale=scale, cu=cu, ctx=ctx, B=B, H=H, Hkv=Hkv, S_max=S_max, layer=layer, max_q=max_q)
+
+
+def run_attention(c):
+    from lmdeploy_b200 import turbomind as tm
+    kd, vd, kp, vp = _cache_tensors(c)
+    out = torch.zeros((int(c["cu"][-1]), c["H"] * D), dtype=torch.float16, device="cuda")
+    tm.fusedMultiHeadAttention(out, dev(c["q"]), kp, vp, c["layer"] * c["Hkv"] * c["S_max"] * D, dev(c["cu"]), dev(c["ctx"]),
+                               c["B"], c["max_q"], c["S_max"], c["H"], c["Hkv"], D, 4 if c["scale"] is not None else 0, c["scale"])
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("q_lens,hist,H,Hkv", [
+    ([1, 64, 65], [0, 0, 0], 2, 2),             # single token, exactly one tile, one row into the second tile
+    ([130, 17, 200], [0, 100, 37], 4, 1),       # history, ragged lengths, grouped-query heads
+    ([300], [211], 8, 2),                       # many key tiles, the diagonal in the middle of a tile
+])
+def test_context_attention_matches_oracle(int8, q_lens, hist, H, Hkv):
+    from tests.helpers import assert_close
+    S_max = max(a + b for a, b in zip(q_lens, hist)) + 3
+    c = attention_case(q_lens, hist, H, Hkv, S_max, layers=2, layer=1, seed=23, int8=int8)
+    got = run_attention(c)
+    want = op.context_attention(c["q"], c["kc"], c["vc"], c["layer"] * c["Hkv"], c["cu"], c["ctx"], H, Hkv, c["scale"])
+    assert_close(got, want, f"context attention (int8={int8})")   # max-abs 2e-2, mean-rel 1e-3: the fp16 bar of the path
+
+
+def test_context_attention_properties_at_full_size():
+    """Llama-2-7B prefill shape (4 x 2048 tokens, 32 heads).  (1) With every value row equal to one vector the output is
+    that vector whatever the scores are.  (2) Causality: changing the keys / values of the LAST position changes no
+    output row except the last one of each sequence."""
+    from lmdeploy_b200 import turbomind as tm
+    B, H, S = 4, 32, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn((B, H, S, D), device="cuda", dtype=torch.float16, generator=g)
+    kc = [torch.randn((H, S, D), device="cuda", dtype=torch.float16, generator=g) for _ in range(B)]
+    vrow = torch.randn((H, 1, D), device="cuda", dtype=torch.float16, generator=g)
+    vc = [vrow.expand(H, S, D).contiguous() for _ in range(B)]
+    kp = torch.tensor([t.data_ptr() for t in kc], dtype=torch.int64, device="cuda")
+    vp = torch.tensor([t.data_ptr() for t in vc], dtype=torch.int64, device="cuda")
+    lens = [2048, 1000, 1, 2047]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    out = torch.zeros((sum(lens), H * D), dtype=torch.float16, device="cuda")
+    tm.fusedMultiHeadAttention(out, q, kp, vp, 0, cu, ctx, B, S, S, H, H, D)
+    torch.cuda.synchronize()
+    want = vrow.reshape(1, H * D).float()
+    assert float((out.float() - want).abs().max()) <= 2e-3 * float(want.abs().max()) + 1e-3
+    # causality
+    vc2 = [torch.randn((H, S, D), device="cuda", dtype=torch.float16, generator=g) for _ in range(B)]
+    vp2 = torch.tensor([t.data_ptr() for t in vc2], dtype=torch.int64, device="cuda")
+    a = torch.zeros_like(out)
+    tm.fusedMultiHeadAttention(a, q, kp, vp2, 0, cu, ctx, B, S, S, H, H, D)
+    for b, n in enumerate(lens):
+        kc[b][:, n - 1] += 1.0
+        vc2[b][:, n - 1] -= 3.0
+    b2 = torch.zeros_like(out)
+    tm.fusedMultiHeadAttention(b2, q, kp, vp2, 0, cu, ctx, B, S, S, H, H, D)
+    torch.cuda.synchronize()
+    last = torch.zeros(sum(lens), dtype=torch.bool, device="cuda")
+    last[(cu[1:] - 1).long()] = True
+    assert torch.equal(a[~last], b2[~last])
+    assert not torch.equal(a[last], b2[last])
