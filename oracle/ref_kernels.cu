@@ -224,3 +224,29 @@ REF_API int ref_transpose_kv_cache(void* key_cache_trans, void* val_cache_trans,
                                       size_per_head, head_num, head_n_rep, (cudaStream_t)stream, quant, kv_scale);
     return finish((cudaStream_t)stream);
 }
+
+// llama_kernels.h:32-34: mask half [batch, max_q_len, max_k_len], 1 = visible
+REF_API int ref_create_causal_masks(void* mask, const int* q_lens, const int* k_lens, int max_q_len, int max_k_len, int batch_size,
+                                    void* stream)
+{
+    turbomind::invokeCreateCausalMasks((half*)mask, q_lens, k_lens, max_q_len, max_k_len, batch_size, (cudaStream_t)stream);
+    return finish((cudaStream_t)stream);
+}
+
+// unfused_attention_kernels.h:22-40 as LlamaContextAttentionLayer.cc:372-382 fills it (half in, half out, in place allowed)
+REF_API int ref_masked_softmax(void* attention_score, const void* qk, const void* attention_mask, int batch_size, int q_length,
+                               int k_length, int num_heads, float qk_scale, void* stream)
+{
+    turbomind::MaskedSoftmaxParam<half, half> param{};
+    param.attention_score    = (half*)attention_score;
+    param.qk                 = (const half*)qk;
+    param.attention_mask     = (const half*)attention_mask;
+    param.batch_size         = batch_size;
+    param.q_length           = q_length;
+    param.k_length           = k_length;
+    param.num_heads          = num_heads;
+    param.qk_scale           = (half)qk_scale;
+    param.linear_bias_slopes = nullptr;
+    turbomind::invokeMaskedSoftmax(param, (cudaStream_t)stream);
+    return finish((cudaStream_t)stream);
+}

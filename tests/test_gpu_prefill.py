@@ -26,7 +26,10 @@ def load_ref():
     lib.ref_add_fused_qkv_bias_transpose.argtypes = [vp] * 8 + [i] * 7 + [f32, i, i, i, vp]
     lib.ref_extend_kv_cache.argtypes = [vp, vp, sz, vp, vp, i, vp, i, vp, i, i, i, vp, i, C.POINTER(f32)]
     lib.ref_transpose_kv_cache.argtypes = [vp, vp, vp, vp, sz, i, vp, i, i, i, i, i, vp, i, C.POINTER(f32)]
-    for n in ("ref_add_fused_qkv_bias_transpose", "ref_extend_kv_cache", "ref_transpose_kv_cache"):
+    lib.ref_create_causal_masks.argtypes = [vp, vp, vp, i, i, i, vp]
+    lib.ref_masked_softmax.argtypes = [vp, vp, vp, i, i, i, i, f32, vp]
+    for n in ("ref_add_fused_qkv_bias_transpose", "ref_extend_kv_cache", "ref_transpose_kv_cache", "ref_create_causal_masks",
+              "ref_masked_softmax"):
         getattr(lib, n).restype = i
     return lib
 
@@ -300,6 +303,40 @@ def test_context_attention_matches_oracle(int8, q_lens, hist, H, Hkv):
     got = run_attention(c)
     want = op.context_attention(c["q"], c["kc"], c["vc"], c["layer"] * c["Hkv"], c["cu"], c["ctx"], H, Hkv, c["scale"])
     assert_close(got, want, f"context attention (int8={int8})")   # max-abs 2e-2, mean-rel 1e-3: the fp16 bar of the path
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_context_attention_against_the_reference_unfused_route(ref, int8):
+    """The reference's own kernels for everything but the two batched GEMMs (which it hands to cuBLAS, as torch.matmul does
+    here): invokeTransposeKVCache -> q k^T (fp16 out) -> invokeCreateCausalMasks + invokeMaskedSoftmax -> p v
+    (src/turbomind/models/llama/LlamaContextAttentionLayer.cc:316-420).  Pins the CPU oracle and the kernel to it."""
+    from tests.helpers import assert_close
+    if ref is None:
+        pytest.skip("oracle/_ref/libtm_ref.so not built")
+    q_lens, hist, H, Hkv = [130, 17, 200], [0, 100, 37], 4, 2
+    S_max = 240
+    c = attention_case(q_lens, hist, H, Hkv, S_max, layers=2, layer=1, seed=29, int8=int8)
+    B, max_q, max_k = c["B"], c["max_q"], int(c["ctx"].max())
+    # --- the reference route
+    kd, vd, kp, vp = _cache_tensors(c)
+    kt = torch.zeros((B, H, max_k, D), dtype=torch.float16, device="cuda")
+    vt = torch.zeros_like(kt)
+    ctx_d, ql_d = dev(c["ctx"]), dev(np.asarray(q_lens, np.int32))
+    sc = None if c["scale"] is None else (C.c_float * 4)(*[float(x) for x in c["scale"]])
+    assert ref.ref_transpose_kv_cache(_p(kt), _p(vt), _p(kp), _p(vp), c["layer"] * Hkv * S_max * D, B, _p(ctx_d), max_k, S_max, D,
+                                      H, H // Hkv, None, 4 if int8 else 0, sc) == 0
+    qd = dev(c["q"])
+    qk = torch.matmul(qd, kt.transpose(2, 3)).contiguous()                      # half [B, H, max_q, max_k]
+    mask = torch.zeros((B, max_q, max_k), dtype=torch.float16, device="cuda")
+    assert ref.ref_create_causal_masks(_p(mask), _p(ql_d), _p(ctx_d), max_q, max_k, B, None) == 0
+    assert ref.ref_masked_softmax(_p(qk), _p(qk), _p(mask), B, max_q, max_k, H, 1.0 / np.sqrt(D), None) == 0
+    o = torch.matmul(qk, vt)                                                    # [B, H, max_q, D]
+    theirs = np.concatenate([o[b, :, :n].transpose(0, 1).reshape(n, H * D).cpu().numpy() for b, n in enumerate(q_lens)])
+    # --- the oracle and the kernel
+    want = op.context_attention(c["q"], c["kc"], c["vc"], c["layer"] * Hkv, c["cu"], c["ctx"], H, Hkv, c["scale"])
+    got = run_attention(c)
+    assert_close(want, theirs, f"CPU oracle vs reference unfused route (int8={int8})")
+    assert_close(got, theirs, f"kernel vs reference unfused route (int8={int8})")
 
 
 def test_context_attention_properties_at_full_size():
