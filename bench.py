@@ -7,6 +7,10 @@ Workloads (``config.workload``):
             pass over the four linears of a layer.  Inputs larger than L2: the weights of every
             projection are replicated until they exceed twice the L2 size and each launch takes
             the next replica.
+  mmha      decode attention, batch 64, KV length uniform in ``--kv-len``, int8 or fp16 cache.
+  prefill   attention side of one prefill layer (QKV bias + RoPE + transpose, KV-cache extend, causal attention
+            over the cache) for ``--batch`` (default 8) sequences of 2048 new tokens.
+  decode    (default) whole-model greedy decode, Llama-2-7B at 1 GPU, Llama-2-70B tensor-parallel at N > 1.
 
 The timed region is bracketed by a barrier + ``torch.cuda.synchronize()``; device time comes from
 CUDA events on the launching stream; SM clocks and throttle reasons are sampled with nvidia-smi
@@ -362,6 +366,139 @@ def run_mmha_workload(args, rank, world, device):
     return res
 
 
+def run_prefill_workload(args, rank, world, device):
+    """Attention side of one Llama-2-7B prefill layer: ``--batch`` sequences (default 8) of 2048 new tokens, 32 heads.
+    A step = QKV bias + RoPE + transpose -> KV-cache extend -> causal attention over the cache.  Inputs larger than L2
+    (the fused QKV buffer alone is 0.4 GB at batch 8).  With --impl reference the same three stages run on the
+    reference's own kernels: its writers, and its unfused attention route (cache transpose, cuBLAS GEMMs through
+    torch.matmul, mask + softmax kernels), because its flash-attention build needs CUTLASS."""
+    import ctypes as C
+    from lmdeploy_b200 import turbomind as tm
+    torch.cuda.set_device(device)
+    B = args.batch if args.batch != 64 else 8
+    H, D, S = args.heads, 128, 2048
+    Hkv = args.kv_heads
+    int8 = args.kv == "int8"
+    S_max = S
+    g = torch.Generator(device=device).manual_seed(11 + rank)
+    qkv = torch.randn(B * S, (H + 2 * Hkv) * D, device=device, generator=g).half()
+    q = torch.empty((B, H, S, D), dtype=torch.float16, device=device)
+    k = torch.empty((B, Hkv, S, D), dtype=torch.float16, device=device)
+    v = torch.empty_like(k)
+    esz = 1 if int8 else 2
+    kc = torch.zeros((B, Hkv * S_max * D * esz), dtype=torch.uint8, device=device)
+    vc = torch.zeros_like(kc)
+    kp = torch.tensor([kc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
+    vp_ = torch.tensor([vc[b].data_ptr() for b in range(B)], dtype=torch.int64, device=device)
+    hist = torch.zeros(B, dtype=torch.int32, device=device)
+    lens = torch.full((B,), S, dtype=torch.int32, device=device)
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=device)
+    out = torch.empty((B * S, H * D), dtype=torch.float16, device=device)
+    scale = [6.0 / 127, 0.0, 6.0 / 127, 0.0] if int8 else None
+    quant = 4 if int8 else 0
+    reflib = load_reference_kernels() if args.impl == "reference" else None
+    if args.impl == "reference" and reflib is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libtm_ref.so not built (python oracle/build_ref.py needs the reference tree)"}
+    P = lambda t: C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p()
+    cur = lambda: C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sc = None if scale is None else (C.c_float * 4)(*scale)
+    if reflib is not None:
+        reflib.ref_add_fused_qkv_bias_transpose.argtypes = [C.c_void_p] * 8 + [C.c_int] * 7 + [C.c_float] + [C.c_int] * 3 + [C.c_void_p]
+        reflib.ref_extend_kv_cache.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                               C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_float)]
+        reflib.ref_transpose_kv_cache.argtypes = [C.c_void_p] * 4 + [C.c_size_t, C.c_int, C.c_void_p] + [C.c_int] * 5 + [C.c_void_p, C.c_int,
+                                                                                                                    C.POINTER(C.c_float)]
+        reflib.ref_create_causal_masks.argtypes = [C.c_void_p] * 3 + [C.c_int] * 3 + [C.c_void_p]
+        reflib.ref_masked_softmax.argtypes = [C.c_void_p] * 3 + [C.c_int] * 4 + [C.c_float, C.c_void_p]
+        kt = torch.empty((B, H, S, D), dtype=torch.float16, device=device)
+        vt = torch.empty_like(kt)
+        mask = torch.empty((B, S, S), dtype=torch.float16, device=device)
+        assert reflib.ref_create_causal_masks(P(mask), P(lens), P(lens), S, S, B, cur()) == 0   # built once per batch, not per layer
+
+    def stage_qkv():
+        if reflib is None:
+            tm.invokeAddFusedQKVBiasTranspose(q, k, v, qkv, None, None, hist, lens, B, S, B * S, H, Hkv, D, D, 10000.0, 2048, False, False)
+        else:
+            assert reflib.ref_add_fused_qkv_bias_transpose(P(q), P(k), P(v), P(qkv), None, None, P(hist), P(lens), B, S, B * S, H, Hkv, D,
+                                                           D, 10000.0, 2048, 0, 0, cur()) == 0
+
+    def stage_extend():
+        if reflib is None:
+            tm.invokeExtendKVCache(kp, vp_, 0, k, v, B, lens, S, hist, S_max, D, Hkv, None, quant, scale)
+        else:
+            assert reflib.ref_extend_kv_cache(P(kp), P(vp_), 0, P(k), P(v), B, P(lens), S, P(hist), S_max, D, Hkv, cur(), quant, sc) == 0
+
+    def stage_attention():
+        if reflib is None:
+            tm.fusedMultiHeadAttention(out, q, kp, vp_, 0, cu, lens, B, S, S_max, H, Hkv, D, quant, scale)
+        else:
+            assert reflib.ref_transpose_kv_cache(P(kt), P(vt), P(kp), P(vp_), 0, B, P(lens), S, S_max, D, H, H // Hkv, cur(), quant, sc) == 0
+            qk = torch.matmul(q, kt.transpose(2, 3))
+            assert reflib.ref_masked_softmax(P(qk), P(qk), P(mask), B, S, S, H, 1.0 / np.sqrt(D), cur()) == 0
+            torch.matmul(qk, vt).transpose(1, 2).reshape(B * S, H * D)
+
+    stages = [("qkv_bias_rope_transpose", stage_qkv), ("extend_kv_cache", stage_extend), ("context_attention", stage_attention)]
+    if reflib is not None:
+        reflib.ref_set_sync(0)
+    stream = torch.cuda.Stream(device)
+    per = {}
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            for _, f in stages:
+                f()
+        torch.cuda.synchronize()
+        for name, f in stages:   # per-stage device time (explains the step time; the step itself is timed below)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(max(2, args.steps // 4)):
+                f()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            per[name] = e0.elapsed_time(e1) / max(2, args.steps // 4)
+        barrier(world)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            for _, f in stages:
+                f()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        barrier(world)
+        ms = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+    if reflib is not None:
+        reflib.ref_set_sync(1)
+    ms = max_over_ranks(ms, world)
+    peaks = measured_peaks()
+    flops = 4.0 * D * H * B * (S * (S + 1) / 2)            # causal: query i sees i + 1 keys; 2 products x 2 flops
+    tf = flops / (per["context_attention"] * 1e-3) * 1e-12
+    qkv_bytes = 2 * qkv.numel() * 2                         # read the fused buffer, write q, k, v
+    ext_bytes = 2 * k.numel() * (2 + esz)                   # read k, v; write the cache rows
+    res = {
+        "metric": "prefill attention tokens/s (QKV RoPE/transpose + KV-cache extend + causal attention, one layer)",
+        "value": round(B * S * world / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": f"f16 q, {args.kv} KV, f32 softmax/accumulate", "data": "synthetic",
+        "config": {"workload": "prefill", "batch": B, "new_tokens": S, "heads": H, "kv_heads": Hkv, "kv": args.kv,
+                   "l2": "inputs larger than L2 (fused QKV buffer %.2f GB)" % (qkv.numel() * 2e-9),
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "roofline": {"bound": "tensor", "kernel": "reference unfused route" if reflib is not None else "context_attention_kernel",
+                     "achieved": round(tf, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": round(tf / peaks["bf16_tflops"], 4), "peak_source": peaks["source"], "algorithmic_flops": flops,
+                     "traffic": None},
+        "stages_ms": {n: round(t, 4) for n, t in per.items()},
+        "stages_gbs": {"qkv_bias_rope_transpose": round(qkv_bytes / per["qkv_bias_rope_transpose"] * 1e-6, 1),
+                       "extend_kv_cache": round(ext_bytes / per["extend_kv_cache"] * 1e-6, 1)},
+        "clocks": clocks, "gpu_launches": args.steps * 3,
+    }
+    if reflib is not None:
+        mark_reference_kernel_arm(res)
+    return res
+
+
 DECODE_WORKLOADS = {
     # name: (config attr, batch, prompt_lo, prompt_hi, new_tokens)
     "decode7b": ("LLAMA2_7B", 64, 128, 1024, 256),
@@ -666,7 +803,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="decode",
-                    help="decode (7B at 1 GPU, 70B tensor-parallel at N > 1) | decode7b | decode70b | gemm | mmha")
+                    help="decode (7B at 1 GPU, 70B tensor-parallel at N > 1) | decode7b | decode70b | gemm | mmha | prefill")
     ap.add_argument("--batch-override", type=int, default=0, help="smaller batch for smoke runs")
     ap.add_argument("--max-prompt", type=int, default=0, help="cap on the prompt length for smoke runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -684,7 +821,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference" and args.workload not in ("gemm", "mmha"):
+    if args.impl == "reference" and args.workload not in ("gemm", "mmha", "prefill"):
         # whole-model workloads: the reference's CPU path (the engine around its kernels is out of scope)
         out = run_reference_arm(args, rank, world)
         if rank == 0:
@@ -704,6 +841,8 @@ def main():
         out = run_gemm_workload(args, rank, world, local)
     elif args.workload == "mmha":
         out = run_mmha_workload(args, rank, world, local)
+    elif args.workload == "prefill":
+        out = run_prefill_workload(args, rank, world, local)
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     if rank == 0:
