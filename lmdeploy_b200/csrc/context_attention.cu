@@ -68,6 +68,13 @@ __device__ __forceinline__ void cp_async_wait_all()
 {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
+// 2^x by the special-function unit (one instruction; relative error 2^-22, far below the fp16 rounding of p)
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_half2(float a, float b)
 {
     const __half2 h = __floats2half2_rn(a, b);
@@ -245,14 +252,15 @@ __global__ void __launch_bounds__(kThreads) context_attention_kernel(CtxParams p
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         }
-        const float corr[2] = {exp2f((row_max[0] - mx[0]) * p.scale_log2), exp2f((row_max[1] - mx[1]) * p.scale_log2)};
+        const float corr[2] = {fast_exp2((row_max[0] - mx[0]) * p.scale_log2), fast_exp2((row_max[1] - mx[1]) * p.scale_log2)};
+        const float off[2]  = {-mx[0] * p.scale_log2, -mx[1] * p.scale_log2};  // p = 2^(s * scale + off): one fma per score
         row_max[0] = mx[0], row_max[1] = mx[1];
         float part[2] = {0.f, 0.f};
         uint32_t pa[4][4];  // probabilities as A fragments of the 4 key blocks of 16
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float p0 = exp2f((s[j][0] - mx[0]) * p.scale_log2), p1 = exp2f((s[j][1] - mx[0]) * p.scale_log2);
-            const float p2 = exp2f((s[j][2] - mx[1]) * p.scale_log2), p3 = exp2f((s[j][3] - mx[1]) * p.scale_log2);
+            const float p0 = fast_exp2(fmaf(s[j][0], p.scale_log2, off[0])), p1 = fast_exp2(fmaf(s[j][1], p.scale_log2, off[0]));
+            const float p2 = fast_exp2(fmaf(s[j][2], p.scale_log2, off[1])), p3 = fast_exp2(fmaf(s[j][3], p.scale_log2, off[1]));
             part[0] += p0 + p1;
             part[1] += p2 + p3;
             pa[j >> 1][(j & 1) * 2]     = pack_half2(p0, p1);

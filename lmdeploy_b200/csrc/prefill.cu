@@ -10,7 +10,7 @@
 // All three are pure HBM traffic, so each moves 16 bytes per thread and does the K and the V half of
 // its job in ONE launch (the reference launches K and V separately, and one 64-thread CTA per
 // (token, head) for the first).  The rotary angles of a token are the same for all of its heads:
-// a CTA computes the 64 (cos, sin) pairs of its token once and applies them to 16 heads.
+// one CTA owns a token, computes its 64 (cos, sin) pairs once and applies them to all heads.
 // The transpose reads a cached row once and writes it to every query head of its group.
 #include "common.cuh"
 #include "mmha.h"
@@ -42,18 +42,38 @@ struct QkvParams {
     int           use_logn;
 };
 
-// grid (token_num, ceil((H + 2 Hkv) / 16)); thread = (head within the CTA, 16-byte vector of the head)
+constexpr int kHeadBatch = 4;  // 16-byte loads a thread keeps in flight: 4 x 16 heads per pass
+
+// grid (token_num); thread = (head within a group of 16, 16-byte vector of the head); the CTA walks all
+// H + 2 Hkv heads of its token in passes of 64, so the token's angles are computed once
 __global__ void __launch_bounds__(kQkvThreads) qkv_bias_rope_transpose_kernel(QkvParams p)
 {
     __shared__ float2 coef[kD / 2];  // (cos, sin) of pair i = elements 2i, 2i + 1
     pdl_wait();
     pdl_launch_dependents();
     const int token = blockIdx.x;
-    const int tgt   = token + (p.padding_offset ? p.padding_offset[token] : 0);  // :877-878
-    const int bi    = tgt / p.seq_len;
-    const int si    = tgt % p.seq_len;
-    const int hist  = p.history_length[bi];
-    const int step  = hist + si;  // :929
+    const int total = p.H + 2 * p.Hkv;
+    const int hsub  = threadIdx.x / kVecPerHead;
+    const int vec   = threadIdx.x % kVecPerHead;
+    const __half* row = p.qkv + (size_t)token * total * kD + vec * 8;
+    uint4 x[kHeadBatch], b[kHeadBatch];
+    auto  load_pass = [&](int h0) {
+#pragma unroll
+        for (int j = 0; j < kHeadBatch; ++j) {
+            const int head = h0 + j * kHeadsPerCta + hsub;
+            x[j] = b[j] = make_uint4(0, 0, 0, 0);
+            if (head < total) {
+                x[j] = *reinterpret_cast<const uint4*>(row + (size_t)head * kD);
+                if (p.bias) b[j] = *reinterpret_cast<const uint4*>(p.bias + (size_t)head * kD + vec * 8);
+            }
+        }
+    };
+    load_pass(0);  // requested first: the angle arithmetic below runs while the rows are in flight
+    const int tgt  = token + (p.padding_offset ? p.padding_offset[token] : 0);  // :877-878
+    const int bi   = tgt / p.seq_len;
+    const int si   = tgt % p.seq_len;
+    const int hist = p.history_length[bi];
+    const int step = hist + si;  // :929
     if (threadIdx.x < kD / 2) {
         float2 c = make_float2(1.f, 0.f);
         if (2 * (int)threadIdx.x < p.rot_dim) {
@@ -72,48 +92,49 @@ __global__ void __launch_bounds__(kQkvThreads) qkv_bias_rope_transpose_kernel(Qk
         coef[threadIdx.x] = c;
     }
     __syncthreads();
-    const int head = blockIdx.y * kHeadsPerCta + threadIdx.x / kVecPerHead;  // over q heads, then k, then v
-    const int vec  = threadIdx.x % kVecPerHead;
-    if (head >= p.H + 2 * p.Hkv) return;
-    const size_t src = (size_t)token * (p.H + 2 * p.Hkv) * kD + (size_t)head * kD + vec * 8;
-    uint4        x   = *reinterpret_cast<const uint4*>(p.qkv + src);
-    __half2*     xh  = reinterpret_cast<__half2*>(&x);
-    if (p.bias) {
-        const uint4    b  = *reinterpret_cast<const uint4*>(p.bias + (size_t)head * kD + vec * 8);
-        const __half2* bh = reinterpret_cast<const __half2*>(&b);
+    // :940-950: scaling of the length at this step, rounded to fp16, multiplied in fp16
+    const float   len1 = (float)(step + 1);
+    const __half2 logn = __half2half2(__float2half(len1 <= (float)p.max_pos ? 1.f : log2f(len1) / log2f((float)p.max_pos)));
+    for (int h0 = 0; h0 < total; h0 += kHeadBatch * kHeadsPerCta) {
+        if (h0) load_pass(h0);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) xh[e] = __hadd2(xh[e], bh[e]);  // fp16 add, :903-904
-    }
-    const bool is_q = head < p.H;
-    if (head < p.H + p.Hkv) {  // q and k rotate, v does not
+        for (int j = 0; j < kHeadBatch; ++j) {
+            const int head = h0 + j * kHeadsPerCta + hsub;
+            if (head >= total) continue;
+            __half2* xh = reinterpret_cast<__half2*>(&x[j]);
+            if (p.bias) {
+                const __half2* bh = reinterpret_cast<const __half2*>(&b[j]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int pr = vec * 4 + e;
-            if (2 * pr < p.rot_dim) {
-                const float2 c = coef[pr];
-                const float2 v = __half22float2(xh[e]);
-                // utils.h:891-904; the contraction the reference build ends up with: second product rounded, first fused
-                xh[e] = __floats2half2_rn(__fmaf_rn(c.x, v.x, -__fmul_rn(c.y, v.y)), __fmaf_rn(c.x, v.y, __fmul_rn(c.y, v.x)));
+                for (int e = 0; e < 4; ++e) xh[e] = __hadd2(xh[e], bh[e]);  // fp16 add, :903-904
+            }
+            const bool is_q = head < p.H;
+            if (head < p.H + p.Hkv) {  // q and k rotate, v does not
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int pr = vec * 4 + e;
+                    if (2 * pr < p.rot_dim) {
+                        const float2 c = coef[pr];
+                        const float2 v = __half22float2(xh[e]);
+                        // utils.h:891-904; the contraction the reference build ends up with: second product rounded, first fused
+                        xh[e] = __floats2half2_rn(__fmaf_rn(c.x, v.x, -__fmul_rn(c.y, v.y)), __fmaf_rn(c.x, v.y, __fmul_rn(c.y, v.x)));
+                    }
+                }
+            }
+            if (is_q && p.use_logn) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xh[e] = __hmul2(logn, xh[e]);
+            }
+            // [B, heads, seq_len, D]
+            if (is_q) {
+                *reinterpret_cast<uint4*>(p.q_buf + (((size_t)bi * p.H + head) * p.seq_len + si) * kD + vec * 8) = x[j];
+            }
+            else {
+                const bool is_k = head < p.H + p.Hkv;
+                const int  kvh  = head - p.H - (is_k ? 0 : p.Hkv);
+                __half*    dst  = is_k ? p.k_buf : p.v_buf;
+                *reinterpret_cast<uint4*>(dst + (((size_t)bi * p.Hkv + kvh) * p.seq_len + si) * kD + vec * 8) = x[j];
             }
         }
-    }
-    if (is_q && p.use_logn) {
-        // :940-950: scaling of the length at this step, rounded to fp16, multiplied in fp16
-        const float len = (float)(step + 1);
-        const float s   = len <= (float)p.max_pos ? 1.f : log2f(len) / log2f((float)p.max_pos);
-        const __half2 sh = __half2half2(__float2half(s));
-#pragma unroll
-        for (int e = 0; e < 4; ++e) xh[e] = __hmul2(sh, xh[e]);
-    }
-    // [B, heads, seq_len, D]
-    if (is_q) {
-        *reinterpret_cast<uint4*>(p.q_buf + (((size_t)bi * p.H + head) * p.seq_len + si) * kD + vec * 8) = x;
-    }
-    else {
-        const bool   is_k = head < p.H + p.Hkv;
-        const int    kvh  = head - p.H - (is_k ? 0 : p.Hkv);
-        __half*      dst  = is_k ? p.k_buf : p.v_buf;
-        *reinterpret_cast<uint4*>(dst + (((size_t)bi * p.Hkv + kvh) * p.seq_len + si) * kD + vec * 8) = x;
     }
 }
 
@@ -259,7 +280,7 @@ extern "C" int tm_add_fused_qkv_bias_transpose(void* q_buf, void* k_buf, void* v
     QkvParams p{(__half*)q_buf, (__half*)k_buf, (__half*)v_buf, (const __half*)QKV, (const __half*)qkv_bias, padding_offset,
                 history_length, input_length, seq_len, head_num, kv_head_num, rotary_embedding_dim, rotary_embedding_base,
                 max_position_embeddings, use_dynamic_ntk, use_logn_attn};
-    const dim3 grid(token_num, (head_num + 2 * kv_head_num + kHeadsPerCta - 1) / kHeadsPerCta);
+    const dim3 grid(token_num);
     return status_of(launch_kernel(qkv_bias_rope_transpose_kernel, grid, dim3(kQkvThreads), 0, (cudaStream_t)stream, false, p));
 }
 

@@ -93,7 +93,7 @@ def _near_fp16(got, want, what, abs_tol=1e-6):
 
 QKV_CASES = [
     dict(lengths=[24, 7, 15], history=[0, 5, 100], seq_len=24, H=4, Hkv=2, kw={}),
-    dict(lengths=[3, 1], history=[0, 9], seq_len=3, H=40, Hkv=40, kw={}, bias=False),                 # 120 heads: 8 CTAs per token
+    dict(lengths=[3, 1], history=[0, 9], seq_len=3, H=40, Hkv=40, kw={}, bias=False),                 # 120 heads: two passes of 64 per CTA
     # dynamic NTK + log-n at positions ~2000: the angle is position / powf(base', .), so one fp32 rounding of the
     # rescaled base moves it by ~2e-4 rad; against the CPU oracle (numpy's pow / log2) that is an absolute 4e-3
     dict(lengths=[16, 9], history=[60, 2000], seq_len=16, H=8, Hkv=1, kw=dict(max_pos=64, ntk=True, logn=True), abs_tol=4e-3),
