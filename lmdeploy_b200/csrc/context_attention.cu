@@ -218,14 +218,19 @@ __global__ void __launch_bounds__(kThreads) context_attention_kernel(CtxParams p
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        {
+            // one ldmatrix.x4 = the B fragments of two key groups for one k-step, fetched one step ahead of the two
+            // (independent) MMAs that use them
+            const int m      = lane >> 3;
+            auto      k_addr = [&](int i) { return k_s + tile_off((2 * (i & 3) + (m >> 1)) * 8 + (lane & 7), 2 * (i >> 2) + (m & 1)); };
+            uint32_t  b[2][4];
+            ldsm_x4(b[0], k_addr(0));
 #pragma unroll
-        for (int kk2 = 0; kk2 < 4; ++kk2) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint32_t b[4];
-                ldsm_x4(b, k_s + tile_off(j * 8 + (lane & 7), 4 * kk2 + (lane >> 3)));
-                mma_m16n8k16(s[j], qf[2 * kk2], b[0], b[1]);
-                mma_m16n8k16(s[j], qf[2 * kk2 + 1], b[2], b[3]);
+            for (int i = 0; i < 32; ++i) {
+                if (i + 1 < 32) ldsm_x4(b[(i + 1) & 1], k_addr(i + 1));
+                const int kk = i >> 2, jp = i & 3;
+                mma_m16n8k16(s[2 * jp], qf[kk], b[i & 1][0], b[i & 1][1]);
+                mma_m16n8k16(s[2 * jp + 1], qf[kk], b[i & 1][2], b[i & 1][3]);
             }
         }
         // ---- causal mask (only tiles that reach the diagonal of this warp's rows)
@@ -274,15 +279,17 @@ __global__ void __launch_bounds__(kThreads) context_attention_kernel(CtxParams p
             o[i][2] *= corr[1], o[i][3] *= corr[1];
         }
         // ---- o += p v
+        {
+            const int m      = lane >> 3;
+            auto      v_addr = [&](int i) { return v_s + tile_off((i >> 3) * 16 + (m & 1) * 8 + (lane & 7), 2 * (i & 7) + (m >> 1)); };
+            uint32_t  b[2][4];
+            ldsm_x4_trans(b[0], v_addr(0));
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-#pragma unroll
-            for (int dn2 = 0; dn2 < 8; ++dn2) {
-                uint32_t  b[4];
-                const int m = lane >> 3;
-                ldsm_x4_trans(b, v_s + tile_off(kb * 16 + (m & 1) * 8 + (lane & 7), 2 * dn2 + (m >> 1)));
-                mma_m16n8k16(o[2 * dn2], pa[kb], b[0], b[1]);
-                mma_m16n8k16(o[2 * dn2 + 1], pa[kb], b[2], b[3]);
+            for (int i = 0; i < 32; ++i) {
+                if (i + 1 < 32) ldsm_x4_trans(b[(i + 1) & 1], v_addr(i + 1));
+                const int kb = i >> 3, dn2 = i & 7;
+                mma_m16n8k16(o[2 * dn2], pa[kb], b[i & 1][0], b[i & 1][1]);
+                mma_m16n8k16(o[2 * dn2 + 1], pa[kb], b[i & 1][2], b[i & 1][3]);
             }
         }
         if (t + 1 < n_tiles) {
