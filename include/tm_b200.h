@@ -325,6 +325,28 @@ TM_API int tm_llama_set_globals(tm_llama* m, const void* tok_embeddings, const v
  * missing or its size does not match the configuration. */
 TM_API int tm_llama_load_workspace(tm_llama* m, const char* dir);
 
+/* Prefill: runs the new tokens of `batch_size` sequences (packed, `token_num` in all) through every layer and
+ * leaves their keys / values in the cache — what LlamaContextDecoder<T>::forward
+ * (src/turbomind/models/llama/LlamaContextDecoder.cc:173-290) does around
+ * LlamaContextAttentionLayer<T>::forward (LlamaContextAttentionLayer.cc:119-247), int4 weights.  The reference
+ * discards the last layer's output (LlamaV2::contextDecode, LlamaV2.cc:204: the prompt's last token goes
+ * through the decoder step instead); `hidden_out` (may be NULL) receives it after the final norm for tests.
+ * All pointers are device memory of the caller; activations live in the model and grow to the largest call.
+ * Not captured into a CUDA graph (shapes change per call); asynchronous on `stream`. */
+typedef struct tm_llama_prefill_state {
+    int        batch_size;
+    int        token_num;        /* sum of the new-token counts                                   */
+    int        max_q_len;        /* largest new-token count                                       */
+    const int* input_ids;        /* [token_num], packed sequence after sequence                   */
+    const int* cu_seqlens;       /* [batch + 1] prefix sums of the new-token counts               */
+    const int* history_lengths;  /* [batch] tokens already cached per sequence                    */
+    const int* context_lengths;  /* [batch] history + new                                         */
+    void**     k_cache_ptrs;     /* as in tm_llama_decode_state                                   */
+    void**     v_cache_ptrs;
+    void*      hidden_out;       /* optional half [token_num, hidden]                             */
+} tm_llama_prefill_state;
+TM_API int tm_llama_prefill(tm_llama* m, const tm_llama_prefill_state* st, void* stream);
+
 /* Decode state, all device memory owned by the caller:
  *   k_cache_ptrs/v_cache_ptrs  [batch] base pointers; sequence b's cache is
  *                              [num_layer][kv_head_num / tp][session_len][128]

@@ -370,6 +370,10 @@ extern "C" int tm_llama_destroy(tm_llama* m)
         if (p) cudaFree(p);
     }
     for (void* p : m->owned) cudaFree(p);
+    for (void* p : {(void*)m->prefill.x, (void*)m->prefill.h, (void*)m->prefill.qkv, (void*)m->prefill.q, (void*)m->prefill.k,
+                    (void*)m->prefill.v, (void*)m->prefill.ctx, (void*)m->prefill.ffn, (void*)m->prefill.pad, (void*)m->prefill.len}) {
+        if (p) cudaFree(p);
+    }
     delete m;
     return TM_OK;
 }

@@ -66,6 +66,14 @@ struct tm_llama {
     int*    order = nullptr;  // sequences by cached length, longest first (attention launch order)
     unsigned char* inactive = nullptr;
 
+    // activations of tm_llama_prefill, sized by the largest call so far
+    struct PrefillBuffers {
+        __half *x = nullptr, *h = nullptr, *qkv = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ctx = nullptr, *ffn = nullptr;
+        int *   pad = nullptr, *len = nullptr;
+        size_t  x_bytes = 0, h_bytes = 0, qkv_bytes = 0, q_bytes = 0, k_bytes = 0, v_bytes = 0, ctx_bytes = 0, ffn_bytes = 0,
+               pad_bytes = 0, len_bytes = 0;
+    } prefill;
+
     cublasHandle_t cublas    = nullptr;
     void*          cublas_ws = nullptr;
 

@@ -90,6 +90,13 @@ class TmLlamaDecodeState(C.Structure):
                 ("hidden_out", C.c_void_p), ("logits_out", C.c_void_p)]
 
 
+class TmLlamaPrefillState(C.Structure):
+    """ctypes mirror of ``tm_llama_prefill_state``."""
+    _fields_ = [("batch_size", C.c_int), ("token_num", C.c_int), ("max_q_len", C.c_int), ("input_ids", C.c_void_p),
+                ("cu_seqlens", C.c_void_p), ("history_lengths", C.c_void_p), ("context_lengths", C.c_void_p),
+                ("k_cache_ptrs", C.c_void_p), ("v_cache_ptrs", C.c_void_p), ("hidden_out", C.c_void_p)]
+
+
 # name -> (restype, argtypes); must list every symbol declared in include/tm_b200.h
 SIGNATURES = {
     "tm_create": (_i, [C.POINTER(_vp), _i]),
@@ -120,6 +127,7 @@ SIGNATURES = {
     "tm_llama_load_workspace": (_i, [_vp, C.c_char_p]),
     "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
+    "tm_llama_prefill": (_i, [_vp, C.POINTER(TmLlamaPrefillState), _vp]),
     "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_fused_qkv_bias_transpose": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,

@@ -174,6 +174,32 @@ class LlamaModel:
         st = torch.cuda.current_stream().cuda_stream if stream is None else stream
         _l.check(_l.lib.tm_llama_decode(self._m, C.byref(state.c), n_steps, int(use_graph), st), "tm_llama_decode")
 
+    def prefill(self, state: "DecodeState", new_tokens, keep_hidden: bool = False, stream=None):
+        """tm_llama_prefill: run ``new_tokens[b]`` (a list of ids per sequence, possibly empty) through all layers on top
+        of the ``state.lengths[b]`` tokens already cached, leave their keys / values in the state's cache and advance
+        ``state.lengths``.  Returns the normed last-layer output [token_num, hidden] when ``keep_hidden``."""
+        import numpy as np
+        dev = torch.device("cuda", self.device)
+        lens = np.asarray([len(t) for t in new_tokens], np.int32)
+        assert len(lens) == state.c.batch_size
+        token_num, max_q = int(lens.sum()), int(lens.max(initial=0))
+        ids = torch.tensor([i for t in new_tokens for i in t], dtype=torch.int32, device=dev)
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+        hist = state.lengths.clone()
+        ctx = hist + torch.from_numpy(lens).to(dev)
+        hidden = torch.zeros((token_num, self.cfg.hidden), dtype=torch.float16, device=dev) if keep_hidden else None
+        c = _l.TmLlamaPrefillState()
+        c.batch_size, c.token_num, c.max_q_len = len(lens), token_num, max_q
+        c.input_ids, c.cu_seqlens = ids.data_ptr(), cu.data_ptr()
+        c.history_lengths, c.context_lengths = hist.data_ptr(), ctx.data_ptr()
+        c.k_cache_ptrs, c.v_cache_ptrs = state.k_ptrs.data_ptr(), state.v_ptrs.data_ptr()
+        c.hidden_out = 0 if hidden is None else hidden.data_ptr()
+        st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        _l.check(_l.lib.tm_llama_prefill(self._m, C.byref(c), st), "tm_llama_prefill")
+        state.lengths.copy_(ctx)
+        torch.cuda.current_stream().synchronize()   # ids / cu / hist / ctx are released when this returns
+        return hidden
+
     def last_launches(self) -> int:
         return int(_l.lib.tm_llama_last_launches(self._m))
 
