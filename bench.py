@@ -10,6 +10,7 @@ Workloads (``config.workload``):
   mmha      decode attention, batch 64, KV length uniform in ``--kv-len``, int8 or fp16 cache.
   prefill   attention side of one prefill layer (QKV bias + RoPE + transpose, KV-cache extend, causal attention
             over the cache) for ``--batch`` (default 8) sequences of 2048 new tokens.
+  prefill7b whole-model prefill of Llama-2-7B through tm_llama_prefill, ``--batch`` (default 8) prompts of 2048 tokens.
   decode    (default) whole-model greedy decode, Llama-2-7B at 1 GPU, Llama-2-70B tensor-parallel at N > 1.
 
 The timed region is bracketed by a barrier + ``torch.cuda.synchronize()``; device time comes from
@@ -499,6 +500,70 @@ def run_prefill_workload(args, rank, world, device):
     return res
 
 
+def run_prefill_model_workload(args, rank, world, device):
+    """Whole-model prefill of a random-init Llama-2-7B (W4A16, ``--kv`` cache) through tm_llama_prefill: ``--batch``
+    (default 8) prompts of 2048 tokens per step, every step into an empty cache.  Tensor-bound: the four W4A16 GEMMs of
+    each layer at 16384 tokens (tcgen05 kernel) and the causal attention."""
+    from lmdeploy_b200 import llama
+    torch.cuda.set_device(device)
+    import dataclasses
+    B = args.batch if args.batch != 64 else 8
+    S = 2048
+    cfg = llama.LLAMA2_7B
+    cfg = dataclasses.replace(cfg, quant_policy=4 if args.kv == "int8" else 0)
+    session_len = S + 64
+    model = llama.LlamaModel(cfg, B, session_len, device, None)
+    model.random_init(seed=0)
+    rng = np.random.default_rng(77 + rank)
+    prompts = [list(rng.integers(0, cfg.vocab_size, size=S)) for _ in range(B)]
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        st = model.new_state(B, 1, np.zeros(B, np.int32), None)
+        for _ in range(args.warmup):
+            st.lengths.zero_()
+            model.prefill(st, prompts)
+        model.handle.check_device_status(stream.cuda_stream)
+        barrier(world)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(device)
+        sampler.start()
+        total = 0.0
+        for _ in range(args.steps):   # the wrapper uploads ids and synchronises per call: device time per call, summed
+            st.lengths.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            model.prefill(st, prompts)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        barrier(world)
+        ms = total / args.steps
+        clocks = sampler.stop()
+        model.handle.check_device_status(stream.cuda_stream)
+        assert int(st.lengths.min().item()) == S
+    ms = max_over_ranks(ms, world)
+    peaks = measured_peaks()
+    T = B * S
+    hid, inter, H, L = cfg.hidden, cfg.inter_size, cfg.head_num, cfg.num_layer
+    gemm_flops = 2.0 * T * (hid * (cfg.head_num + 2 * cfg.kv_head_num) * 128 + hid * hid + 2 * hid * inter + inter * hid) * L
+    attn_flops = 4.0 * 128 * H * B * (S * (S + 1) / 2) * L
+    tf = (gemm_flops + attn_flops) / (ms * 1e-3) * 1e-12
+    return {
+        "metric": "prefill tokens/s (Llama-2-7B W4A16, whole model)", "value": round(T * world / (ms * 1e-3), 1), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": f"f16 activations, int4 weights, {args.kv} KV, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "prefill7b", "batch": B, "prompt_tokens": S, "kv": args.kv,
+                   "l2": "inputs larger than L2 (activations of 16384 tokens: 0.13 GB per [tokens, hidden] buffer)",
+                   "parallelism": "replicas only" if world > 1 else "single GPU"},
+        "roofline": {"bound": "tensor", "kernel": "whole prefill (W4A16 GEMMs at 16384 tokens + causal attention)",
+                     "achieved": round(tf, 1), "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": round(tf / peaks["bf16_tflops_sustained"], 4), "peak_source": peaks["source"],
+                     "algorithmic_flops": gemm_flops + attn_flops, "traffic": None},
+        "clocks": clocks, "gpu_launches": args.steps * (3 + 10 * L),
+    }
+
+
 DECODE_WORKLOADS = {
     # name: (config attr, batch, prompt_lo, prompt_hi, new_tokens)
     "decode7b": ("LLAMA2_7B", 64, 128, 1024, 256),
@@ -803,7 +868,7 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="decode",
-                    help="decode (7B at 1 GPU, 70B tensor-parallel at N > 1) | decode7b | decode70b | gemm | mmha | prefill")
+                    help="decode (7B at 1 GPU, 70B tensor-parallel at N > 1) | decode7b | decode70b | gemm | mmha | prefill | prefill7b")
     ap.add_argument("--batch-override", type=int, default=0, help="smaller batch for smoke runs")
     ap.add_argument("--max-prompt", type=int, default=0, help="cap on the prompt length for smoke runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -843,6 +908,8 @@ def main():
         out = run_mmha_workload(args, rank, world, local)
     elif args.workload == "prefill":
         out = run_prefill_workload(args, rank, world, local)
+    elif args.workload == "prefill7b":
+        out = run_prefill_model_workload(args, rank, world, local)
     else:
         raise SystemExit(f"unknown workload {args.workload}")
     if rank == 0:
