@@ -80,12 +80,19 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b)
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-// 4 int8 -> 4 halves, half(q * scale + zp) with one fp32 fused multiply-add (llama_kernels.cu:309-316)
+// 4 int8 -> 4 halves, half(q * scale + zp) with one fp32 fused multiply-add (llama_kernels.cu:309-316).  The
+// integer -> float step avoids the conversion unit (a quarter-rate pipe shared with ex2): byte q + 128 is dropped into
+// the mantissa of 2^23, and 2^23 + 128 subtracted again — exact, so the result is the same float as (float)q.
 __device__ __forceinline__ uint2 dequant4(uint32_t w, float scale, float zp)
 {
+    const uint32_t u = w ^ 0x80808080u;
+    const float    f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.f;
+    const float    f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.f;
+    const float    f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.f;
+    const float    f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.f;
     uint2 r;
-    r.x = pack_half2(__fmaf_rn((float)(int8_t)(w), scale, zp), __fmaf_rn((float)(int8_t)(w >> 8), scale, zp));
-    r.y = pack_half2(__fmaf_rn((float)(int8_t)(w >> 16), scale, zp), __fmaf_rn((float)(int8_t)(w >> 24), scale, zp));
+    r.x = pack_half2(__fmaf_rn(f0, scale, zp), __fmaf_rn(f1, scale, zp));
+    r.y = pack_half2(__fmaf_rn(f2, scale, zp), __fmaf_rn(f3, scale, zp));
     return r;
 }
 
