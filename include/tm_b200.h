@@ -325,6 +325,40 @@ TM_API int tm_llama_set_globals(tm_llama* m, const void* tok_embeddings, const v
  * missing or its size does not match the configuration. */
 TM_API int tm_llama_load_workspace(tm_llama* m, const char* dir);
 
+/* ------------------------------------------------------------------------------------------
+ * KV slab manager: sequence id -> cache slab with least-recently-used eviction.  Replaces LlamaCacheManager
+ *   (src/turbomind/models/llama/LlamaCacheManager.h:13-100, LlamaCacheManager.cc:16-183): create / fetch /
+ *   update / erase / contains with the same policy.  A slab holds keys then values of one sequence,
+ *   2 x layer_num x head_num x max_seq_len x size_per_head x elem_bits / 8 bytes; slabs come from chunks of
+ *   `chunk_size` slabs allocated on demand up to `max_entry_count` (the first chunk at creation).  fetch / create
+ *   pin the sequence (timestamp = UINT64_MAX); update stamps it and makes it evictable; when no slab is free the
+ *   sequence with the smallest stamp loses its slab and its cache_len becomes 0.
+ *   Errors: unknown id -> TM_ERR_INVALID_ARG (the reference aborts); every slab pinned -> TM_ERR_WORKSPACE
+ *   ("No enough cache entries."); allocation failure -> TM_ERR_CUDA.
+ *   device >= 0: slabs in that GPU's memory, zero-filled with cudaMemsetAsync on `stream`;
+ *   device == -1: slabs in host memory (for tests of the policy without a GPU).
+ *   One manager is used by one host thread at a time, like a handle.
+ */
+typedef struct tm_cache_manager tm_cache_manager;
+typedef struct tm_cache_sequence { /* LlamaCacheManager::Sequence, LlamaCacheManager.h:45-61 */
+    uint64_t id;
+    size_t   max_seq_len;
+    size_t   cache_len;    /* 0 = cache miss                                              */
+    size_t   token_count;  /* tokens stored by the last update (read them with tm_cache_tokens) */
+    void*    k_cache;
+    void*    v_cache;
+    uint64_t timestamp;
+} tm_cache_sequence;
+TM_API int tm_cache_manager_create(tm_cache_manager** out, size_t layer_num, size_t head_num, size_t size_per_head,
+                                   size_t max_seq_len, size_t elem_bits, size_t max_entry_count, size_t chunk_size, int device);
+TM_API int tm_cache_manager_destroy(tm_cache_manager* m);
+TM_API int tm_cache_create(tm_cache_manager* m, uint64_t id, void* stream, tm_cache_sequence* out);
+TM_API int tm_cache_fetch(tm_cache_manager* m, uint64_t id, void* stream, tm_cache_sequence* out);
+TM_API int tm_cache_update(tm_cache_manager* m, const tm_cache_sequence* seq, const int* token_ids, size_t token_count);
+TM_API int tm_cache_tokens(const tm_cache_manager* m, uint64_t id, int* token_ids, size_t capacity, size_t* token_count);
+TM_API int tm_cache_erase(tm_cache_manager* m, uint64_t id);
+TM_API int tm_cache_contains(const tm_cache_manager* m, uint64_t id);
+
 /* Prefill: runs the new tokens of `batch_size` sequences (packed, `token_num` in all) through every layer and
  * leaves their keys / values in the cache — what LlamaContextDecoder<T>::forward
  * (src/turbomind/models/llama/LlamaContextDecoder.cc:173-290) does around

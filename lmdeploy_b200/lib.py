@@ -28,7 +28,24 @@ class TmError(RuntimeError):
         super().__init__(f"{where}: {status_string(status)} ({status})")
 
 
+def _preload_bundled_nccl() -> None:
+    """One NCCL per process: when PyTorch's wheel ships its own libnccl.so.2 (nvidia.nccl), load that one before this
+    library, whose NCCL dependency would otherwise bind the system copy under the same soname and leave a later
+    ``import torch`` with an NCCL that lacks symbols it needs."""
+    import importlib.util
+    try:
+        spec = importlib.util.find_spec("nvidia.nccl")
+    except (ImportError, ValueError):
+        spec = None
+    for d in (list(spec.submodule_search_locations) if spec and spec.submodule_search_locations else []):
+        path = os.path.join(d, "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            C.CDLL(path, mode=C.RTLD_GLOBAL)
+            return
+
+
 def _load() -> C.CDLL:
+    _preload_bundled_nccl()
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing: build it with `python -m lmdeploy_b200.build` "
@@ -90,6 +107,12 @@ class TmLlamaDecodeState(C.Structure):
                 ("hidden_out", C.c_void_p), ("logits_out", C.c_void_p)]
 
 
+class TmCacheSequence(C.Structure):
+    """ctypes mirror of ``tm_cache_sequence``."""
+    _fields_ = [("id", C.c_uint64), ("max_seq_len", C.c_size_t), ("cache_len", C.c_size_t), ("token_count", C.c_size_t),
+                ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("timestamp", C.c_uint64)]
+
+
 class TmLlamaPrefillState(C.Structure):
     """ctypes mirror of ``tm_llama_prefill_state``."""
     _fields_ = [("batch_size", C.c_int), ("token_num", C.c_int), ("max_q_len", C.c_int), ("input_ids", C.c_void_p),
@@ -127,6 +150,14 @@ SIGNATURES = {
     "tm_llama_load_workspace": (_i, [_vp, C.c_char_p]),
     "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
+    "tm_cache_manager_create": (_i, [C.POINTER(_vp), _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i]),
+    "tm_cache_manager_destroy": (_i, [_vp]),
+    "tm_cache_create": (_i, [_vp, C.c_uint64, _vp, C.POINTER(TmCacheSequence)]),
+    "tm_cache_fetch": (_i, [_vp, C.c_uint64, _vp, C.POINTER(TmCacheSequence)]),
+    "tm_cache_update": (_i, [_vp, C.POINTER(TmCacheSequence), C.POINTER(C.c_int), _sz]),
+    "tm_cache_tokens": (_i, [_vp, C.c_uint64, C.POINTER(C.c_int), _sz, C.POINTER(_sz)]),
+    "tm_cache_erase": (_i, [_vp, C.c_uint64]),
+    "tm_cache_contains": (_i, [_vp, C.c_uint64]),
     "tm_llama_prefill": (_i, [_vp, C.POINTER(TmLlamaPrefillState), _vp]),
     "tm_rmsnorm": (_i, [_vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
