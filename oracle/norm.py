@@ -8,9 +8,9 @@ TEST INFRASTRUCTURE.  Follows
   normalisation applied to the stored fp16 residual; ops at :41-63)
 
 The fused residual-add form is pinned against the reference kernel's outputs on a B200
-(tests/golden/ref_kernel_vectors.npz, tests/test_gpu_reference_kernels.py); the plain form is a
-restatement only (parity unpinned: its reference file does not link without the reference's
-flash-attention sources).
+(tests/golden/ref_kernel_vectors.npz, tests/test_gpu_reference_kernels.py); the plain form is pinned
+against the reference kernel run beside it (tests/test_gpu_reference_kernels.py,
+test_rmsnorm_matches_reference_kernel).
 """
 from __future__ import annotations
 

@@ -1,12 +1,16 @@
-"""CPU restatement (numpy) of the reference's prefill-side writers around the KV cache, lmdeploy v0.0.9.
+"""CPU restatement (numpy) of the reference's prefill-side writers around the KV cache and of its context attention,
+lmdeploy v0.0.9.
 
 Test infrastructure only: nothing under lmdeploy_b200/ imports this module.  Pinned against the
 reference kernels themselves (oracle/_ref, built from the reference sources where they lie) by
-tests/test_gpu_prefill.py, and against vectors those kernels produced (tests/golden).
+tests/test_gpu_prefill.py, and against vectors those kernels produced (tests/golden/ref_prefill_vectors.npz,
+tests/test_oracle_prefill_vectors.py).  Context attention is pinned against the reference's unfused route (its cache
+transpose, mask and softmax kernels, GEMMs by cuBLAS); its flash-attention kernel needs CUTLASS and is not built.
 
   add_fused_qkv_bias_transpose  src/turbomind/kernels/unfused_attention_kernels.cu:852-976
   extend_kv_cache               src/turbomind/models/llama/llama_kernels.cu:245-464
   transpose_kv_cache            src/turbomind/models/llama/llama_kernels.cu:497-660
+  context_attention             src/turbomind/models/llama/LlamaContextAttentionLayer.cc:257-420
 """
 from __future__ import annotations
 
