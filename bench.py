@@ -888,6 +888,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and args.workload == "prefill7b":
+        if rank == 0:   # the reference's prefill needs its engine and its flash-attention build (CUTLASS): neither is built
+            print(json.dumps({"impl": "reference", "unavailable": "whole-model prefill of the reference needs its engine and "
+                              "CUTLASS flash attention; use --workload prefill for its kernels"}), flush=True)
+        return
     if args.impl == "reference" and args.workload not in ("gemm", "mmha", "prefill"):
         # whole-model workloads: the reference's CPU path (the engine around its kernels is out of scope)
         out = run_reference_arm(args, rank, world)
