@@ -33,7 +33,7 @@ struct QkvParams {
     const int*    padding_offset;
     const int*    history_length;
     const int*    input_length;
-    int           seq_len;
+    int           batch, seq_len;
     int           H, Hkv;
     int           rot_dim;
     float         rope_base;
@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(kQkvThreads) qkv_bias_rope_transpose_kernel(Qk
     const int tgt  = token + (p.padding_offset ? p.padding_offset[token] : 0);  // :877-878
     const int bi   = tgt / p.seq_len;
     const int si   = tgt % p.seq_len;
+    if (tgt < 0 || bi >= p.batch) return;  // a padding offset that points outside [batch, seq_len]: nothing is written
     const int hist = p.history_length[bi];
     const int step = hist + si;  // :929
     if (threadIdx.x < kD / 2) {
@@ -196,6 +197,7 @@ __global__ void __launch_bounds__(kCacheThreads) extend_kv_cache_kernel(CachePar
     const int  vec  = idx % kVecPerHead;
     const int  row  = idx / kVecPerHead;
     if (row >= p.length[bi]) return;
+    if (row + p.history[bi] >= p.max_seq_len) return;  // never past the rows a cache head holds
     const __half* src  = (is_v ? p.v_lin : p.k_lin) + (((size_t)bi * p.Hkv + hi) * p.max_len + row) * kD + vec * 8;
     const uint4   x    = *reinterpret_cast<const uint4*>(src);
     const size_t  dsti = p.offset + ((size_t)hi * p.max_seq_len + row + p.history[bi]) * kD + vec * 8;
@@ -278,7 +280,7 @@ extern "C" int tm_add_fused_qkv_bias_transpose(void* q_buf, void* k_buf, void* v
     if (!aligned16({q_buf, k_buf, v_buf, QKV, qkv_bias})) return TM_ERR_INVALID_ARG;
     if (token_num == 0 || batch_size == 0) return TM_OK;
     QkvParams p{(__half*)q_buf, (__half*)k_buf, (__half*)v_buf, (const __half*)QKV, (const __half*)qkv_bias, padding_offset,
-                history_length, input_length, seq_len, head_num, kv_head_num, rotary_embedding_dim, rotary_embedding_base,
+                history_length, input_length, batch_size, seq_len, head_num, kv_head_num, rotary_embedding_dim, rotary_embedding_base,
                 max_position_embeddings, use_dynamic_ntk, use_logn_attn};
     const dim3 grid(token_num);
     return status_of(launch_kernel(qkv_bias_rope_transpose_kernel, grid, dim3(kQkvThreads), 0, (cudaStream_t)stream, false, p));

@@ -375,3 +375,19 @@ def test_context_attention_properties_at_full_size():
     last[(cu[1:] - 1).long()] = True
     assert torch.equal(a[~last], b2[~last])
     assert not torch.equal(a[last], b2[last])
+
+
+def test_writers_never_leave_their_buffers():
+    """More new tokens than a cache head has rows left: the surplus rows are dropped, the next head's rows stay as they
+    were; a padding offset that points past the batch writes nothing."""
+    from lmdeploy_b200 import turbomind as tm
+    c = cache_case(B=1, Hkv=2, layers=1, layer=0, S_max=16, max_q=8, q_len=[8], hist=[12], seed=31, int8=False)
+    kd, vd, kp, vp = _cache_tensors(c)
+    tm.invokeExtendKVCache(kp, vp, 0, dev(c["k_src"]), dev(c["v_src"]), 1, dev(c["q_len"]), 8, dev(c["hist"]), 16, D, 2)
+    torch.cuda.synchronize()
+    got = kd[0].cpu().numpy().reshape(2, 16, D)
+    assert np.array_equal(got[:, 12:], c["k_src"][0, :, :4]) and np.array_equal(got[:, :12], c["kc"][0][:, :12])
+    case = qkv_case([4], [0], 4, 2, 1, 33)
+    case["pad"] = np.asarray([0, 0, 100, -50], np.int32)          # tokens 2 and 3 point outside [1, 4]
+    q, k, v = run_qkv(case, "ours", None)
+    assert q[0, :, :2].any() and not q[0, :, 2:].any() and not k[0, :, 2:].any() and not v[0, :, 2:].any()
