@@ -56,7 +56,9 @@ extern "C" int tm_create(tm_handle** out, int device)
         h->max_smem = (int)prop.sharedMemPerBlockOptin;
         h->l2_bytes = prop.l2CacheSize;
         // scratch: split-K partial tiles + self-resetting tickets, status word
-        h->scratch_bytes = 256u << 20;
+        // TM_B200_GEMM_SCRATCH_MB: more scratch lets one launch of the many-token GEMM cover more tokens (prefill)
+        const int scratch_mb = env_int("TM_B200_GEMM_SCRATCH_MB", 256);
+        h->scratch_bytes = (size_t)(scratch_mb < 64 ? 64 : (scratch_mb > 16384 ? 16384 : scratch_mb)) << 20;
         h->counter_ints  = 1u << 16;
         e                = cudaMalloc(&h->scratch, h->scratch_bytes);
     }
