@@ -75,7 +75,6 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_small_prepare(h->max_smem);
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    h->gemv_dev_mode = env_int("TM_B200_GEMV_DEV_MODE", 0);
     h->pdl           = env_int("TM_B200_PDL", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
@@ -127,6 +126,11 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     else if (n == "pdl" && (value == 0 || value == 1)) {
         h->pdl = value;
     }
+    else if (n == "gemm_wait_cycles" && value >= 0) {
+        // bound, in SM clock cycles, of the tcgen05 GEMM's wait for the partners of a split column tile
+        // (0 = the default of about a quarter of a second); tests set a tiny value to see the time-out path
+        h->gemm_wait_cycles = value;
+    }
     else {
         return TM_ERR_INVALID_ARG;
     }
@@ -161,7 +165,7 @@ extern "C" size_t tm_gemm_s4_f16_workspace_bytes(int m, int n, int k)
     GemmSmallPlan pl = gemm_small_plan(m, n, k, 256, 227 * 1024);
     size_t        b  = pl.workspace_floats * sizeof(float) + pl.counter_ints * sizeof(int) + 256;
     if (n > 16) {
-        GemmTcPlan   tc = gemm_tc_plan(m, n < 128 ? n : 128, k, 256);
+        GemmTcPlan   tc = gemm_tc_plan(m, n, k, 256);
         const size_t t  = tc.workspace_floats * sizeof(float) + tc.counter_ints * sizeof(int) + 256;
         if (t > b) b = t;
     }
@@ -219,6 +223,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.T          = nt;
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
+            p.max_wait_cycles = h->gemm_wait_cycles;
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
             h->launches += 1;
             if (e != cudaSuccess) {
@@ -271,7 +276,6 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
         p.T          = nt;
         p.K          = k;
         p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
-        p.dev_mode   = h->gemv_dev_mode;
 
         cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
         h->launches += 1;

@@ -1,5 +1,5 @@
-// Shared device helpers for the sm_100a kernels: mbarrier + bulk-copy (TMA) wrappers with
-// bounded waits, warp-level MMA, and the device status word.
+// Shared device helpers for the sm_100a kernels: mbarrier wrappers with bounded waits, warp-level
+// MMA, programmatic dependent launch, and the device status word.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -11,11 +11,8 @@ namespace tmb {
 // Bits of the device status word (one unsigned per handle).  A kernel that gives up on a
 // bounded wait ORs its bit in and finishes without touching its output any further.
 enum : unsigned {
-    kStatusGemvFullWait  = 1u << 0,
-    kStatusGemvEmptyWait = 1u << 1,
-    kStatusGemmPipeWait  = 1u << 2,
-    kStatusGemmTmemWait  = 1u << 3,
-    kStatusMmhaPipeWait  = 1u << 4,
+    kStatusGemmPipeWait  = 1u << 2,  // tcgen05 GEMM: a pipeline barrier (copies, expanded weight, MMA completion)
+    kStatusGemmTmemWait  = 1u << 3,  // tcgen05 GEMM: accumulator hand-over or the partners of a split tile
 };
 
 // Upper bound, in SM clock cycles, on one mbarrier wait (about 0.15-0.3 s): far above any
@@ -35,11 +32,6 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 __device__ __forceinline__ void fence_mbar_init()
 {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async_smem()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
@@ -80,45 +72,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
         }
     }
     return true;
-}
-
-// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
-// dst, src 16-byte aligned; bytes a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src),
-                 "r"(bytes),
-                 "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// Same, with an L2 eviction-priority hint created by createpolicy.
-__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t pol)
-{
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
-            "r"(smem_u32(dst)),
-        "l"(src),
-        "r"(bytes),
-        "r"(smem_u32(bar)),
-        "l"(pol)
-        : "memory");
-}
-
-__device__ __forceinline__ uint64_t policy_evict_first()
-{
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-
-__device__ __forceinline__ uint64_t policy_evict_last()
-{
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
 }
 
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may

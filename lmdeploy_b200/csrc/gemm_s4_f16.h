@@ -19,7 +19,6 @@ struct GemmSmallParams {
     unsigned*            status;
     int                  N, T, K;
     int                  fused_silu;
-    int                  dev_mode;  // developer experiments (TM_B200_GEMV_DEV_MODE): 1 no unpack/MMA, 2 no publish
     // filled in by gemm_small_launch from the plan
     int units_per_cta, total_units, slots_per_chunk, n_col_tiles, stages;
 };
@@ -55,7 +54,8 @@ struct GemmTcParams {
     int                  N, T, K;
     int                  fused_silu;
     // filled in by gemm_tc_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, a_stages, acc_stride;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, acc_stride;
+    long long max_wait_cycles;  // bound of the wait for the partners of a split tile; 0 = the default
 };
 
 struct GemmTcPlan {

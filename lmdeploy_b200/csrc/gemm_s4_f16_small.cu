@@ -258,49 +258,47 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
                     }
                 }
             }
-            if (!(p.dev_mode & 1)) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const bool fresh = (u == 0 && h == 0);  // first slab of the group: accumulators start at zero
-                    uint32_t   bf[NT][4];
+            for (int h = 0; h < 2; ++h) {
+                const bool fresh = (u == 0 && h == 0);  // first slab of the group: accumulators start at zero
+                uint32_t   bf[NT][4];
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) load_x_frag(bf[j], x_lane + s * kXUnit + h * kXSlab + j * 512);
-                    // group sums of the activations, in the accumulator layout (every row alike)
+                for (int j = 0; j < NT; ++j) load_x_frag(bf[j], x_lane + s * kXUnit + h * kXSlab + j * 512);
+                // group sums of the activations, in the accumulator layout (every row alike)
 #pragma unroll
-                    for (int j = 0; j < NT; ++j) {
-                        if (fresh) {
-                            mma_m16n8k16_init(sx[j], ones, bf[j][0], bf[j][1]);
-                        }
-                        else {
-                            mma_m16n8k16(sx[j], ones, bf[j][0], bf[j][1]);
-                        }
-                        mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
+                for (int j = 0; j < NT; ++j) {
+                    if (fresh) {
+                        mma_m16n8k16_init(sx[j], ones, bf[j][0], bf[j][1]);
                     }
-                    // all eight fragments of the slab first (independent chains the scheduler can
-                    // interleave), then the MMAs, k halves outermost so that back-to-back MMAs hit
-                    // different accumulators
-                    uint32_t af[kTilesPerWarp][4][4];
+                    else {
+                        mma_m16n8k16(sx[j], ones, bf[j][0], bf[j][1]);
+                    }
+                    mma_m16n8k16(sx[j], ones, bf[j][2], bf[j][3]);
+                }
+                // all eight fragments of the slab first (independent chains the scheduler can
+                // interleave), then the MMAs, k halves outermost so that back-to-back MMAs hit
+                // different accumulators
+                uint32_t af[kTilesPerWarp][4][4];
+#pragma unroll
+                for (int w = 0; w < kTilesPerWarp; ++w) {
+                    const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes);
+                    const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+                    for (int wi = 0; wi < 4; ++wi) unpack_s4_biased(wv[wi], af[w][wi]);
+                }
+#pragma unroll
+                for (int k16 = 0; k16 < 2; ++k16) {
 #pragma unroll
                     for (int w = 0; w < kTilesPerWarp; ++w) {
-                        const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * kSlabBytes + w * kTileBytes);
-                        const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) unpack_s4_biased(wv[wi], af[w][wi]);
-                    }
+                        for (int a = 0; a < 2; ++a) {
 #pragma unroll
-                    for (int k16 = 0; k16 < 2; ++k16) {
-#pragma unroll
-                        for (int w = 0; w < kTilesPerWarp; ++w) {
-#pragma unroll
-                            for (int a = 0; a < 2; ++a) {
-#pragma unroll
-                                for (int j = 0; j < NT; ++j) {
-                                    if (fresh && k16 == 0) {
-                                        mma_m16n8k16_init(acc[w][a][j], af[w][2 * k16 + a], bf[j][0], bf[j][1]);
-                                    }
-                                    else {
-                                        mma_m16n8k16(acc[w][a][j], af[w][2 * k16 + a], bf[j][2 * k16], bf[j][2 * k16 + 1]);
-                                    }
+                            for (int j = 0; j < NT; ++j) {
+                                if (fresh && k16 == 0) {
+                                    mma_m16n8k16_init(acc[w][a][j], af[w][2 * k16 + a], bf[j][0], bf[j][1]);
+                                }
+                                else {
+                                    mma_m16n8k16(acc[w][a][j], af[w][2 * k16 + a], bf[j][2 * k16], bf[j][2 * k16 + 1]);
                                 }
                             }
                         }
@@ -332,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
             kk = 0;
             ++jt;
         }
-        if (!seg_end || (p.dev_mode & 2)) {
+        if (!seg_end) {
             continue;
         }
 

@@ -23,8 +23,8 @@ struct tm_handle {
     int                mmha_chunk      = 0;  // 0 = automatic; TM_B200_MMHA_CHUNK overrides
     int                mmha_warps      = 0;  // 0 = automatic; TM_B200_MMHA_WARPS (1, 2 or 4) overrides
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
+    int                gemm_wait_cycles = 0; // 0 = default bound of the split-tile wait of the tcgen05 GEMM (option "gemm_wait_cycles")
     int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
-    int                gemv_dev_mode   = 0;  // TM_B200_GEMV_DEV_MODE: timing experiments (results are then wrong)
 };
 
 namespace tmb {

@@ -130,8 +130,14 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int g    = lane >> 2;
     const int c    = lane & 3;
 
+    // `order`, `finished` and `lengths` are written by kernels earlier in the stream, but never by the
+    // kernel directly ahead of this one (a GEMM), whose own wait has already covered them.  A CTA
+    // that has nothing to do must still wait for that kernel before it exits: a grid that completes
+    // without waiting would let the kernel after this one start while the one before it still runs.
     const int bi = p.order != nullptr ? p.order[blockIdx.z] : blockIdx.z;
     if (p.finished != nullptr && p.finished[bi]) {
+        pdl_wait();
+        pdl_launch_dependents();
         return;  // template.cuh:1298-1300: neither out nor the cache is touched
     }
     const int rep    = p.H / p.Hkv;
@@ -147,6 +153,8 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int n_split = max(1, (n_past + p.chunk - 1) / p.chunk);
     const int split   = blockIdx.x;
     if (split >= n_split) {
+        pdl_wait();
+        pdl_launch_dependents();
         return;
     }
     const bool last_split = (split == n_split - 1);

@@ -83,6 +83,39 @@ def test_llama7b_projections(name, n, k, t):
     assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"{name} t={t}")
 
 
+@pytest.mark.parametrize("name,n,k", LLAMA7B)
+@pytest.mark.parametrize("t", [32, 512, 2048])
+def test_llama7b_projections_benchmark_grid(name, n, k, t):
+    """The remaining token counts of the benchmark's shape sweep ({1, 8, 32, 128, 512, 2048} x the four
+    Llama-2-7B projections; 1, 8 and 128 are in test_llama7b_projections).  gate_up also runs with the
+    fused SiLU epilogue (output [t, 11008]); 512 and 2048 tokens take several passes of 128 tokens."""
+    lin = _linear(n, k, 0)
+    x = _x(t, k, 1000 + t)
+    w = torch.from_numpy(lin["w_kn"])
+    want = (torch.from_numpy(x).float() @ w.float()).half()
+    assert_close(_run(lin, x, n, k), want.numpy(), f"{name} t={t}")
+    if name == "gate_up":
+        y = _run(lin, x, n, k, fused=True)
+        assert_close(y, ogemm.silu_mul_interleaved(want).numpy(), f"{name} silu t={t}", rel_slack=2.0 ** -9)
+
+
+def test_baseline_config0_exact_case():
+    """BASELINE config 0 as written: torch.manual_seed(0); X = randn(16, 4096).half(); W = (randn(11008, 4096)
+    * 0.02).half(); group-128 asymmetric int4 (q and z clamped to 0..15); Y = X . dequant(W)^T, fp32
+    accumulate, fp16 out.  Weight packing and layout conversion by the oracle, GEMM through tm_gemm_s4_f16."""
+    from oracle import awq, s4_format as f
+    torch.manual_seed(0)
+    x = torch.randn(16, 4096).half()
+    w = (torch.randn(11008, 4096) * 0.02).half()
+    qr = awq.quantize(w, 128)
+    t = awq.to_awq_tensors(qr)
+    a, q = f.convert_s4_k_m8(t.qweight, t.scales, t.qzeros, 11008, 4096, 128)
+    w_nk = awq.pseudo_quant_weight(qr, 128)
+    lin = dict(A_dev=dev(a, torch.int32), Q_dev=dev(q))
+    want = (x.float() @ w_nk.float().t()).half().numpy()
+    assert_close(_run(lin, x.numpy(), 11008, 4096), want, "config 0")
+
+
 @pytest.mark.parametrize("t", [5, 128])
 @pytest.mark.parametrize("n,k", [(1280, 8192), (8192, 1024), (8192, 3584), (2560, 8192), (8192, 2048)])
 def test_llama70b_tp8_and_tp4_shapes(n, k, t):
