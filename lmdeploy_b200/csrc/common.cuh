@@ -59,15 +59,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
+// Same test, but the hardware may park the thread for up to `ns` nanoseconds until the phase completes:
+// a waiting thread then costs no issue slots (a bare try_wait loop takes them from the warps that work).
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Returns false when the time budget ran out (caller records the status bit).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long max_cycles = kMaxWaitCycles)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kMaxWaitCycles) {
+    while (!mbar_try_wait_sleep(bar, parity, 20000u)) {
+        if (clock64() - t0 > max_cycles) {
             return false;
         }
     }

@@ -54,7 +54,7 @@ struct GemmTcParams {
     int                  N, T, K;
     int                  fused_silu;
     // filled in by gemm_tc_launch from the plan
-    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, acc_stride;
+    int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, a_stages, acc_stride, k_split, parts_per_tile;
     long long max_wait_cycles;  // bound of the wait for the partners of a split tile; 0 = the default
 };
 
@@ -64,6 +64,7 @@ struct GemmTcPlan {
     int    n_col_tiles;    // 256-feature tiles
     int    total_units;    // 128x256 weight units
     int    units_per_cta;
+    int    parts_per_tile;  // CTAs per column tile (each with up to units_per_cta groups of it); 0 = the flat unit list cut evenly
     int    ctas;
     int    slots_per_chunk;
     size_t smem_bytes;

@@ -9,23 +9,15 @@
 //                tcgen05.mma (M = 128, N = token tile, K = 16 per instruction, fp16 x fp16 -> fp32, A
 //                from TMEM, B from shared memory) and commits completions to mbarriers
 //   warps 3..18  two teams of eight, one per 128-feature tile.  Every warp streams its own share of
-//                the packed weight through a private cp.async ring and expands it (lop3 nibble
-//                unpack, exact (q - z) in fp16) straight into TMEM with tcgen05.st, from where the
-//                tensor core takes its A operand (no shared-memory round trip); the same warps read
-//                the accumulators back with tcgen05.ld and store C (optionally through the
+//                the packed weight through a private cp.async ring and expands it: lop3 nibble
+//                unpack, exact (q - z) in fp16, one fp16 multiply by the scale (bit-identical to the
+//                reference's dequantised weight, kernels/gemm_s_f16/common.h:115-156, 218-235),
+//                tcgen05.st of the fragments straight into TMEM, from where the tensor core takes
+//                its A operand (no shared-memory round trip); at the end of a column tile the
+//                warps read the accumulators with tcgen05.ld and store C (optionally through the
 //                SiLU(gate) * up epilogue) or the split-K partial
-// Two variants (template parameter FOLD):
-//   FOLD (token tile <= 64)  The tensor core sees the integers (q - z); every 128-row group gets a
-//                fresh accumulator (two per team, used in turn) and the expanding warps add it,
-//                times the group's scale, to fp32 sums they keep in registers:
-//                    y[n][t] += s[g][n] * sum_{k in g} (q - z)[k][n] x[t][k]
-//                This takes the scale multiplies out of the expansion (9 instead of 13 instructions
-//                per packed word); the weight differs from the reference's fp16_rn((q - z) s) by that
-//                one rounding (the products are exact in fp32 here), as in the small-token kernel.
-//   !FOLD (token tile 65..128)  The expansion multiplies by the scale in fp16, bit-identical to the
-//                reference's dequantised weight (kernels/gemm_s_f16/common.h:115-156, 218-235), and a
-//                column tile accumulates over all of its groups in TMEM (two accumulators of 128
-//                columns leave no room for per-group accumulators).
+// A waiting thread sleeps in the mbarrier (try_wait with a time hint): the three single-lane roles
+// would otherwise take a quarter of the issue slots from the expanding warps.
 // Partial tiles of CTAs that share a column tile meet in scratch memory; every CTA of the tile then
 // sums its own share of the feature rows in a fixed order.  Every wait is bounded.
 //
@@ -40,6 +32,32 @@
 // Developer build only (never defined by lmdeploy_b200/build.py): time stamps of selected warps of selected CTAs.
 __device__ long long g_tc_trace[8][2048];
 __device__ int       g_tc_trace_n[8];
+__device__ unsigned long long g_tc_span[512][2];  // per launch: first CTA start, last CTA end (globaltimer ns)
+__device__ int                g_tc_launch;
+__device__ unsigned long long g_tc_cta[160][4];   // launch 5: per CTA start, end (ns), smid, units
+extern "C" __attribute__((visibility("default"))) int tm_dev_gemm_ctas(unsigned long long* out)
+{
+    cudaMemcpyFromSymbol(out, g_tc_cta, sizeof(unsigned long long) * 640);
+    return 0;
+}
+extern "C" __attribute__((visibility("default"))) int tm_dev_gemm_spans(unsigned long long* out, int reset)
+{
+    cudaMemcpyFromSymbol(out, g_tc_span, sizeof(unsigned long long) * 1024);
+    if (reset) {
+        static unsigned long long init[1024];
+        for (int i = 0; i < 512; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0ull; }
+        cudaMemcpyToSymbol(g_tc_span, init, sizeof(init));
+        int z = 0;
+        cudaMemcpyToSymbol(g_tc_launch, &z, sizeof(z));
+    }
+    return 0;
+}
+__device__ __forceinline__ unsigned long long tc_globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 extern "C" __attribute__((visibility("default"))) int tm_dev_gemm_trace(long long* out, int* counts)
 {
     cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 8 * 2048);
@@ -77,14 +95,15 @@ constexpr int kXSTMax    = 6;                    // activation stages
 constexpr int kTeamWarps = 8;
 constexpr int kDqWarps   = kTeams * kTeamWarps;
 constexpr int kDqThreads = kDqWarps * 32;
-constexpr int kDqWarp0   = 1 + kTeams;           // first expanding warp
+constexpr int kIssuers   = 2 * kTeams;           // issuer warps: (team, K half); the second halves idle at token tiles > 64
+constexpr int kDqWarp0   = 1 + kIssuers;         // first expanding warp
 constexpr int kThreads   = (kDqWarp0 + kDqWarps) * 32;
 constexpr int kTmemCols  = 512;                  // accumulators + expanded-weight stages, power of two
 
 struct Bars {
     uint64_t a_full[kTeams][kASTMax], a_empty[kTeams][kASTMax];
     uint64_t x_full[kXSTMax], x_empty[kXSTMax];
-    uint64_t acc_full[kTeams][2], acc_empty[kTeams][2];  // per team and accumulator
+    uint64_t acc_full[kTeams], acc_empty[kTeams];  // per team
     uint32_t tmem_base;
     int      flag;
 };
@@ -109,6 +128,35 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         "l"(desc_b),
         "r"(idesc),
         "r"(accumulate)
+        : "memory");
+}
+
+// Four MMAs: one 64-wide K block (four 16-wide steps) of a unit, operands precomputed so that an MMA costs the
+// issuing thread three instructions.  `first`: the first MMA overwrites the accumulator.
+__device__ __forceinline__ void umma_f16_ts_x4(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi, uint32_t idesc,
+                                               uint32_t first)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p, t;\n"
+        ".reg .b64 d;\n"
+        ".reg .b32 a, l;\n"
+        "setp.eq.b32 p, %5, 0;\n"      // accumulate unless first
+        "setp.eq.b32 t, 0, 0;\n"       // always accumulate
+        "mov.b64 d, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, p;\n"
+        "add.u32 a, %1, 8;\n  add.u32 l, %2, 2;\n  mov.b64 d, {l, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %4, t;\n"
+        "add.u32 a, %1, 16;\n add.u32 l, %2, 4;\n  mov.b64 d, {l, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %4, t;\n"
+        "add.u32 a, %1, 24;\n add.u32 l, %2, 6;\n  mov.b64 d, {l, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], d, %4, t;\n"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a),
+        "r"(desc_lo),
+        "r"(desc_hi),
+        "r"(idesc),
+        "r"(first)
         : "memory");
 }
 
@@ -156,6 +204,20 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8])
     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// sixteen fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16])
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __device__ __forceinline__ uint32_t hmul2_ftz(uint32_t a, uint32_t b)
 {
     uint32_t r;
@@ -172,9 +234,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 __device__ __forceinline__ void warp_wait(uint64_t* bar, uint32_t parity, bool& dead, unsigned* status, unsigned bit)
 {
     if (dead) return;
-    // one lane polls; the shuffle hands the outcome (and, as a warp-level sync, the ordering) to the rest
+    // Usually the phase is complete already: every lane tests it (same answer in every lane, no divergence).
+    if (mbar_try_wait(bar, parity)) return;
+    // Otherwise one lane sleeps in the barrier; the shuffle hands the outcome (and, as a warp-level sync, the
+    // ordering) to the rest.
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;  // suspending wait: leaves the issue slots to the busy warps
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) {
         if ((threadIdx.x & 31) == 0) atomicOr(status, bit);
@@ -182,27 +247,12 @@ __device__ __forceinline__ void warp_wait(uint64_t* bar, uint32_t parity, bool& 
     }
 }
 
-// eight fp32 columns of this thread's TMEM lane, no wait (pair with tmem_ld_wait)
-__device__ __forceinline__ void tmem_ld8_nowait(uint32_t taddr, float* v)
-{
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_ld_wait()
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-template<bool FOLD>
 __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParams p, const __grid_constant__ CUtensorMap x_map)
 {
     const int kXST = p.x_stages;
-    constexpr int kAST = 2;         // expanded-weight stages per team (in TMEM)
+    const int kAST = p.a_stages;    // per team
     const int accS = p.acc_stride;  // TMEM columns of one accumulator
+    const int KS   = p.k_split;     // issuers (and accumulators) per team: 2 at token tiles <= 64, else 1
     extern __shared__ unsigned char smem_dyn[];
     // tiles the tensor core reads must sit on 1024-byte boundaries (the swizzle is a function of
     // the address bits)
@@ -210,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm   = smem_dyn + (base - raw);
 
-    const int TT      = p.token_tile;             // UMMA N, multiple of 16, <= 128 (<= 64 with FOLD)
+    const int TT      = p.token_tile;             // UMMA N, multiple of 16, <= 128
     const int x_bytes = 2 * TT * 128;             // two K blocks of TT rows x 128 B
     unsigned char* x_ring = sm;                                   // kXST x x_bytes (multiples of 1024)
     unsigned char* w_ring = x_ring + kXST * x_bytes;              // kDqWarps x kWST x kWarpStage
@@ -225,6 +275,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     if (blockIdx.x == 64 && blockIdx.y == 0) trow = warp == kDqWarp0 ? 4 : warp == 1 ? 5 : warp == kDqWarp0 + 5 ? 6 : -1;
     if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0) trow = warp == kDqWarp0 ? 7 : trow;
     TC_TRACE(trow, 1, 0);
+    const int launch_idx = *(volatile int*)&g_tc_launch;
+    const long long clk_begin = clock64();
+    const unsigned long long gt_begin = tc_globaltimer();
+    if (tid == 0 && launch_idx < 512) atomicMin(&g_tc_span[launch_idx][0], gt_begin);
 #endif
 
     const int t0     = blockIdx.y * 128;
@@ -232,8 +286,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
 
     const int G         = p.K / kGroup;
     const int upc       = p.units_per_cta;
-    const int u_begin   = blockIdx.x * upc;
-    const int n_units   = min(u_begin + upc, p.total_units) - u_begin;
+    // Two ways of dealing the (column tile, group) units to the CTAs: `parts` CTAs per column tile, each with up
+    // to `upc` consecutive groups of it (no CTA touches two tiles); or, with parts == 0, the flat unit list cut
+    // into runs of `upc` (a run may end one tile and begin the next).
+    const int parts     = p.parts_per_tile;
+    const int u_begin   = parts ? (blockIdx.x / parts) * G + (blockIdx.x % parts) * upc : blockIdx.x * upc;
+    const int n_units   = parts ? min(upc, G - (int)(blockIdx.x % parts) * upc) : min(u_begin + upc, p.total_units) - u_begin;
+    // the CTAs that share column tile `tile`: first CTA and how many
+    auto tile_ctas = [&](int tile, int& c_first) {
+        if (parts) {
+            c_first = tile * parts;
+            return parts;
+        }
+        c_first = (tile * G) / upc;
+        return ((tile + 1) * G - 1) / upc - c_first + 1;
+    };
     const int n_tiles32 = p.N / 32;
 
     // ---- expanding warps: identity and the state of their copy front ---------------------------
@@ -244,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                                        // and which half of the token columns it drains
     // private ring of this warp: per unit its own 2 x 512 B of packed weight (32-feature tile,
     // 32-row slabs 2 kh, 2 kh + 1 of the group) + the 128 B of {zero, scale} of its 32 features
-    const uint32_t       my_ring   = base + (uint32_t)(w_ring - sm) + (uint32_t)(dw < 0 ? 0 : dw) * kWST * kWarpStage;
+    const uint32_t       my_ring   = base + (uint32_t)(w_ring - sm) + (uint32_t)(dw < 0 ? 0 : dw) * kWST * kWarpStage + lane * 16;
     const unsigned char* my_ring_g = w_ring + (dw < 0 ? 0 : dw) * kWST * kWarpStage;
     // the copy front runs kWST - 1 units ahead of the expansion: this lane's 16 bytes of the warp's
     // first slab and of the {zero, scale} row.  A warp whose tile lies beyond N re-reads the last
@@ -261,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     };
     int to_issue = n_units;
     auto issue_unit = [&](int stage) {
-        const uint32_t dst = my_ring + stage * kWarpStage + lane * 16;
+        const uint32_t dst = my_ring + stage * kWarpStage;
         cp_async16(dst, i_w);
         cp_async16(dst + kTileBytes, i_w + slab_b);
         if (lane < 8) cp_async16(dst + 2 * kTileBytes, i_q);
@@ -289,16 +356,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         for (int m = 0; m < kTeams; ++m) {
             for (int s = 0; s < kASTMax; ++s) {
                 mbar_init(&bars->a_full[m][s], kTeamWarps);
-                mbar_init(&bars->a_empty[m][s], 1);
+                mbar_init(&bars->a_empty[m][s], KS);
             }
-            for (int b = 0; b < 2; ++b) {
-                mbar_init(&bars->acc_full[m][b], 1);
-                mbar_init(&bars->acc_empty[m][b], kTeamWarps);
-            }
+            mbar_init(&bars->acc_full[m], KS);
+            mbar_init(&bars->acc_empty[m], kTeamWarps);
         }
         for (int s = 0; s < kXSTMax; ++s) {
             mbar_init(&bars->x_full[s], 1);
-            mbar_init(&bars->x_empty[s], kTeams);
+            mbar_init(&bars->x_empty[s], kTeams * KS);
         }
         fence_mbar_init();
     }
@@ -313,8 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     tc_fence_after();
     const uint32_t tmem   = bars->tmem_base;
     TC_TRACE(trow, 2, 0);
-    // TMEM columns: accumulators [team][FOLD ? 2 : 1] x accS, then the expanded-weight stages
-    const uint32_t a_base = tmem + kTeams * (FOLD ? 2 : 1) * accS;
+    const uint32_t a_base = tmem + kTeams * KS * accS;  // first expanded-weight stage
 
     if (warp == 0) {
         // ================================================================== activation loader
@@ -339,30 +403,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             if (++g == G) g = 0;
         }
     }
-    else if (warp <= kTeams) {
-        // ================================================================== MMA issuers, one per team
-        // A single lane runs the whole loop: waits, eight MMAs, commits.  Nothing here needs the warp.
-        if (lane == 0) {
-            const int      m       = warp - 1;
+    else if (warp <= kIssuers) {
+        // ================================================================== MMA issuers
+        // One lane per (team, K half) runs the whole loop: waits, four (or eight) MMAs, commits.  The issue rate
+        // of one thread among busy warps (about 100 cycles per MMA), not the tensor pipe (about 35 at 64 tokens),
+        // bounds the MMA throughput of small token tiles: four issuers on four different schedulers share the
+        // work there, each half of K with an accumulator of its own (summed by the epilogue).
+        const int m = (warp - 1) & 1;
+        const int h = (warp - 1) >> 1;
+        if (lane == 0 && h < KS) {
             const uint32_t idesc   = (1u << 4) | ((uint32_t)(TT >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+            const uint32_t d_tmem  = tmem + (m * KS + h) * accS;
             const uint32_t kb_step = (uint32_t)(TT * 128) >> 4;  // descriptor units (16 B) between the two K blocks
             const uint64_t d_ring  = make_desc(base + (uint32_t)(x_ring - sm));
+            const uint32_t d_hi    = (uint32_t)(d_ring >> 32);
+            // (the low word of the descriptor carries the address: 14 bits of 16-byte units, never a carry out)
+            const uint32_t d_lo    = (uint32_t)d_ring + (uint32_t)h * kb_step;
             const uint32_t x_step  = (uint32_t)x_bytes >> 4;
             int  seg_idx = 0;
-            bool first   = true;  // !FOLD: first MMA of the current segment overwrites the accumulator
+            bool first   = true;  // first MMA of the current segment overwrites the accumulator
             int  g       = u_begin % G;
             int  sa = 0, sx = 0;
             uint32_t pa = 0, px = 0;  // phase parity of the weight / activation rings
             for (int it = 0; it < n_units; ++it) {
                 bool ok = true;
-                const int buf = FOLD ? (it & 1) : 0;
-                if (FOLD) {
-                    // the expanding warps must have read what this accumulator held two units ago
-                    if (it >= 2) ok = mbar_wait(&bars->acc_empty[m][buf], ((it >> 1) - 1) & 1);
-                }
-                else if (first && seg_idx > 0) {
-                    // the epilogue of the previous segment must have drained the accumulator
-                    ok = mbar_wait(&bars->acc_empty[m][0], (seg_idx - 1) & 1);
+                if (first && seg_idx > 0) {
+                    // the epilogue of the previous segment must have drained the accumulators
+                    ok = mbar_wait(&bars->acc_empty[m], (seg_idx - 1) & 1);
                 }
                 ok = ok && mbar_wait(&bars->x_full[sx], px) && mbar_wait(&bars->a_full[m][sa], pa);
                 if (!ok) {
@@ -371,25 +438,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
                 tc_fence_after();
                 TC_TRACE(trow, 20, it);
-                const uint32_t d_tmem = tmem + (uint32_t)((FOLD ? m * 2 + buf : m) * accS);
-                const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols;
-                const uint64_t d0     = d_ring + (uint64_t)(sx * x_step);
-                uint32_t       accum  = (FOLD || first) ? 0u : 1u;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // K block j / 4, 16-wide K step j % 4 (32 bytes inside the 128-byte rows)
-                    umma_f16_ts(d_tmem, a_tmem + j * 8, d0 + (uint64_t)((j >> 2) * kb_step + (j & 3) * 2), idesc, accum);
-                    accum = 1u;
-                }
+                const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols + (uint32_t)h * 32;
+                const uint32_t lo     = d_lo + (uint32_t)sx * x_step;
+                umma_f16_ts_x4(d_tmem, a_tmem, lo, d_hi, idesc, first ? 1u : 0u);
+                if (KS == 1) umma_f16_ts_x4(d_tmem, a_tmem + 32, lo + kb_step, d_hi, idesc, 0u);
                 umma_commit(&bars->a_empty[m][sa]);
                 umma_commit(&bars->x_empty[sx]);
                 TC_TRACE(trow, 21, it);
                 first = false;
-                if (FOLD) {
-                    umma_commit(&bars->acc_full[m][buf]);
-                }
-                else if ((it == n_units - 1) || (g == G - 1)) {
-                    umma_commit(&bars->acc_full[m][0]);
+                if ((it == n_units - 1) || (g == G - 1)) {
+                    umma_commit(&bars->acc_full[m]);
                     ++seg_idx;
                     first = true;
                 }
@@ -412,10 +470,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         // one may still be using.
         pdl_wait();
 
-        // split-K: [slot][128 tokens][256 feature rows] fp32 partial tiles (a warp touches 128 contiguous
-        // bytes per token), per tile a count of CTAs whose partial is complete and a count of CTAs that
-        // are done reading.  Tiles this CTA shares with others are reduced after its last unit.
-        float* const slots  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * (size_t)(128 * kSuperN);
+        // split-K: [slot][TT tokens][256 feature rows] fp32 partial tiles (a warp touches 128 contiguous
+        // bytes per token: whole sectors), per tile a count of CTAs whose partial is complete and a count of
+        // CTAs that are done reading.  Tiles this CTA shares with others are reduced after its last unit.
+        const size_t slot_floats = (size_t)kSuperN * TT;
+        float* const slots  = p.workspace + (size_t)blockIdx.y * p.slots_per_chunk * slot_floats;
         int* const   arrive = p.counters + (size_t)blockIdx.y * p.n_col_tiles;
         int* const   done   = p.counters + (size_t)(gridDim.y + blockIdx.y) * p.n_col_tiles;
         constexpr int kMaxPending = 4;
@@ -424,9 +483,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
         // Every CTA of a split tile reduces its own share of the feature rows, once all partials of the
         // tile are in scratch: nobody reads more than one tile's worth, and the sum runs in CTA order.
         auto reduce_share = [&](int tjs) {
-            const int c_first = (tjs * G) / upc;
-            const int c_last  = ((tjs + 1) * G - 1) / upc;
-            const int n_split = c_last - c_first + 1;
+            int       c_first;
+            const int n_split = tile_ctas(tjs, c_first);
             const int col0    = tjs * kSuperN;
             if (dtid == 0) {
                 // Bounded wait for the other CTAs of the tile.  The plan splits tiles between CTAs only
@@ -438,6 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 for (;;) {
                     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrive + tjs) : "memory");
                     if (seen >= n_split || clock64() - t_begin > p.max_wait_cycles) break;
+                    __nanosleep(64);
                 }
                 if (seen < n_split) atomicOr(p.status, kStatusGemmTmemWait);
                 bars->flag = seen >= n_split;
@@ -451,22 +510,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 const int f1     = j == n_split - 1 ? n_cols : ((n_cols * (j + 1) / n_split) & ~3);
                 const int quads  = (f1 - f0) / 4;
                 const int items  = t_rows * quads;
+                const float* tile_slots = slots + (size_t)(c_first + tjs) * slot_floats;
                 for (int i = dtid; i < items; i += kDqThreads) {
                     const int    t    = i / quads;
                     const int    n    = f0 + (i - t * quads) * 4;
-                    const float* src  = slots + (size_t)t * kSuperN + n;
+                    const float* src  = tile_slots + (size_t)t * kSuperN + n;
                     float4       acc  = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int cc = c_first; cc <= c_last; cc += 4) {
-                        float4 part[4];
+                    for (int cc = 0; cc < n_split; cc += 8) {
+                        float4 part[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
+                        for (int e = 0; e < 8; ++e) {
                             part[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (cc + e <= c_last) {
-                                part[e] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(cc + e + tjs) * (size_t)(128 * kSuperN)));
-                            }
+                            if (cc + e < n_split) part[e] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(cc + e) * slot_floats));
                         }
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {  // absent slots add +0
+                        for (int e = 0; e < 8; ++e) {  // absent slots add +0
                             acc.x += part[e].x, acc.y += part[e].y, acc.z += part[e].z, acc.w += part[e].w;
                         }
                     }
@@ -496,67 +554,159 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
             }
         };
 
-        const int      ccount = TT / 2;  // token columns per warp: [kh * ccount, +ccount)
+        const int      ccount = TT / 2;                      // token columns per warp: [kh * ccount, +ccount)
         const int      n_row  = m * kTileN + q * 32 + lane;  // feature row of the CTA tile held by this thread
-        // fp32 sums of this thread's feature row over the units of the current segment (FOLD)
-        float y[FOLD ? 32 : 1];
-#pragma unroll
-        for (int i = 0; i < (FOLD ? 32 : 1); ++i) y[i] = 0.f;
-        float s_prev = 0.f;   // scale of this thread's feature row for the unit expanded last (FOLD)
-        int   prev_js = 0;
-        bool  prev_end = false;
+        const uint32_t a_lane = ((uint32_t)(q * 32) << 16) + (uint32_t)(kh * 32);  // TMEM lanes and first column of this warp's share of a stage
 
-        // output of a finished segment: `get(col, v)` delivers eight token columns of this thread's row
-        auto finish_segment = [&](int this_js, auto&& get) {
-            const int c_first = (this_js * G) / upc;
-            const int c_last  = ((this_js + 1) * G - 1) / upc;
-            const int n_split = c_last - c_first + 1;
-            const int col0    = this_js * kSuperN;
-            const int n_glob  = col0 + n_row;
-            // eight token columns of this thread's feature row -> C
-            auto store_c = [&](const float (&v)[8], int col) {
+        int      js = u_begin / G, g = u_begin - js * G;
+        int      sw = 0, sw_fill = kWST - 1;  // ring slot read now / refilled now (the one read one unit ago)
+        int      sa = 0;
+        uint32_t pa = 0;                      // phase parity of the team's expanded-weight ring
+        for (int it = 0; it < n_units; ++it) {
+            TC_TRACE(trow, 30, it);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kWST - 2) : "memory");
+            __syncwarp();
+            // the tensor core must be done with what this TMEM stage held kAST units ago (the first
+            // round passes at once: a fresh barrier counts as having completed the phase before)
+            warp_wait(&bars->a_empty[m][sa], pa ^ 1u, dead, p.status, kStatusGemmPipeWait);
+            tc_fence_after();
+            TC_TRACE(trow, 32, it);
+            {
+                const unsigned char* sb = my_ring_g + sw * kWarpStage;
+                const __half2*       qs = reinterpret_cast<const __half2*>(sb + 2 * kTileBytes);
+                uint32_t z1024[2], nz64[2], s_lo[2], s_hi[2];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int t = t0 + col + i;
-                    if (p.fused_silu) {
-                        // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pair (gate, up) = rows (n, n + 1)
-                        const float mine  = __half2float(__float2half_rn(v[i]));
-                        const float other = __shfl_down_sync(0xffffffffu, mine, 1);
-                        if ((lane & 1) == 0 && t < p.T && n_glob < p.N) {
-                            const float silu = mine / (1.f + __expf(-mine));
-                            p.C[(size_t)t * (p.N / 2) + n_glob / 2] = __float2half_rn(silu * other);
-                        }
-                    }
-                    else if (t < p.T && n_glob < p.N) {
-                        p.C[(size_t)t * p.N + n_glob] = __float2half_rn(v[i]);
+                for (int a = 0; a < 2; ++a) {
+                    const __half2 q_lo = qs[a * 16 + r];
+                    const __half2 q_hi = qs[a * 16 + r + 8];
+                    const __half2 zl2  = __half2half2(__hadd(__low2half(q_lo), __float2half_rn(960.f)));
+                    const __half2 zh2  = __half2half2(__hneg(__low2half(q_hi)));
+                    const __half2 sl2  = __half2half2(__high2half(q_lo));
+                    const __half2 sh2  = __half2half2(__high2half(q_hi));
+                    z1024[a] = reinterpret_cast<const uint32_t&>(zl2);
+                    nz64[a]  = reinterpret_cast<const uint32_t&>(zh2);
+                    s_lo[a]  = reinterpret_cast<const uint32_t&>(sl2);
+                    s_hi[a]  = reinterpret_cast<const uint32_t&>(sh2);
+                }
+                const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols + a_lane;
+                // all fragments first (independent chains the scheduler can interleave), then the stores
+                uint32_t f[8][4];
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    const uint4    w     = reinterpret_cast<const uint4*>(sb)[kk * 32 + lane];
+                    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int wi = 0; wi < 4; ++wi) {
+                        const int a = wi & 1;
+                        uint32_t (&fr)[4] = f[kk * 4 + wi];
+                        unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], fr);
+                        fr[0] = hmul2_ftz(fr[0], s_lo[a]);
+                        fr[1] = hmul2_ftz(fr[1], s_hi[a]);
+                        fr[2] = hmul2_ftz(fr[2], s_lo[a]);
+                        fr[3] = hmul2_ftz(fr[3], s_hi[a]);
                     }
                 }
-            };
-            if (!dead) {
-                float* mine = slots + (size_t)(blockIdx.x + this_js) * (size_t)(128 * kSuperN) + n_row;
-                for (int cb = 0; cb < ccount; cb += 8) {
-                    const int col = kh * ccount + cb;
-                    float     v[8];
-                    get(cb, col, v);
-                    if (n_split > 1) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) __stcg(mine + (size_t)(col + i) * kSuperN, v[i]);
-                    }
-                    else {
-                        store_c(v, col);
+                for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+                    for (int wi = 0; wi < 4; ++wi) {
+                        const int k16 = wi >> 1;
+                        const int a   = wi & 1;
+                        const uint32_t (&fr)[4] = f[kk * 4 + wi];
+                        // rows q*32 + a*16 .. +15 (TMEM lanes), k = 32 (2 kh + kk) + 16 k16 .. +15 (8 columns)
+                        tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(kk * 16 + k16 * 8), fr[0], fr[1], fr[2], fr[3]);
                     }
                 }
             }
-            return n_split;
-        };
-        // after the segment's values have left the accumulators / registers
-        auto publish_segment = [&](int this_js, int n_split) {
+            // expanded tile visible to the tensor core; packed stage free again
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->a_full[m][sa]);
+            TC_TRACE(trow, 33, it);
+            // refill the slot that was read one unit ago (everyone in the warp is past its reads)
+            if (to_issue > 0) issue_unit(sw_fill);
+            --to_issue;
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            sw      = (sw == kWST - 1) ? 0 : sw + 1;
+            sw_fill = (sw_fill == kWST - 1) ? 0 : sw_fill + 1;
+            if (++sa == kAST) {
+                sa = 0;
+                pa ^= 1u;
+            }
+
+            const int  this_js = js;
+            const bool seg_end = (it == n_units - 1) || (g == G - 1);
+            if (++g == G) {
+                g = 0;
+                ++js;
+            }
+            if (!seg_end) continue;
+
+            // ---- 256-feature tile this_js finished for this CTA: drain the accumulators -----------
+            int       c_first;
+            const int n_split = tile_ctas(this_js, c_first);
+            const int col0    = this_js * kSuperN;
+            TC_TRACE(trow, 34, it);
+            warp_wait(&bars->acc_full[m], seg_idx & 1, dead, p.status, kStatusGemmTmemWait);
+            tc_fence_after();
+            TC_TRACE(trow, 35, it);
+            const int n_glob = col0 + n_row;
+            const uint32_t my_acc = tmem + m * KS * accS + ((uint32_t)(q * 32) << 16);
+            if (!dead) {
+                float* mine = slots + (size_t)(blockIdx.x + this_js) * slot_floats + n_row;
+                for (int cb = 0; cb < ccount; cb += 16) {
+                    // sixteen token columns of this thread's feature row (eight, twice, where ccount is not a
+                    // multiple of 16: the second half then repeats columns the other warp owns and is dropped)
+                    const int col = kh * ccount + cb;
+                    float     v[16];
+                    tmem_ld16(my_acc + (uint32_t)col, v);
+                    if (KS == 2) {
+                        float v2[16];
+                        tmem_ld16(my_acc + (uint32_t)(accS + col), v2);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += v2[i];
+                    }
+                    const int valid = min(16, ccount - cb);  // 8 or 16
+                    if (n_split > 1) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (i < valid) __stcg(mine + (size_t)(col + i) * kSuperN, v[i]);
+                        }
+                    }
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int t = t0 + col + i;
+                            const bool in = i < valid && t < p.T && n_glob < p.N;
+                            if (p.fused_silu) {
+                                // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pair (gate, up) = rows (n, n + 1)
+                                const float mine_v = __half2float(__float2half_rn(v[i]));
+                                const float other  = __shfl_down_sync(0xffffffffu, mine_v, 1);
+                                if ((lane & 1) == 0 && in) {
+                                    const float silu = mine_v / (1.f + __expf(-mine_v));
+                                    p.C[(size_t)t * (p.N / 2) + n_glob / 2] = __float2half_rn(silu * other);
+                                }
+                            }
+                            else if (in) {
+                                p.C[(size_t)t * p.N + n_glob] = __float2half_rn(v[i]);
+                            }
+                        }
+                    }
+                }
+            }
+            ++seg_idx;
+            // the accumulators may be overwritten now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty[m]);
+            TC_TRACE(trow, 37, it);
             if (n_split > 1) {
-                // publish the partial; its reduction waits until this CTA has no units left
-                __threadfence();
+                // publish the partial (its reduction waits until this CTA has no units left): the barrier orders
+                // every thread's stores before the fence of the one thread that then counts the CTA in
                 named_bar_sync(1, kDqThreads);
                 if (dtid == 0) {
-                    __threadfence();  // release: the partial of every thread, ordered before by the barrier
+                    __threadfence();
                     atomicAdd(arrive + this_js, 1);
                 }
                 if (n_pend == kMaxPending) {
@@ -566,175 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
                 pend[n_pend++] = this_js;
             }
-        };
-
-        int      js = u_begin / G, g = u_begin - js * G;
-        int      sw = 0, sw_fill = kWST - 1;  // ring slot read now / refilled now (the one read one unit ago)
-        int      sa = 0;
-        uint32_t pa = 0;                      // phase parity of the team's expanded-weight ring
-        const int n_iter = FOLD ? n_units + 1 : n_units;  // FOLD: the accumulator of a unit is folded one iteration later
-        for (int it = 0; it < n_iter; ++it) {
-            float s_cur    = 0.f;
-            int   this_js  = js;
-            bool  seg_end  = false;
-            if (it < n_units) {
-                TC_TRACE(trow, 30, it);
-                asm volatile("cp.async.wait_group %0;" ::"n"(kWST - 2) : "memory");
-                __syncwarp();
-                TC_TRACE(trow, 31, it);
-                // the tensor core must be done with what this TMEM stage held kAST units ago (the first
-                // round passes at once: a fresh barrier counts as having completed the phase before)
-                warp_wait(&bars->a_empty[m][sa], pa ^ 1u, dead, p.status, kStatusGemmPipeWait);
-                tc_fence_after();
-                TC_TRACE(trow, 32, it);
-                {
-                    const unsigned char* sb = my_ring_g + sw * kWarpStage;
-                    const __half2*       qs = reinterpret_cast<const __half2*>(sb + 2 * kTileBytes);
-                    uint32_t z1024[2], nz64[2], s_lo[2], s_hi[2];
-#pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const __half2 q_lo = qs[a * 16 + r];
-                        const __half2 q_hi = qs[a * 16 + r + 8];
-                        const __half2 zl2  = __half2half2(__hadd(__low2half(q_lo), __float2half_rn(960.f)));
-                        const __half2 zh2  = __half2half2(__hneg(__low2half(q_hi)));
-                        z1024[a] = reinterpret_cast<const uint32_t&>(zl2);
-                        nz64[a]  = reinterpret_cast<const uint32_t&>(zh2);
-                        if (!FOLD) {
-                            const __half2 sl2 = __half2half2(__high2half(q_lo));
-                            const __half2 sh2 = __half2half2(__high2half(q_hi));
-                            s_lo[a] = reinterpret_cast<const uint32_t&>(sl2);
-                            s_hi[a] = reinterpret_cast<const uint32_t&>(sh2);
-                        }
-                    }
-                    if (FOLD) s_cur = __half2float(__high2half(qs[lane]));  // feature row q * 32 + lane of the team's tile
-                    const uint32_t a_tmem = a_base + (m * kAST + sa) * kACols + ((uint32_t)(q * 32) << 16);
-                    // one 32-row slab at a time: its four fragments first (independent chains the scheduler can
-                    // interleave), then their stores
-#pragma unroll
-                    for (int kk = 0; kk < 2; ++kk) {
-                        const int      k32   = kh * 2 + kk;  // 32-row slab of the group: k = 32 k32 .. +31
-                        const uint4    w     = reinterpret_cast<const uint4*>(sb)[kk * 32 + lane];
-                        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
-                        uint32_t       f[4][4];
-#pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) {
-                            const int a = wi & 1;
-                            unpack_s4_minus_zero(wv[wi], z1024[a], nz64[a], f[wi]);
-                            if (!FOLD) {
-                                f[wi][0] = hmul2_ftz(f[wi][0], s_lo[a]);
-                                f[wi][1] = hmul2_ftz(f[wi][1], s_hi[a]);
-                                f[wi][2] = hmul2_ftz(f[wi][2], s_lo[a]);
-                                f[wi][3] = hmul2_ftz(f[wi][3], s_hi[a]);
-                            }
-                        }
-#pragma unroll
-                        for (int wi = 0; wi < 4; ++wi) {
-                            const int k16 = wi >> 1;
-                            const int a   = wi & 1;
-                            // rows q*32 + a*16 .. +15 (TMEM lanes), k = 32 k32 + 16 k16 .. +15 (8 columns)
-                            tmem_st_16x128b_x2(a_tmem + ((uint32_t)(a * 16) << 16) + (uint32_t)(k32 * 16 + k16 * 8), f[wi][0], f[wi][1],
-                                               f[wi][2], f[wi][3]);
-                        }
-                    }
-                }
-                // expanded tile visible to the tensor core; packed stage free again
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->a_full[m][sa]);
-                TC_TRACE(trow, 33, it);
-                // refill the slot that was read one unit ago (everyone in the warp is past its reads)
-                if (to_issue > 0) issue_unit(sw_fill);
-                --to_issue;
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                sw      = (sw == kWST - 1) ? 0 : sw + 1;
-                sw_fill = (sw_fill == kWST - 1) ? 0 : sw_fill + 1;
-                if (++sa == kAST) {
-                    sa = 0;
-                    pa ^= 1u;
-                }
-                seg_end = (it == n_units - 1) || (g == G - 1);
-                if (++g == G) {
-                    g = 0;
-                    ++js;
-                }
-            }
-
-            if (FOLD) {
-                if (it >= 1) {
-                    // ---- fold the accumulator of unit it - 1 into the fp32 sums ---------------------
-                    const int u   = it - 1;
-                    const int buf = u & 1;
-                    TC_TRACE(trow, 34, it);
-                    warp_wait(&bars->acc_full[m][buf], (uint32_t)(u >> 1) & 1u, dead, p.status, kStatusGemmTmemWait);
-                    tc_fence_after();
-                    TC_TRACE(trow, 35, it);
-                    const uint32_t my_acc = tmem + (uint32_t)((m * 2 + buf) * accS) + ((uint32_t)(q * 32) << 16) + (uint32_t)(kh * ccount);
-                    // two halves of up to 16 columns each (registers): load, wait, accumulate
-#pragma unroll
-                    for (int hf = 0; hf < 2; ++hf) {
-                        float v[16];
-                        if (!dead) {
-#pragma unroll
-                            for (int cb = 0; cb < 16; cb += 8) {
-                                if (hf * 16 + cb < ccount) tmem_ld8_nowait(my_acc + (uint32_t)(hf * 16 + cb), v + cb);
-                            }
-                            tmem_ld_wait();
-                        }
-                        if (hf == 1) {
-                            // the accumulator may be overwritten now
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty[m][buf]);
-                        }
-                        if (!dead) {
-#pragma unroll
-                            for (int cb = 0; cb < 16; cb += 8) {
-                                if (hf * 16 + cb < ccount) {
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i) y[hf * 16 + cb + i] = fmaf(s_prev, v[cb + i], y[hf * 16 + cb + i]);
-                                }
-                            }
-                        }
-                    }
-                    TC_TRACE(trow, 36, it);
-                    if (prev_end) {
-                        // ---- 256-feature tile prev_js finished for this CTA --------------------------
-                        const int n_split = finish_segment(prev_js, [&](int cb, int, float (&o)[8]) {
-#pragma unroll
-                            for (int cc = 0; cc < 32; cc += 8) {
-                                if (cc == cb) {
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i) o[i] = y[cc + i];
-                                }
-                            }
-                        });
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) y[i] = 0.f;
-                        TC_TRACE(trow, 37, it);
-                        publish_segment(prev_js, n_split);
-                        TC_TRACE(trow, 38, it);
-                    }
-                }
-                s_prev   = s_cur;
-                prev_js  = this_js;
-                prev_end = seg_end;
-                continue;
-            }
-
-            if (!seg_end) continue;
-
-            // ---- !FOLD: 256-feature tile this_js finished for this CTA: drain the accumulator --------
-            warp_wait(&bars->acc_full[m][0], seg_idx & 1, dead, p.status, kStatusGemmTmemWait);
-            tc_fence_after();
-            const uint32_t my_acc  = tmem + m * accS + ((uint32_t)(q * 32) << 16);
-            const int      n_split = finish_segment(this_js, [&](int, int col, float (&o)[8]) { tmem_ld8(my_acc + (uint32_t)col, o); });
-            ++seg_idx;
-            // the accumulator may be overwritten now
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0 && !dead) mbar_arrive(&bars->acc_empty[m][0]);
-            publish_segment(this_js, n_split);
+            TC_TRACE(trow, 38, it);
         }
         TC_TRACE(trow, 40, 0);
         for (int i = 0; i < n_pend; ++i) {
@@ -749,6 +731,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
     }
+#ifdef TM_B200_GEMM_TRACE
+    if (tid == 0 && launch_idx < 512) {
+        atomicMax(&g_tc_span[launch_idx][1], tc_globaltimer());
+        if (launch_idx == 5 && blockIdx.x < 160 && blockIdx.y == 0) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            g_tc_cta[blockIdx.x][0] = gt_begin;
+            g_tc_cta[blockIdx.x][1] = tc_globaltimer();
+            g_tc_cta[blockIdx.x][2] = smid;
+            g_tc_cta[blockIdx.x][3] = (unsigned long long)n_units;
+        }
+        if (blockIdx.x == 0 && blockIdx.y == 0) {
+            if (launch_idx + 256 < 512) {   // CTA 0's own duration in SM cycles and in ns, stored 256 rows further down
+                g_tc_span[launch_idx + 256][0] = (unsigned long long)(clock64() - clk_begin);
+                g_tc_span[launch_idx + 256][1] = tc_globaltimer() - gt_begin;
+            }
+            // the last thing CTA 0 does; every CTA of the launch has long read the index
+            __threadfence();
+            atomicAdd(&g_tc_launch, 1);
+        }
+    }
+#endif
 }
 
 using PFN_encodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -768,6 +772,8 @@ PFN_encodeTiled lookup_encode_tiled()
 }
 
 int x_stages_for(int token_tile) { return token_tile > 64 ? 3 : kXSTMax; }
+int a_stages_for(int token_tile) { (void)token_tile; return 2; }
+int k_split_for(int token_tile) { return token_tile > 64 ? 1 : 2; }
 int acc_stride_for(int token_tile) { return token_tile > 64 ? 128 : 64; }
 
 }  // namespace
@@ -785,40 +791,55 @@ GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
     pl.n_col_tiles = (N + kSuperN - 1) / kSuperN;
     const int G    = K / kGroup;
     pl.total_units = pl.n_col_tiles * G;
+    pl.parts_per_tile = 0;
     if ((long long)pl.t_chunks * pl.n_col_tiles >= sm_count) {
         // enough whole column tiles to fill the device: one per CTA, nothing is split, nobody waits
         pl.units_per_cta = G;
+        pl.ctas          = pl.n_col_tiles;
     }
     else {
         // K is split between CTAs only while the whole grid is a single wave of one CTA per SM: CTAs
         // that share a column tile wait for one another, so all of them must be able to run together
         int ctas = sm_count / pl.t_chunks;
         if (ctas > pl.total_units) ctas = pl.total_units;
-        pl.units_per_cta = (pl.total_units + ctas - 1) / ctas;
+        const int flat = (pl.total_units + ctas - 1) / ctas;  // units per CTA when the flat unit list is cut evenly
+        // Prefer a whole number of CTAs per column tile when that costs at most one unit more per CTA: a CTA whose
+        // run of units crosses from one tile into the next publishes and reduces two partial tiles instead of one.
+        const int per_tile = ctas / pl.n_col_tiles;            // >= 1 here
+        const int part     = (G + per_tile - 1) / per_tile;    // units per CTA with per_tile CTAs on every tile
+        if (per_tile >= 2 && part <= flat + 1) {
+            pl.parts_per_tile = (G + part - 1) / part;
+            pl.units_per_cta  = part;
+            pl.ctas           = pl.n_col_tiles * pl.parts_per_tile;
+        }
+        else {
+            pl.units_per_cta = flat;
+            pl.ctas          = (pl.total_units + flat - 1) / flat;
+        }
     }
-    pl.ctas            = (pl.total_units + pl.units_per_cta - 1) / pl.units_per_cta;
     pl.slots_per_chunk = pl.ctas + pl.n_col_tiles;
     pl.smem_bytes      = gemm_tc_smem_bytes(pl.token_tile);
-    pl.workspace_floats = pl.units_per_cta % G == 0 ? 0 : (size_t)pl.t_chunks * pl.slots_per_chunk * 128 * kSuperN;
+    pl.workspace_floats = pl.units_per_cta % G == 0 ? 0 : (size_t)pl.t_chunks * pl.slots_per_chunk * pl.token_tile * kSuperN;
     pl.counter_ints     = (size_t)2 * pl.t_chunks * pl.n_col_tiles;  // arrivals and finished readers per tile
     return pl;
 }
 
 cudaError_t gemm_tc_prepare(int max_smem)
 {
-    cudaError_t e = cudaFuncSetAttribute(gemm_s4_f16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(gemm_s4_f16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    return cudaFuncSetAttribute(gemm_s4_f16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
 
 cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st, bool pdl)
 {
     p.units_per_cta   = pl.units_per_cta;
+    p.parts_per_tile  = pl.parts_per_tile;
     p.total_units     = pl.total_units;
     p.slots_per_chunk = pl.slots_per_chunk;
     p.n_col_tiles     = pl.n_col_tiles;
     p.token_tile      = pl.token_tile;
     p.x_stages        = x_stages_for(pl.token_tile);
+    p.a_stages        = a_stages_for(pl.token_tile);
+    p.k_split         = k_split_for(pl.token_tile);
     if (p.max_wait_cycles <= 0) p.max_wait_cycles = kMaxWaitCycles;
     p.acc_stride      = acc_stride_for(pl.token_tile);
 
@@ -837,10 +858,7 @@ cudaError_t gemm_tc_launch(const GemmTcPlan& pl, GemmTcParams p, cudaStream_t st
         return cudaErrorInvalidValue;
     }
     dim3 grid(pl.ctas, pl.t_chunks);
-    if (pl.token_tile <= 64) {
-        return launch_kernel(gemm_s4_f16_tc_kernel<true>, grid, dim3(kThreads), pl.smem_bytes, st, pdl, p, x_map);
-    }
-    return launch_kernel(gemm_s4_f16_tc_kernel<false>, grid, dim3(kThreads), pl.smem_bytes, st, pdl, p, x_map);
+    return launch_kernel(gemm_s4_f16_tc_kernel, grid, dim3(kThreads), pl.smem_bytes, st, pdl, p, x_map);
 }
 
 }  // namespace tmb
