@@ -44,7 +44,9 @@ typedef struct tm_handle tm_handle;
 /* Per-device state: SM count, split-K scratch, split-KV scratch, device status word.
  * One handle is used by one host thread at a time (the reference runs one engine thread per
  * GPU: src/turbomind/models/llama/LlamaV2.cc:435-438); handles of different devices may be
- * used concurrently.  No process-global mutable state. */
+ * used concurrently.  No process-global mutable state, with two exceptions: the per-device table behind
+ * tm_gemm_s4_f16_noalloc (guarded by a mutex) and a thread-local switch the decode driver sets around its
+ * own launches. */
 TM_API int tm_create(tm_handle** out, int device);
 TM_API int tm_destroy(tm_handle* h);
 TM_API const char* tm_status_string(int status);
@@ -85,8 +87,9 @@ TM_API int tm_gemm_s4_f16(tm_handle* h, void* C, const void* A, const void* B, c
  * not meet cudaMalloc's device-wide synchronisation.  No counterpart in the reference (its GEMM
  * needs no scratch).  It takes no handle and calls no allocator: the split-K scratch is an 8 MB
  * array built into the library image (every GPU that loads the library holds it until exit).
- * Limits: n <= 16 tokens, and a shape whose partial tiles fit the 8 MB (all Llama-2 projections
- * do); anything larger returns TM_ERR_WORKSPACE.  Runs on the CURRENT device, asynchronously on
+ * Limits: n <= 16 tokens, and a shape whose partial tiles fit the 8 MB: every Llama-2-7B projection
+ * and every tensor-parallel shard of Llama-2-70B does at all n <= 16; the un-sharded 70B gate_up
+ * (m = 57344) does up to 8 tokens only.  Anything larger returns TM_ERR_WORKSPACE.  Runs on the CURRENT device, asynchronously on
  * `stream`.  The first call on a device resolves the array's device address and sets kernel
  * attributes: make that call before any stream capture.  All calls share the one array, so two
  * calls that overlap on the GPU (different streams) race; calls on one stream are safe.  A
@@ -414,6 +417,12 @@ typedef struct tm_llama_decode_state {
 TM_API int tm_llama_decode(tm_llama* m, const tm_llama_decode_state* st, int n_steps, int use_graph, void* stream);
 /* Kernels (own + library) launched by the most recent tm_llama_decode call. */
 TM_API unsigned long long tm_llama_last_launches(const tm_llama* m);
+/* tm_llama_decode and tm_llama_prefill only enqueue work.  What goes wrong on the device afterwards — a bounded
+ * wait inside a kernel that gave up, a prefill whose history + new tokens exceed session_len (the surplus rows
+ * are dropped, never written outside a cache head) — is recorded in the status word of the model's handle.
+ * This call synchronises `stream`, reads and clears that word: TM_OK, or TM_ERR_DEVICE_TIMEOUT with the bits in
+ * *word (tm_check_device_status on the model's handle).  Call it wherever the host synchronises anyway. */
+TM_API int tm_llama_check_status(tm_llama* m, void* stream, unsigned* word);
 
 #ifdef __cplusplus
 }

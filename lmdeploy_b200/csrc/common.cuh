@@ -13,6 +13,8 @@ namespace tmb {
 enum : unsigned {
     kStatusGemmPipeWait  = 1u << 2,  // tcgen05 GEMM: a pipeline barrier (copies, expanded weight, MMA completion)
     kStatusGemmTmemWait  = 1u << 3,  // tcgen05 GEMM: accumulator hand-over or the partners of a split tile
+    kStatusPrefillOverflow = 1u << 5,  // prefill: a sequence's history + new tokens exceed the cache (session_len) or
+                                       // its new tokens exceed max_q_len: the surplus rows were dropped
 };
 
 // Upper bound, in SM clock cycles, on one mbarrier wait (about 0.15-0.3 s): far above any

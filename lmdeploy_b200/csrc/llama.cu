@@ -279,7 +279,7 @@ int run_step(StepCtx& c)
         ++c.launches;
     }
     if (st.logits_out) {
-        gather_logits_kernel<<<148 * 4, 256, 0, s>>>(st.logits_out, m.logits, B, m.local_vocab, tp);
+        gather_logits_kernel<<<m.h->sm_count * 4, 256, 0, s>>>(st.logits_out, m.logits, B, m.local_vocab, tp);
         if (!c.ok_cuda()) return c.rc;
     }
     argmax_kernel<<<B, 1024, 0, s>>>(m.logits, m.picked, st.output_ids, st.step, m.inactive, B, m.local_vocab, tp, st.max_steps);
@@ -417,6 +417,12 @@ extern "C" int tm_llama_set_globals(tm_llama* m, const void* tok_embeddings, con
         m->graph_exec = nullptr;
     }
     return TM_OK;
+}
+
+extern "C" int tm_llama_check_status(tm_llama* m, void* stream, unsigned* word)
+{
+    if (!m) return TM_ERR_INVALID_ARG;
+    return tm_check_device_status(m->h, stream, word);
 }
 
 extern "C" unsigned long long tm_llama_last_launches(const tm_llama* m)

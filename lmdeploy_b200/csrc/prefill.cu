@@ -196,7 +196,8 @@ __global__ void __launch_bounds__(kCacheThreads) extend_kv_cache_kernel(CachePar
     const int  idx  = blockIdx.x * kCacheThreads + threadIdx.x;
     const int  vec  = idx % kVecPerHead;
     const int  row  = idx / kVecPerHead;
-    if (row >= p.length[bi]) return;
+    // a length beyond what the contiguous side holds per head is a caller error: never read the neighbouring head
+    if (row >= p.length[bi] || row >= p.max_len) return;
     if (row + p.history[bi] >= p.max_seq_len) return;  // never past the rows a cache head holds
     const __half* src  = (is_v ? p.v_lin : p.k_lin) + (((size_t)bi * p.Hkv + hi) * p.max_len + row) * kD + vec * 8;
     const uint4   x    = *reinterpret_cast<const uint4*>(src);
@@ -227,7 +228,8 @@ __global__ void __launch_bounds__(kCacheThreads) transpose_kv_cache_kernel(Cache
     const int  idx  = blockIdx.x * kCacheThreads + threadIdx.x;
     const int  vec  = idx % kVecPerHead;
     const int  row  = idx / kVecPerHead;
-    if (row >= p.length[bi]) return;
+    // rows beyond what either side holds per head (a caller error) are skipped, not taken from the next head
+    if (row >= p.length[bi] || row >= p.max_len || row >= p.max_seq_len) return;
     const size_t srci = p.offset + ((size_t)hi * p.max_seq_len + row) * kD + vec * 8;
     const void*  base = (is_v ? p.v_cache : p.k_cache)[bi];
     uint4        x;

@@ -4,6 +4,7 @@
 // int4 path: per layer { qkv GEMM, bias + RoPE + transpose, cache extend, causal attention over the cache,
 // o GEMM, [allreduce], add + norm, w1|w3 GEMM with SiLU, w2 GEMM, [allreduce], add + norm }.  Tokens are
 // packed ([token_num, hidden] activations, no padding rows reach a GEMM).  Asynchronous on `stream`.
+#include "common.cuh"
 #include "llama.h"
 #include "tm_b200.h"
 
@@ -13,11 +14,17 @@ namespace {
 
 // per packed token: offset to its padded index b * max_q_len + s (what invokeGetPaddingOffsetAndCuSeqLens yields,
 // src/turbomind/kernels/bert_preprocess_kernels.cu:54); per sequence: its length
-__global__ void prefill_prepare_kernel(const int* cu_seqlens, int B, int max_q_len, int* padding_offset, int* input_length)
+__global__ void prefill_prepare_kernel(const int* cu_seqlens, int B, int max_q_len, int* padding_offset, int* input_length,
+                                       const int* history, const int* context, int session_len, unsigned* status)
 {
     const int b = blockIdx.x;
     const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
-    if (threadIdx.x == 0) input_length[b] = n;
+    if (threadIdx.x == 0) {
+        input_length[b] = n;
+        // The writers drop rows that do not fit (they never write outside a cache head), the attention clamps: the
+        // result is then wrong without a fault, so the caller's mistake is recorded in the device status word.
+        if (n > max_q_len || history[b] + n > session_len || context[b] != history[b] + n) atomicOr(status, kStatusPrefillOverflow);
+    }
     for (int s = threadIdx.x; s < n; s += blockDim.x) padding_offset[t0 + s] = b * max_q_len + s - (t0 + s);
 }
 
@@ -84,7 +91,8 @@ extern "C" int tm_llama_prefill(tm_llama* m, const tm_llama_prefill_state* st, v
     LlamaLinear linear(m->h);
 
     if (rc == TM_OK) {
-        prefill_prepare_kernel<<<B, 256, 0, s>>>(st->cu_seqlens, B, S, pb.pad, pb.len);
+        prefill_prepare_kernel<<<B, 256, 0, s>>>(st->cu_seqlens, B, S, pb.pad, pb.len, st->history_lengths, st->context_lengths,
+                                                 cfg.session_len, m->h->status);
         launched();
     }
     if (rc == TM_OK) {

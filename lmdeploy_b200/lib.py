@@ -150,6 +150,7 @@ SIGNATURES = {
     "tm_llama_load_workspace": (_i, [_vp, C.c_char_p]),
     "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
+    "tm_llama_check_status": (_i, [_vp, _vp, C.POINTER(C.c_uint)]),
     "tm_cache_manager_create": (_i, [C.POINTER(_vp), _sz, _sz, _sz, _sz, _sz, _sz, _sz, _i]),
     "tm_cache_manager_destroy": (_i, [_vp]),
     "tm_cache_create": (_i, [_vp, C.c_uint64, _vp, C.POINTER(TmCacheSequence)]),

@@ -200,6 +200,15 @@ class LlamaModel:
         torch.cuda.current_stream().synchronize()   # ids / cu / hist / ctx are released when this returns
         return hidden
 
+    def check_status(self, stream=None) -> None:
+        """tm_llama_check_status: synchronise the stream and raise if a kernel of this model recorded a fault
+        (a bounded wait that gave up, a prefill past session_len)."""
+        st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        w = C.c_uint(0)
+        rc = _l.lib.tm_llama_check_status(self._m, st, C.byref(w))
+        if rc != _l.TM_OK:
+            raise _l.TmError(rc, f"tm_llama_check_status: device status word 0x{w.value:x}")
+
     def last_launches(self) -> int:
         return int(_l.lib.tm_llama_last_launches(self._m))
 

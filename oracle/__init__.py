@@ -22,6 +22,7 @@ Pin status
   ``tests/golden/ref_kernel_vectors.npz``, which ``tests/test_oracle_ref_vectors.py`` checks on the
   CPU (format bit for bit, the rest within the fp16 tolerances), and
   ``tests/test_gpu_reference_kernels.py`` runs reference kernel, library and oracle side by side
-  on a GPU.  Not pinned: the plain ``rmsnorm`` (its reference file needs the reference's
-  flash-attention sources to link) and ``oracle.decoder`` (the sequencing of the above).
+  on a GPU.  The plain ``rmsnorm`` of ``oracle.norm`` is pinned the same way (``llama_kernels.cu`` is part
+  of that build; the flash-attention entry it references is an empty stub in ``ref_kernels.cu``).
+  Not pinned: ``oracle.decoder`` (the sequencing of the pinned parts).
 """

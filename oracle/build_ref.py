@@ -16,7 +16,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT_DIR, "libtm_ref.so")
-DEFAULT_REFERENCE = os.environ.get("TM_REFERENCE_ROOT", "/root/reference")
+# the reference tree: TM_REFERENCE_ROOT, else a checkout named "reference" beside this repository
+DEFAULT_REFERENCE = os.environ.get("TM_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 REFERENCE_SOURCES = [
     "src/turbomind/kernels/gemm_s_f16/format.cu",
@@ -26,6 +27,7 @@ REFERENCE_SOURCES = [
     "src/turbomind/models/llama/llama_decoder_kernels.cu",
     "src/turbomind/models/llama/llama_kernels.cu",
     "src/turbomind/kernels/unfused_attention_kernels.cu",
+    "src/turbomind/models/llama/LlamaCacheManager.cc",
     "src/turbomind/utils/logger.cc",
     "src/turbomind/utils/Tensor.cc",
 ]

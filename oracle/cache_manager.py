@@ -1,9 +1,12 @@
 """CPU restatement of the reference's KV slab manager policy (LlamaCacheManager, lmdeploy v0.0.9:
 src/turbomind/models/llama/LlamaCacheManager.cc:16-183), with slabs as small integers instead of memory.
 
-Test infrastructure only: nothing under lmdeploy_b200/ imports this module.  Parity unpinned: the reference has no test
-or golden vector for this class and its constructor needs the engine's allocator and logger; this file follows the
-source line by line (linear scans, vector order, FT_CHECK as exceptions)."""
+Test infrastructure only: nothing under lmdeploy_b200/ imports this module.  The reference has no test or golden vector
+for this class; this file follows the source line by line (linear scans, vector order, FT_CHECK as exceptions) and is
+pinned against the reference class itself: LlamaCacheManager.cc is compiled unmodified into oracle/_ref/libtm_ref.so (a
+cudaMalloc allocator stub behind it), tests/golden/make_ref_cache_manager_trace.py recorded its answers to seeded
+operation streams on a B200 (tests/golden/ref_cache_manager_trace.npz, replayed on the CPU by tests/test_cache_manager.py),
+and tests/test_gpu_cache_manager.py runs reference and library side by side."""
 from __future__ import annotations
 
 NEVER = 2 ** 64 - 1   # static_cast<uint64_t>(-1): "in use"

@@ -12,6 +12,7 @@
 //                                                                   invokeTransposeKVCache
 //   src/turbomind/kernels/unfused_attention_kernels.cu              invokeAddFusedQKVBiasTranspose
 //   src/turbomind/utils/logger.cc, src/turbomind/utils/Tensor.cc    (needed by the file above)
+//   src/turbomind/models/llama/LlamaCacheManager.cc                 KV slab manager (host code; entry layer at the end)
 // They build for sm_100a as they are (mma.sync / ldmatrix / cp.async).  llama_kernels.cu also holds the
 // FlashAttentionOp front end, whose implementation needs CUTLASS and is not built: the empty
 // FlashAttentionOpImpl below only satisfies the linker and aborts if it is ever called.
@@ -249,4 +250,123 @@ REF_API int ref_masked_softmax(void* attention_score, const void* qk, const void
     param.linear_bias_slopes = nullptr;
     turbomind::invokeMaskedSoftmax(param, (cudaStream_t)stream);
     return finish((cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// LlamaCacheManager (src/turbomind/models/llama/LlamaCacheManager.{h,cc}), the reference's KV slab manager,
+// compiled unmodified and driven through a flat C layer.  The engine's allocator is replaced by the few
+// lines below (plain cudaMalloc / cudaFree): the manager only calls malloc(size, false) and free(&ptr).
+#include "src/turbomind/models/llama/LlamaCacheManager.h"
+
+#include <cstring>
+
+namespace {
+
+class PlainCudaAllocator: public turbomind::IAllocator {
+public:
+    void* malloc(size_t size, const bool is_set_zero = true, bool is_host = false) override
+    {
+        void* p = nullptr;
+        if (cudaMalloc(&p, size) != cudaSuccess) return nullptr;
+        if (is_set_zero) cudaMemset(p, 0, size);
+        return p;
+    }
+    void free(void** ptr, bool is_host = false) const override
+    {
+        if (ptr && *ptr) cudaFree(*ptr);
+        if (ptr) *ptr = nullptr;
+    }
+    void         setStream(cudaStream_t) override {}
+    cudaStream_t returnStream() override { return nullptr; }
+    void         memSet(void* ptr, const int val, const size_t size) override { cudaMemset(ptr, val, size); }
+
+protected:
+    bool                   isExist(void*) const override { return false; }
+    turbomind::ReallocType isReMalloc(void*, size_t) const override { return turbomind::ReallocType::INCREASE; }
+};
+
+struct RefCacheManager {
+    PlainCudaAllocator            alloc;
+    turbomind::LlamaCacheManager* mgr = nullptr;
+};
+
+void fill(const turbomind::LlamaCacheManager::Sequence& s, unsigned long long* out)
+{
+    // id, max_seq_len, cache_len, token_count, k_cache, v_cache, timestamp
+    out[0] = s.id, out[1] = s.max_seq_len, out[2] = s.cache_len, out[3] = s.token_ids.size();
+    out[4] = (unsigned long long)(uintptr_t)s.k_cache, out[5] = (unsigned long long)(uintptr_t)s.v_cache, out[6] = s.timestamp;
+}
+
+}  // namespace
+
+REF_API void* ref_cache_manager_create(size_t layer_num, size_t head_num, size_t size_per_head, size_t max_seq_len, size_t elem_bits,
+                                       size_t max_entry_count, size_t chunk_size)
+{
+    auto* m = new RefCacheManager();
+    try {
+        m->mgr = new turbomind::LlamaCacheManager(layer_num, head_num, size_per_head, max_seq_len, elem_bits, max_entry_count,
+                                                  chunk_size, /*rank*/ 1, &m->alloc);
+    }
+    catch (const std::exception& e) {
+        std::fprintf(stderr, "ref_cache_manager_create: %s\n", e.what());
+        delete m;
+        return nullptr;
+    }
+    return m;
+}
+
+REF_API void ref_cache_manager_destroy(void* h)
+{
+    auto* m = (RefCacheManager*)h;
+    if (!m) return;
+    delete m->mgr;
+    delete m;
+}
+
+// op: 0 create, 1 fetch.  out[7] as in fill().  Returns 0, or -1 when the reference throws (unknown id, every slab pinned).
+REF_API int ref_cache_get(void* h, int op, unsigned long long id, unsigned long long* out, int* tokens, size_t capacity)
+{
+    auto* m = (RefCacheManager*)h;
+    try {
+        const auto s = op == 0 ? m->mgr->create(id, nullptr) : m->mgr->fetch(id, nullptr);
+        fill(s, out);
+        for (size_t i = 0; i < s.token_ids.size() && i < capacity; ++i) tokens[i] = s.token_ids[i];
+    }
+    catch (const std::exception&) {
+        return -1;
+    }
+    return cudaDeviceSynchronize() == cudaSuccess ? 0 : -2;
+}
+
+// update(seq): the caller hands back what create / fetch returned, with new tokens and cache_len
+REF_API int ref_cache_update(void* h, const unsigned long long* seq, const int* tokens, size_t token_count)
+{
+    auto* m = (RefCacheManager*)h;
+    turbomind::LlamaCacheManager::Sequence s{};
+    s.id = seq[0], s.max_seq_len = seq[1], s.cache_len = seq[2];
+    s.k_cache = (void*)(uintptr_t)seq[4], s.v_cache = (void*)(uintptr_t)seq[5], s.timestamp = seq[6];
+    s.token_ids.assign(tokens, tokens + token_count);
+    try {
+        m->mgr->update(s, nullptr);
+    }
+    catch (const std::exception&) {
+        return -1;
+    }
+    return 0;
+}
+
+REF_API int ref_cache_erase(void* h, unsigned long long id)
+{
+    try {
+        ((RefCacheManager*)h)->mgr->erase(id);
+    }
+    catch (const std::exception&) {
+        return -1;
+    }
+    return 0;
+}
+
+REF_API int ref_cache_contains(void* h, unsigned long long id)
+{
+    return ((RefCacheManager*)h)->mgr->contains(id) ? 1 : 0;
 }

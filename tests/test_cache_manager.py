@@ -154,3 +154,21 @@ def test_random_operations_follow_the_reference_policy(seed, max_entries, chunk)
             if o.contains(i):
                 assert m.tokens(i) == o._entry(i).token_ids
     m.close()
+
+
+@pytest.mark.parametrize("seed,max_entries,chunk", [(0, 4, 2), (1, 7, 3), (2, 1, 1), (3, 16, 16)])
+def test_outcomes_recorded_from_the_reference_manager(seed, max_entries, chunk):
+    """The golden file holds what the reference's own LlamaCacheManager (compiled unmodified, run on a B200 by
+    tests/golden/make_ref_cache_manager_trace.py) answered to a seeded stream of 1500 operations: which slab every
+    create / fetch handed out, cached lengths, token counts, pinned or not, which ids exist after every operation.
+    Both the CPU restatement and the library (host slabs) must give the same answers."""
+    import os
+    from tests import cache_trace as ct
+    assert os.path.exists(ct.GOLDEN), "tests/golden/ref_cache_manager_trace.npz is missing"
+    want = np.load(ct.GOLDEN)[f"rows_{seed}"]
+    ops = ct.gen_ops(seed, max_entries)
+    for adapter in (ct.OracleAdapter(max_entries, chunk), ct.LibAdapter(max_entries, chunk, -1)):
+        got = ct.run(adapter, ops, 2 * max_entries + 2)
+        adapter.close()
+        bad = np.nonzero((got != want).any(axis=1))[0]
+        assert bad.size == 0, f"{type(adapter).__name__}: first difference at operation {bad[0]}: {ops[bad[0]]} got {got[bad[0]]} want {want[bad[0]]}"

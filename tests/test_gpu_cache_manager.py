@@ -2,6 +2,7 @@
 values, usable as the per-sequence cache pointers of the prefill writers."""
 import ctypes as C
 
+import numpy as np
 import pytest
 import torch
 
@@ -50,3 +51,28 @@ def test_slabs_serve_as_kv_cache_of_the_writers():
     torch.cuda.synchronize()
     assert float(kt[0].abs().max()) == 0 and float(vt[0].abs().max()) == 0
     l.lib.tm_cache_manager_destroy(m)
+
+
+@pytest.mark.parametrize("seed,max_entries,chunk", [(0, 4, 2), (1, 7, 3), (2, 1, 1), (3, 16, 16)])
+def test_same_answers_as_the_reference_manager_side_by_side(seed, max_entries, chunk):
+    """The reference's own LlamaCacheManager (LlamaCacheManager.cc compiled unmodified into oracle/_ref, a cudaMalloc
+    allocator stub behind it) and tm_cache_* with device slabs, driven by the same 1500 seeded operations: same slab
+    for every sequence at every step, same lengths, same pinned state, same set of known ids."""
+    import ctypes as C
+    import os
+    from tests import cache_trace as ct
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libtm_ref.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/libtm_ref.so not built (python oracle/build_ref.py needs the reference tree)")
+    ref = C.CDLL(path)
+    if not hasattr(ref, "ref_cache_manager_create"):
+        pytest.skip("oracle/_ref/libtm_ref.so predates the cache manager entry layer")
+    ops = ct.gen_ops(seed, max_entries)
+    a, b = ct.RefAdapter(ref, max_entries, chunk), ct.LibAdapter(max_entries, chunk, torch.cuda.current_device())
+    want, got = ct.run(a, ops, 2 * max_entries + 2), ct.run(b, ops, 2 * max_entries + 2)
+    a.close()
+    b.close()
+    bad = np.nonzero((got != want).any(axis=1))[0]
+    assert bad.size == 0, f"first difference at operation {bad[0]}: {ops[bad[0]]} got {got[bad[0]]} want {want[bad[0]]}"
+    if os.path.exists(ct.GOLDEN):
+        assert np.array_equal(np.load(ct.GOLDEN)[f"rows_{seed}"], want), "the committed golden trace is stale"

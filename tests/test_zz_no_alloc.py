@@ -43,6 +43,32 @@ def test_noalloc_matches_handle_entry_point_twice(n, k, t, fused):
                      rel_slack=2.0 ** -9 if fused else 0.0)
 
 
+def test_noalloc_largest_llama_shape_fits_up_to_eight_tokens():
+    """The un-sharded Llama-2-70B gate_up projection (m = 57344, k = 8192) is the largest shape of the two models:
+    its partial tiles fit the built-in 8 MB up to 8 tokens; at 9..16 tokens the plan needs 8.5 MB and the entry
+    point says so instead of overrunning the array."""
+    from lmdeploy_b200 import lib as l
+    n, k = 57344, 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    A = torch.randint(-2 ** 31, 2 ** 31 - 1, (k, n // 8), dtype=torch.int32, device="cuda", generator=g)   # any nibbles are a weight
+    z = torch.randint(64, 80, (k // 128, n, 1), device="cuda", generator=g).half()
+    s = (torch.rand(k // 128, n, 1, device="cuda", generator=g) * 0.01 + 0.002).half()
+    Q = torch.cat([z, s], dim=-1).contiguous()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    h = l.default_handle(torch.cuda.current_device())
+    for t in (1, 8):
+        x = torch.randn(t, k, device="cuda", generator=g).half()
+        ref = torch.empty(t, n // 2, dtype=torch.float16, device="cuda")
+        out = torch.full((t, n // 2), 123.0, dtype=torch.float16, device="cuda")
+        assert l.lib.tm_gemm_s4_f16(h.ptr, ref.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, None, 0, st) == l.TM_OK
+        assert l.lib.tm_gemm_s4_f16_noalloc(out.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, st) == l.TM_OK
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref), "same kernel, same plan: bit-identical"
+    x = torch.randn(16, k, device="cuda", generator=g).half()
+    out = torch.empty(16, n // 2, dtype=torch.float16, device="cuda")
+    assert l.lib.tm_gemm_s4_f16_noalloc(out.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, 16, k, 128, 1, st) == l.TM_ERR_WORKSPACE
+
+
 def test_noalloc_rejects_what_does_not_fit():
     from lmdeploy_b200 import lib as l
     buf = torch.zeros(1 << 20, dtype=torch.float16, device="cuda")
