@@ -384,6 +384,26 @@ typedef struct tm_llama_prefill_state {
 } tm_llama_prefill_state;
 TM_API int tm_llama_prefill(tm_llama* m, const tm_llama_prefill_state* st, void* stream);
 
+/* config.ini of a TurboMind workspace (`dir`/config.ini, section [llama]: written by
+ * lmdeploy/serve/turbomind/deploy.py:209-239, read by LlamaTritonModel's constructor,
+ * src/turbomind/triton_backend/llama/LlamaTritonModel.cc:118-143) -> tm_llama_config, with the defaults of
+ * handleMissingParams (:59-98).  tensor_para_rank is set to 0: the caller fills in its own rank.  The keys the decode
+ * driver has no use for land in `info` (may be NULL).  TM_ERR_IO: no file or no [llama] section; TM_ERR_INVALID_ARG: a
+ * required key is missing or a value does not parse. */
+typedef struct tm_llama_workspace_info {
+    char model_name[64];
+    char weight_type[16];           /* "int4" for the W4A16 workspaces this library loads */
+    int  start_id, end_id;
+    int  rotary_embedding_dim;
+    int  max_context_token_num;     /* already multiplied by session_len when <= max_batch_size (:146-148) */
+    int  step_length;
+    int  cache_max_entry_count, cache_chunk_size;
+    int  use_context_fmha;
+    int  attn_bias;
+    int  max_position_embeddings, use_dynamic_ntk, use_logn_attn;
+} tm_llama_workspace_info;
+TM_API int tm_llama_read_config(const char* dir, tm_llama_config* cfg, tm_llama_workspace_info* info);
+
 /* Decode state, all device memory owned by the caller:
  *   k_cache_ptrs/v_cache_ptrs  [batch] base pointers; sequence b's cache is
  *                              [num_layer][kv_head_num / tp][session_len][128]

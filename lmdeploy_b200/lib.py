@@ -92,6 +92,15 @@ class TmLlamaConfig(C.Structure):
                 ("tensor_para_rank", C.c_int), ("max_batch_size", C.c_int), ("session_len", C.c_int)]
 
 
+class TmLlamaWorkspaceInfo(C.Structure):
+    """ctypes mirror of ``tm_llama_workspace_info``."""
+    _fields_ = [("model_name", C.c_char * 64), ("weight_type", C.c_char * 16), ("start_id", C.c_int), ("end_id", C.c_int),
+                ("rotary_embedding_dim", C.c_int), ("max_context_token_num", C.c_int), ("step_length", C.c_int),
+                ("cache_max_entry_count", C.c_int), ("cache_chunk_size", C.c_int), ("use_context_fmha", C.c_int),
+                ("attn_bias", C.c_int), ("max_position_embeddings", C.c_int), ("use_dynamic_ntk", C.c_int),
+                ("use_logn_attn", C.c_int)]
+
+
 class TmLlamaLayerWeights(C.Structure):
     """ctypes mirror of ``tm_llama_layer_weights``."""
     _fields_ = [(n, C.c_void_p) for n in (
@@ -148,6 +157,7 @@ SIGNATURES = {
     "tm_llama_set_layer": (_i, [_vp, _i, C.POINTER(TmLlamaLayerWeights)]),
     "tm_llama_set_globals": (_i, [_vp, _vp, _vp, _vp]),
     "tm_llama_load_workspace": (_i, [_vp, C.c_char_p]),
+    "tm_llama_read_config": (_i, [C.c_char_p, C.POINTER(TmLlamaConfig), C.POINTER(TmLlamaWorkspaceInfo)]),
     "tm_llama_decode": (_i, [_vp, C.POINTER(TmLlamaDecodeState), _i, _i, _vp]),
     "tm_llama_last_launches": (C.c_ulonglong, [_vp]),
     "tm_llama_check_status": (_i, [_vp, _vp, C.POINTER(C.c_uint)]),
