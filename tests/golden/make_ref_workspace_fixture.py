@@ -37,9 +37,10 @@ def make_checkpoint(seed=0):
     """HF / AWQ naming: qweight int32 [in, out / 8], qzeros int32 [in / 128, out / 8], scales fp16 [in / 128, out]"""
     cfg, p = HF_CONFIG, {}
     hid, inter = cfg["hidden_size"], cfg["intermediate_size"]
+    kv = cfg["num_key_value_heads"] * 128
     g = torch.Generator().manual_seed(seed)
     for i in range(cfg["num_hidden_layers"]):
-        shapes = {"self_attn.q_proj": (hid, hid), "self_attn.k_proj": (hid, hid), "self_attn.v_proj": (hid, hid), "self_attn.o_proj": (hid, hid),
+        shapes = {"self_attn.q_proj": (hid, hid), "self_attn.k_proj": (kv, hid), "self_attn.v_proj": (kv, hid), "self_attn.o_proj": (hid, hid),
                   "mlp.gate_proj": (inter, hid), "mlp.up_proj": (inter, hid), "mlp.down_proj": (hid, inter)}
         for j, (name, (n, k)) in enumerate(shapes.items()):
             t, _, _ = oawq.make_awq_linear(n, k, 1000 * seed + 10 * i + j, 128, 0.05)
