@@ -277,6 +277,31 @@ def run_gemm_workload(args, rank, world, device):
             us = e0.elapsed_time(e1) * 1e3 / (n_rep * c["reps"])
             b = gemm_bytes(c["n"], c["k"], T, c["fused"])
             per[c["name"]] = dict(us=round(us, 3), gbs=round(b / us * 1e-3, 1), bytes=b)
+        if reflib is None:
+            # the same launches chained by programmatic dependent launch, as the decode driver issues them: a kernel
+            # starts fetching its weights while the one before it drains (launch gap and first-byte latency overlap)
+            h.set_option("pdl_direct", 1)
+            try:
+                for c, ws in zip(cases, weights):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        for i in range(c["reps"]):
+                            one(c, ws, i)
+                    n_rep = max(3, 200 // c["reps"])
+                    g.replay()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record(stream)
+                    for _ in range(n_rep):
+                        g.replay()
+                    e1.record(stream)
+                    torch.cuda.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / (n_rep * c["reps"])
+                    per[c["name"]]["us_chained"] = round(us, 3)
+                    per[c["name"]]["gbs_chained"] = round(per[c["name"]]["bytes"] / us * 1e-3, 1)
+            finally:
+                h.set_option("pdl_direct", 0)
+            h.check_device_status(stream.cuda_stream)
         clocks = sampler.stop()
         ms_e2e = h2d = d2h = None
         if reflib is None:
@@ -303,7 +328,10 @@ def run_gemm_workload(args, rank, world, device):
                      "algorithmic_bytes": dom["bytes"],
                      # DRAM bytes / algorithmic bytes measured with ncu on the qkv and o shapes (profiles/)
                      "traffic": int(dom["bytes"] * (1.03 if T > 16 else 1.0))},
-        "per_kernel": per, "clocks": clocks, "gpu_launches": int(launches),
+        "per_kernel": per,
+        "per_kernel_note": "us: launches back to back on one stream, each waiting for the one before it; us_chained: the same "
+                           "launches with programmatic dependent launch (as inside the decode step)",
+        "clocks": clocks, "gpu_launches": int(launches),
     }
     if reflib is not None:
         mark_reference_kernel_arm(out)
@@ -825,6 +853,10 @@ def run_decode_workload(args, rank, world, device, name):
 
         # ---- per-kernel device time on the same tensors (events around runs of launches) ------
         per = time_decode_kernels(model, st, cfg, B, world, stream, tm, session_len)
+        # the metric's second half, "W4 GEMM HBM GB/s vs peak": the GEMV at one token on the same weights
+        m1 = time_layer_gemms(model, cfg, 1, stream, tm, st.lengths.device, chained=False)
+        m1c = time_layer_gemms(model, cfg, 1, stream, tm, st.lengths.device, chained=True)
+        h.check_device_status(stream.cuda_stream)
 
     ms_step = max_over_ranks(ms / K, world)
     ms_e2e_step = max_over_ranks(ms_e2e / K, world)
@@ -855,6 +887,11 @@ def run_decode_workload(args, rank, world, device, name):
         "step_roofline": {"bytes_per_step_per_gpu": int(total_b), "weights": int(w_b), "lm_head": int(head_b), "kv": int(kvb),
                           "achieved_gbs_per_gpu": round(total_b / (ms_step * 1e-3) * 1e-9, 1),
                           "frac_of_hbm_peak": round(total_b / (ms_step * 1e-3) * 1e-9 / peaks["hbm_gbs"], 4)},
+        "per_kernel_m1": {k: dict(v, frac=round(v["gbs"] / peaks["hbm_gbs"], 4), us_chained=m1c[k]["us"], gbs_chained=m1c[k]["gbs"],
+                                  frac_chained=round(m1c[k]["gbs"] / peaks["hbm_gbs"], 4)) for k, v in m1.items()},
+        "per_kernel_m1_note": "gemm_s4_f16_small_kernel at 1 token on this model's weights (per-rank shapes); us / gbs / frac: launches "
+                              "back to back, each waiting for the one before it; *_chained: with programmatic dependent launch, as "
+                              "inside the decode step",
         "per_kernel": per,
         "per_kernel_note": "each kernel timed alone (no overlap with its neighbours), a different layer's weights / cache every "
                            "launch (L2-cold): the sum exceeds ms_per_step, where programmatic dependent launch overlaps them",
@@ -864,6 +901,43 @@ def run_decode_workload(args, rank, world, device, name):
     if rank == 0 and world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_decode_baseline(MODEL_SHAPES[attr], B, int(round(plan["mean_len"])), seconds=15.0)
     model.close()
+    return out
+
+
+def time_layer_gemms(model, cfg, tokens, stream, tm, dev, chained):
+    """Device time of the four W4A16 projections of a layer at `tokens` tokens, each timed alone over the model's own
+    layers (a different layer's weights every launch: 3.4 GB in all, far beyond L2).  chained: launches carry the
+    programmatic-serialization attribute, as in the decode step."""
+    layers = [model._keep[i:i + 6] for i in range(0, 6 * cfg.num_layer, 6)]   # norm, norm, qkv, o, w13, w2
+    op = tm.LlamaLinear(dev.index)
+    h = model.handle
+    out = {}
+    h.set_option("pdl_direct", int(chained))
+    try:
+        for nm, idx, fused in (("qkv", 2, False), ("o", 3, False), ("w13+silu", 4, True), ("w2", 5, False)):
+            w0 = layers[0][idx]
+            x = torch.randn(tokens, w0.input_dims, device=dev).half()
+            y = torch.empty(tokens, w0.output_dims // (2 if fused else 1), dtype=torch.float16, device=dev)
+            launch = lambda i: op.forward(y, x, tokens, layers[i % cfg.num_layer][idx], op.kFusedSiluFfn if fused else op.kGemm)
+            n_it = max(cfg.num_layer, 32)
+            for i in range(3):
+                launch(i)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                for i in range(n_it):
+                    launch(i)
+            gr.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            gr.replay()
+            b.record(stream)
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / n_it
+            nb = gemm_bytes(w0.output_dims, w0.input_dims, tokens, fused)
+            out[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), bytes=int(nb))
+    finally:
+        h.set_option("pdl_direct", 0)
     return out
 
 

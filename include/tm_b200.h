@@ -59,6 +59,9 @@ TM_API int tm_check_device_status(tm_handle* h, void* stream, unsigned* word);
 TM_API unsigned long long tm_launch_count(const tm_handle* h);
 /* Tuning knobs of this handle (no reference counterpart; the same knobs are read from the environment
  * at tm_create).  `name`: "gemm_tc_min_n" (token count from which the tcgen05 GEMM is used),
+ * "pdl_direct" (1: GEMM / attention calls made directly through the handle launch with programmatic stream
+ * serialization, as the decode driver's do; only where no kernel ahead in the stream writes weights or cached rows),
+ * "gemm_wait_cycles" (bound of the tcgen05 GEMM's wait for the partners of a split tile, 0 = default; tests),
  * "mmha_chunk" (cached tokens per KV split, 0 = automatic), "mmha_warps" (warps per attention CTA: 1, 2,
  * 4 or 0 = automatic), "pdl" (1 = tm_llama_decode launches with programmatic dependent launch).
  * Returns TM_ERR_INVALID_ARG for an unknown name or value. */

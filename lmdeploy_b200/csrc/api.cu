@@ -126,6 +126,12 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     else if (n == "pdl" && (value == 0 || value == 1)) {
         h->pdl = value;
     }
+    else if (n == "pdl_direct" && (value == 0 || value == 1)) {
+        // GEMM and attention calls made DIRECTLY through this handle also launch with programmatic stream
+        // serialization: the kernel may start (and request the packed weights / cache rows of earlier steps) while the
+        // kernel before it in the stream still runs.  Only for callers whose preceding kernels never write those.
+        h->pdl_direct = value;
+    }
     else if (n == "gemm_wait_cycles" && value >= 0) {
         // bound, in SM clock cycles, of the tcgen05 GEMM's wait for the partners of a split column tile
         // (0 = the default of about a quarter of a second); tests set a tiny value to see the time-out path
@@ -224,7 +230,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
             p.max_wait_cycles = h->gemm_wait_cycles;
-            cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
+            cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream, g_pdl != 0 || h->pdl_direct != 0);
             h->launches += 1;
             if (e != cudaSuccess) {
                 h->last_cuda_error = (int)e;
@@ -277,7 +283,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
         p.K          = k;
         p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
 
-        cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream, g_pdl != 0);
+        cudaError_t e = gemm_small_launch(pl, p, (cudaStream_t)stream, g_pdl != 0 || h->pdl_direct != 0);
         h->launches += 1;
         if (e != cudaSuccess) {
             h->last_cuda_error = (int)e;
@@ -368,7 +374,7 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     p.counters        = h->attn_counters;
     p.status          = h->status;
 
-    cudaError_t e = mmha_launch(pl, p, int8, (cudaStream_t)stream, g_pdl != 0);
+    cudaError_t e = mmha_launch(pl, p, int8, (cudaStream_t)stream, g_pdl != 0 || h->pdl_direct != 0);
     h->launches += 1;
     if (e != cudaSuccess) {
         h->last_cuda_error = (int)e;

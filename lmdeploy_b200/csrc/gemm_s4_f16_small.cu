@@ -28,6 +28,31 @@
 
 #include <mutex>
 
+#ifdef TM_B200_GEMM_TRACE
+// Developer build only (never defined by lmdeploy_b200/build.py): per-CTA time stamps of one launch.
+__device__ unsigned long long g_small_trace[640][4];  // start, first data, loop end, end (globaltimer ns)
+__device__ int                g_small_launch;
+extern "C" __attribute__((visibility("default"))) int tm_dev_gemv_trace(unsigned long long* out, int want_launch)
+{
+    cudaMemcpyFromSymbol(out, g_small_trace, sizeof(unsigned long long) * 640 * 4);
+    int z = -want_launch;   // the launch that reaches 0 is recorded
+    cudaMemcpyToSymbol(g_small_launch, &z, sizeof(z));
+    return 0;
+}
+__device__ __forceinline__ unsigned long long small_globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define SMALL_TRACE(slot)                                                                                              \
+    do {                                                                                                                   \
+        if (trace_on && threadIdx.x == 0 && blockIdx.x < 640) g_small_trace[blockIdx.x][slot] = small_globaltimer();       \
+    } while (0)
+#else
+#define SMALL_TRACE(slot) do { } while (0)
+#endif
+
 namespace tmb {
 
 namespace {
@@ -44,7 +69,7 @@ constexpr int kSlabBytes    = kTilesPerWarp * kTileBytes;    // a warp's part of
 constexpr int kWarpStage    = 2 * kSlabBytes + 256;          // two slabs + {zero, scale} of the 64 columns
 
 // stages of the cp.async rings per token-tile count
-__host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 4 : 6; }
+__host__ __device__ constexpr int stages_for(int nt) { return nt == 1 ? 5 : 6; }
 // co-resident CTAs per SM
 __host__ __device__ constexpr int ctas_per_sm_for(int nt) { return nt == 1 ? 2 : 1; }
 
@@ -106,6 +131,10 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
     const int lane = tid & 31;
     const int r    = lane >> 2;  // fragment row
     const int c    = lane & 3;   // fragment column pair
+#ifdef TM_B200_GEMM_TRACE
+    const bool trace_on = *(volatile int*)&g_small_launch == 0 && blockIdx.y == 0;
+    SMALL_TRACE(0);
+#endif
 
     // token chunk handled by this CTA row
     const int t0     = blockIdx.y * TP;
@@ -232,6 +261,7 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
         for (int u = 0; u < 2; ++u) {
             if (it == 0 && u == 0) {
                 cp_async_wait<0>();  // everything requested so far: the first units and their activations
+                SMALL_TRACE(1);
             }
             else {
                 cp_async_wait<ST - 2>();
@@ -321,6 +351,7 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
                     tot[w][a][j][2] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][0], acc[w][a][j][2]), tot[w][a][j][2]);
                     tot[w][a][j][3] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[j][1], acc[w][a][j][3]), tot[w][a][j][3]);
                 }
+        if (it + 2 >= n_units) SMALL_TRACE(2);
         const int  this_jt = jt;
         const int  tile0   = jt * kTilesPerUnit;
         const int  ntw     = min(kTilesPerUnit, n_tiles32 - tile0) - my_t0;  // tiles of this warp that exist
@@ -389,9 +420,10 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
                             const int t = j * 8 + 2 * c + (i & 1);
                             if (t < t_rows) __stcg(slot + t * kUnitCols + n, tot[w][a][j][i]);
                         }
-            __threadfence();
+            // the barrier orders every thread's stores before the fence of the one thread that takes the ticket
             __syncthreads();
             if (tid == 0) {
+                __threadfence();
                 int*      counter = p.counters + (size_t)blockIdx.y * p.n_col_tiles + this_jt;
                 const int ticket  = atomicAdd(counter, 1);
                 const int is_last = (ticket == n_split - 1);
@@ -456,6 +488,11 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
                     for (int i = 0; i < 4; ++i) tot[w][a][j][i] = 0.f;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
+#ifdef TM_B200_GEMM_TRACE
+    SMALL_TRACE(3);
+    __syncthreads();
+    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(&g_small_launch, 1);
+#endif
 }
 
 }  // namespace
