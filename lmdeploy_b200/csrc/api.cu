@@ -293,7 +293,8 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     return TM_OK;
 }
 
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order);
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order,
+                        const tmb::MmhaSeqDesc* desc = nullptr, const float2* rope_table = nullptr);
 
 extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* stream)
 {
@@ -302,7 +303,8 @@ extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* strea
 
 // pos_from_length: the RoPE position of sequence b is length_per_sample[b] (what the engine's
 // timestep - padding evaluates to), so that nothing in the launch depends on the step number.
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order)
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order,
+                        const tmb::MmhaSeqDesc* desc, const float2* rope_table)
 {
     if (!h || !a) return TM_ERR_INVALID_ARG;
     if (!a->out || !a->q || !a->k || !a->v || !a->length_per_sample || !a->k_cache_per_sample || !a->v_cache_per_sample) {
@@ -353,6 +355,9 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     p.finished        = a->finished;
     p.padding         = a->total_padding_tokens;
     p.order           = order;
+    p.desc            = desc;
+    // the table holds plain rotary coefficients of the cached length: usable when that is the position asked for
+    p.rope_table      = (pos_from_length && !a->use_dynamic_ntk && a->rotary_embedding_dim == 128) ? rope_table : nullptr;
     p.B               = a->batch_size;
     p.H               = a->num_heads;
     p.Hkv             = a->num_kv_heads;

@@ -9,7 +9,8 @@
 #include <cstring>
 #include <new>
 
-int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order);
+int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order,
+                        const tmb::MmhaSeqDesc* desc = nullptr, const float2* rope_table = nullptr);
 
 namespace tmb {
 
@@ -41,32 +42,43 @@ int LlamaLinear::forward(void* out, const void* in, int batch_size, const LlamaD
 
 namespace {
 
-// input token and activity of every sequence for this step
+// Per step, one block of 64 threads per sequence: input token and activity, the attention's launch order (longest
+// cached sequence first) with everything the attention needs to know about the sequence gathered into one record,
+// and the rotation coefficients of the sequence's position (the same for every layer and head: computed here once
+// with the calls the attention kernel would make, decoder_masked_multihead_attention_utils.h:885-897).
 __global__ void prepare_step_kernel(const int* step, const int* start_step, const int* forced_ids, const int* picked,
                                     int* ids_in, unsigned char* inactive, int B, int max_steps, int vocab, const int* lengths,
-                                    int* order)
+                                    int* order, MmhaSeqDesc* desc, void* const* k_ptrs, void* const* v_ptrs, float2* rope_table,
+                                    float rope_base, int rot_dim)
 {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= B) return;
-    {
-        // attention launch order: longest cached sequence first (rank by length, ties by index)
-        const int mine = lengths[b];
-        int       rank = 0;
-        for (int j = 0; j < B; ++j) {
-            const int l = lengths[j];
-            rank += (l > mine || (l == mine && j < b)) ? 1 : 0;
-        }
-        order[rank] = b;
+    const int b    = blockIdx.x;
+    const int mine = lengths[b];
+    if (threadIdx.x < 64 && 2 * (int)threadIdx.x < rot_dim) {
+        const float inv_freq = (float)mine / powf(rope_base, (float)(2 * threadIdx.x) / (float)rot_dim);
+        float       sn, cs;
+        sincosf(inv_freq, &sn, &cs);
+        rope_table[(size_t)b * 64 + threadIdx.x] = make_float2(cs, sn);
     }
-    const int s   = *step;
+    if (threadIdx.x != 0) return;
+    const int  s   = *step;
     const bool off = s >= max_steps || (start_step != nullptr && s < start_step[b]);
-    inactive[b]   = off ? 1 : 0;
-    int id        = picked[b];
+    inactive[b]    = off ? 1 : 0;
+    int id         = picked[b];
     if (!off && forced_ids != nullptr) {
         const int f = forced_ids[(size_t)s * B + b];
         if (f >= 0) id = f;
     }
     ids_in[b] = min(max(id, 0), vocab - 1);
+    // attention launch order: longest cached sequence first (rank by length, ties by index)
+    int rank = 0;
+    for (int j = 0; j < B; ++j) {
+        const int l = lengths[j];
+        rank += (l > mine || (l == mine && j < b)) ? 1 : 0;
+    }
+    order[rank] = b;
+    MmhaSeqDesc d;
+    d.k_cache = k_ptrs[b], d.v_cache = v_ptrs[b], d.length = mine, d.seq = b, d.finished = off ? 1 : 0, d.reserved = 0;
+    desc[rank] = d;
 }
 
 // x[b, :] = table[ids[b], :]   (kernels/decoding_kernels.cu:69-106)
@@ -190,9 +202,9 @@ int run_step(StepCtx& c)
         ~PdlScope() { g_pdl = 0; }
     } pdl_scope(m.h->pdl);
 
-    prepare_step_kernel<<<(B + 127) / 128, 128, 0, s>>>(
-        st.step, st.start_step, st.forced_ids, m.picked, m.ids_in, m.inactive, B, st.max_steps, cfg.vocab_size,
-        st.sequence_lengths, m.order);
+    prepare_step_kernel<<<B, 64, 0, s>>>(st.step, st.start_step, st.forced_ids, m.picked, m.ids_in, m.inactive, B, st.max_steps,
+                                         cfg.vocab_size, st.sequence_lengths, m.order, m.seq_desc, st.k_cache_ptrs, st.v_cache_ptrs,
+                                         m.rope_table, cfg.rope_theta, cfg.size_per_head);
     if (!c.ok_cuda()) return c.rc;
     embedding_lookup_kernel<<<B, 128, 0, s>>>(m.x, (const __half*)m.tok_embeddings, m.ids_in, m.hidden);
     if (!c.ok_cuda()) return c.rc;
@@ -236,7 +248,7 @@ int run_step(StepCtx& c)
         a.attention_k_zp             = w.past_kv_scale[1];
         a.attention_v_scale          = w.past_kv_scale[2];
         a.attention_v_zp             = w.past_kv_scale[3];
-        if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order))) return c.rc;
+        if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order, m.seq_desc, m.rope_table))) return c.rc;
         if (!c.ok(linear.forward(m.hbuf, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
         if (m.comm && m.comm->world > 1) {
             if (!c.ok(tm_allreduce_sum_f16(m.comm, m.hbuf, (size_t)B * m.hidden, s))) return c.rc;  // :292-297
@@ -345,6 +357,8 @@ extern "C" int tm_llama_create(tm_llama** out, tm_handle* h, tm_comm* comm, cons
     alloc((void**)&m->picked, B * 4);
     alloc((void**)&m->inactive, B);
     alloc((void**)&m->order, (size_t)B * sizeof(int));
+    alloc((void**)&m->seq_desc, (size_t)B * sizeof(MmhaSeqDesc));
+    alloc((void**)&m->rope_table, (size_t)B * 64 * sizeof(float2));
     alloc(&m->cublas_ws, 32u << 20);
     if (e == cudaSuccess) e = cudaMemset(m->picked, 0, B * 4);
     bool ok = e == cudaSuccess;
@@ -366,7 +380,7 @@ extern "C" int tm_llama_destroy(tm_llama* m)
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
     if (m->cublas) cublasDestroy(m->cublas);
     for (void* p : {(void*)m->x, (void*)m->hbuf, (void*)m->qkv, (void*)m->ctx, (void*)m->ffn, (void*)m->logits_local,
-                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, m->cublas_ws}) {
+                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, (void*)m->seq_desc, (void*)m->rope_table, m->cublas_ws}) {
         if (p) cudaFree(p);
     }
     for (void* p : m->owned) cudaFree(p);

@@ -64,6 +64,8 @@ struct tm_llama {
     float * logits_local = nullptr, *logits = nullptr;
     int *   ids_in = nullptr, *picked = nullptr;
     int*    order = nullptr;  // sequences by cached length, longest first (attention launch order)
+    tmb::MmhaSeqDesc* seq_desc   = nullptr;  // the same order, with lengths, cache pointers and flags gathered per sequence
+    float2*           rope_table = nullptr;  // [batch][64] {cos, sin} of every sequence's position in this step
     unsigned char* inactive = nullptr;
 
     // activations of tm_llama_prefill, sized by the largest call so far

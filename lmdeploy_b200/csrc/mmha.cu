@@ -21,6 +21,31 @@
 
 #include <cfloat>
 
+#ifdef TM_B200_GEMM_TRACE
+// Developer build only (never defined by lmdeploy_b200/build.py): per-CTA time stamps of one launch.
+__device__ unsigned long long g_mmha_trace[4096][12];
+__device__ int                g_mmha_launch;
+extern "C" __attribute__((visibility("default"))) int tm_dev_mmha_trace(unsigned long long* out, int want_launch)
+{
+    cudaMemcpyFromSymbol(out, g_mmha_trace, sizeof(unsigned long long) * 4096 * 12);
+    int z = -want_launch;
+    cudaMemcpyToSymbol(g_mmha_launch, &z, sizeof(z));
+    return 0;
+}
+__device__ __forceinline__ unsigned long long mmha_globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define MMHA_TRACE(slot)                                                                                               \
+    do {                                                                                                                   \
+        if (trace_on && threadIdx.x == 0) g_mmha_trace[trace_id][slot] = mmha_globaltimer();                               \
+    } while (0)
+#else
+#define MMHA_TRACE(slot) do { } while (0)
+#endif
+
 namespace tmb {
 namespace {
 
@@ -129,13 +154,32 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int lane = tid & 31;
     const int g    = lane >> 2;
     const int c    = lane & 3;
+#ifdef TM_B200_GEMM_TRACE
+    const int  trace_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    const bool trace_on = *(volatile int*)&g_mmha_launch == 0 && trace_id < 4096;
+    MMHA_TRACE(0);
+#endif
 
     // `order`, `finished` and `lengths` are written by kernels earlier in the stream, but never by the
     // kernel directly ahead of this one (a GEMM), whose own wait has already covered them.  A CTA
     // that has nothing to do must still wait for that kernel before it exits: a grid that completes
     // without waiting would let the kernel after this one start while the one before it still runs.
-    const int bi = p.order != nullptr ? p.order[blockIdx.z] : blockIdx.z;
-    if (p.finished != nullptr && p.finished[bi]) {
+    int                  bi, tlength, fin = 0;
+    const unsigned char *k_base, *v_base;
+    if (p.desc != nullptr) {
+        const uint4 d0 = __ldg(reinterpret_cast<const uint4*>(p.desc + blockIdx.z));
+        const uint4 d1 = __ldg(reinterpret_cast<const uint4*>(p.desc + blockIdx.z) + 1);
+        k_base  = reinterpret_cast<const unsigned char*>(((unsigned long long)d0.y << 32) | d0.x);
+        v_base  = reinterpret_cast<const unsigned char*>(((unsigned long long)d0.w << 32) | d0.z);
+        tlength = (int)d1.x, bi = (int)d1.y, fin = (int)d1.z;
+    }
+    else {
+        bi = p.order != nullptr ? p.order[blockIdx.z] : blockIdx.z;
+        if (p.finished != nullptr) fin = p.finished[bi];
+        tlength = 0;
+        k_base = v_base = nullptr;
+    }
+    if (fin) {
         pdl_wait();
         pdl_launch_dependents();
         return;  // template.cuh:1298-1300: neither out nor the cache is touched
@@ -147,7 +191,11 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int head0  = kvh * rep + hb * kHeadsPerCta;      // first query head of this CTA
     const int nheads = min(kHeadsPerCta, rep - hb * kHeadsPerCta);
 
-    const int tlength = p.lengths[bi];
+    if (p.desc == nullptr) {
+        tlength = p.lengths[bi];
+        k_base  = reinterpret_cast<const unsigned char*>(p.k_cache[bi]);
+        v_base  = reinterpret_cast<const unsigned char*>(p.v_cache[bi]);
+    }
     const int first   = max(0, tlength + 1 - p.S_max);
     const int n_past  = tlength - first;
     const int n_split = max(1, (n_past + p.chunk - 1) / p.chunk);
@@ -162,10 +210,8 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     const int  s1         = min(s0 + p.chunk, tlength);
     const int  n_blocks   = (max(s1 - s0, 0) + kBlockTok - 1) / kBlockTok;
 
-    const unsigned char* kc =
-        reinterpret_cast<const unsigned char*>(p.k_cache[bi]) + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
-    const unsigned char* vc =
-        reinterpret_cast<const unsigned char*>(p.v_cache[bi]) + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
+    const unsigned char* kc = k_base + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
+    const unsigned char* vc = v_base + (p.cache_offset + (size_t)kvh * p.S_max * kD) * (ROWB / kD);
 
     // ---------------------------------------------------------------- KV ring: start the loads
     unsigned char* my_ring = ring + warp * WARPB;
@@ -196,20 +242,29 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
         }
     };
     const int my_blocks = (n_blocks > warp) ? (n_blocks - warp + kWarps - 1) / kWarps : 0;
+    // every stage of the ring is requested up front: nothing is being read yet
 #pragma unroll
-    for (int sidx = 0; sidx < NSTAGE - 1; ++sidx) {
+    for (int sidx = 0; sidx < NSTAGE; ++sidx) {
         if (sidx < my_blocks) {
             issue_block(sidx, sidx);
         }
         cp_async_commit();
     }
 
-    // The cache rows requested above were written by earlier steps; q, k, v of the new token come
-    // from the kernel before this one.
-    pdl_wait();
-    pdl_launch_dependents();
+    MMHA_TRACE(1);   // first copies issued
 
     // ---------------------------------------------------------------- q (+k, v of the new token)
+    // The rotation coefficients depend on the position only: they are taken from the table the decode driver fills
+    // once per step (positions do not depend on layer or head), or worked out here, before the wait for the kernel
+    // ahead of this one.  After the wait every thread requests all of its q / k / v values at once (one round trip to
+    // L2, not one per row) and only then rotates and stores them.
+    constexpr int kPairThreads = kThreads < 64 ? kThreads : 64;
+    constexpr int kParts       = kThreads / kPairThreads;                          // 1 or 2 threads share a pair index
+    constexpr int kPairIters   = 64 / kPairThreads;                                // pair indices per thread
+    constexpr int kRowIters    = (kHeadsPerCta + 2 + kParts - 1) / kParts;         // rows per thread: 8 query heads, k, v
+    const int     q_part       = tid / kPairThreads;                               // which rows this thread handles
+    float         cs[kPairIters], sn[kPairIters];
+    float         logn = 1.f;
     {
         float base = p.rope_base;
         if (p.use_dynamic_ntk) {
@@ -220,64 +275,91 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
                 base *= powf(alpha, (float)p.rot_dim / ((float)p.rot_dim - 2.f));
             }
         }
-        float logn = 1.f;
         if (p.use_logn && (float)(tlength + 1) > (float)p.max_pos) {
             logn = log2f((float)(tlength + 1)) / log2f((float)p.max_pos);  // utils.h:854-860
         }
-        const int   pad  = p.padding ? p.padding[bi] : 0;
-        const float pos  = p.pos_from_length ? (float)tlength : (float)(p.timestep - pad);  // template.cuh:1391-1395
-        constexpr int kPairThreads = kThreads < 64 ? kThreads : 64;
-        constexpr int kParts       = kThreads / kPairThreads;  // 1 or 2 threads share a pair index
-        const int     part         = tid / kPairThreads;       // which rows this thread handles
-        for (int pr = tid % kPairThreads; pr < 64; pr += kPairThreads) {  // pair index: elements 2pr, 2pr+1
-        float       cs = 1.f, sn = 0.f;
-        const bool  rot = 2 * pr < p.rot_dim;
-        if (rot) {
-            const float inv_freq = pos / powf(base, (float)(2 * pr) / (float)p.rot_dim);  // utils.h:885-889
-            sincosf(inv_freq, &sn, &cs);
-        }
-        const __half* xrow = p.qkv + (size_t)bi * p.stride;
-        // rows 0..7: query heads (zero beyond nheads); row 8: k; row 9: v
-        for (int row = part; row < kHeadsPerCta + 2; row += kParts) {
-            const bool is_q = row < kHeadsPerCta;
-            if (!is_q && !last_split) {
-                continue;
-            }
-            int col;  // column of the fused qkv row
-            if (is_q) {
-                col = (head0 + row) * kD;
-            }
-            else if (row == kHeadsPerCta) {
-                col = (p.H + kvh) * kD;
-            }
-            else {
-                col = (p.H + p.Hkv + kvh) * kD;
-            }
-            float2 x = make_float2(0.f, 0.f);
-            if (!is_q || row < nheads) {
-                __half2 h = *reinterpret_cast<const __half2*>(xrow + col + 2 * pr);
-                if (p.bias) {
-                    h = __hadd2(h, *reinterpret_cast<const __half2*>(p.bias + col + 2 * pr));  // fp16 add, :1381-1382
+        const int   pad = p.padding ? p.padding[bi] : 0;
+        const float pos = p.pos_from_length ? (float)tlength : (float)(p.timestep - pad);  // template.cuh:1391-1395
+#pragma unroll
+        for (int it = 0; it < kPairIters; ++it) {
+            const int pr = tid % kPairThreads + it * kPairThreads;  // pair index: elements 2pr, 2pr+1
+            cs[it] = 1.f, sn[it] = 0.f;
+            if (2 * pr < p.rot_dim) {
+                if (p.rope_table != nullptr) {
+                    const float2 t = __ldg(p.rope_table + (size_t)bi * 64 + pr);
+                    cs[it] = t.x, sn[it] = t.y;
                 }
-                x = __half22float2(h);
+                else {
+                    const float inv_freq = pos / powf(base, (float)(2 * pr) / (float)p.rot_dim);  // utils.h:885-889
+                    sincosf(inv_freq, &sn[it], &cs[it]);
+                }
             }
-            if (rot && row <= kHeadsPerCta) {  // q and k only
-                const float2 y = make_float2(cs * x.x - sn * x.y, cs * x.y + sn * x.x);  // utils.h:891-897
-                x              = y;
-            }
-            __half2 h = __floats2half2_rn(x.x, x.y);
-            if (is_q && logn != 1.f) {
-                h = __hmul2(h, __float2half2_rn(logn));
-            }
-            __half* dstp = is_q ? q_s + row * kD : (row == kHeadsPerCta ? knew_s : vnew_s);
-            *reinterpret_cast<__half2*>(dstp + 2 * pr) = h;
-        }
         }
     }
+    MMHA_TRACE(8);   // coefficients done
+
+    // The cache rows requested above were written by earlier steps; q, k, v of the new token come
+    // from the kernel before this one.
+    pdl_wait();
+    pdl_launch_dependents();
+    {
+        const __half* xrow = p.qkv + (size_t)bi * p.stride;
+        __half2       raw[kPairIters][kRowIters];
+        // rows 0..7: query heads (zero beyond nheads); row 8: k; row 9: v
+        auto column_of = [&](int row) {
+            return row < kHeadsPerCta ? (head0 + row) * kD : (row == kHeadsPerCta ? (p.H + kvh) * kD : (p.H + p.Hkv + kvh) * kD);
+        };
+        auto wanted = [&](int row) {
+            return row < kHeadsPerCta + 2 && (row < kHeadsPerCta ? row < nheads : last_split);
+        };
+#pragma unroll
+        for (int it = 0; it < kPairIters; ++it) {
+            const int pr = tid % kPairThreads + it * kPairThreads;
+#pragma unroll
+            for (int ri = 0; ri < kRowIters; ++ri) {
+                const int row = q_part + ri * kParts;
+                raw[it][ri]   = __float2half2_rn(0.f);
+                if (wanted(row)) {
+                    const int col = column_of(row);
+                    raw[it][ri]   = *reinterpret_cast<const __half2*>(xrow + col + 2 * pr);
+                    if (p.bias) {
+                        raw[it][ri] = __hadd2(raw[it][ri], *reinterpret_cast<const __half2*>(p.bias + col + 2 * pr));  // fp16 add, :1381-1382
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < kPairIters; ++it) {
+            const int  pr  = tid % kPairThreads + it * kPairThreads;
+            const bool rot = 2 * pr < p.rot_dim;
+#pragma unroll
+            for (int ri = 0; ri < kRowIters; ++ri) {
+                const int  row  = q_part + ri * kParts;
+                const bool is_q = row < kHeadsPerCta;
+                if (row >= kHeadsPerCta + 2 || (!is_q && !last_split)) continue;
+                float2 x = __half22float2(raw[it][ri]);
+                if (rot && row <= kHeadsPerCta) {  // q and k only
+                    x = make_float2(cs[it] * x.x - sn[it] * x.y, cs[it] * x.y + sn[it] * x.x);  // utils.h:891-897
+                }
+                __half2 h = __floats2half2_rn(x.x, x.y);
+                if (is_q && logn != 1.f) {
+                    h = __hmul2(h, __float2half2_rn(logn));
+                }
+                __half* dstp = is_q ? q_s + row * kD : (row == kHeadsPerCta ? knew_s : vnew_s);
+                *reinterpret_cast<__half2*>(dstp + 2 * pr) = h;
+            }
+        }
+    }
+    MMHA_TRACE(9);   // q, k, v staged by this thread
     __syncthreads();
+    MMHA_TRACE(10);
 
     // per-head sum of q (for a non-zero K zero point) and the new token's own score
     for (int h = warp; h < kHeadsPerCta; h += kWarps) {
+        if (h >= nheads) {  // rows of zeros
+            if (lane == 0) sumq_s[h] = snew_s[h] = 0.f;
+            continue;
+        }
         float sq = 0.f, dot = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -298,37 +380,7 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
         }
     }
 
-    // the new token goes into the cache (one CTA per sequence and KV head does it)
-    if (last_split && hb == 0) {
-        const size_t   slot = (size_t)(tlength % p.S_max) * ROWB;
-        unsigned char* kd   = const_cast<unsigned char*>(kc) + slot;
-        unsigned char* vd   = const_cast<unsigned char*>(vc) + slot;
-        if (INT8) {
-            for (int t2 = tid; t2 < 64; t2 += kThreads) {
-                const bool          is_v = t2 >= 32;
-                const int           d    = (t2 & 31) * 4;
-                const __half*       src  = is_v ? vnew_s : knew_s;
-                const float         sc   = is_v ? p.v_scale : p.k_scale;
-                const float         zp   = is_v ? p.v_zp : p.k_zp;
-                uint32_t            w    = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // template.cuh:976-981: round(clamp((x - zp) / scale)), round = half away from zero
-                    float v = __fdiv_rn(__half2float(src[d + i]) - zp, sc);
-                    v       = fmaxf(-128.f, fminf(127.f, v));
-                    w |= ((uint32_t)(int)roundf(v) & 0xffu) << (8 * i);
-                }
-                *reinterpret_cast<uint32_t*>((is_v ? vd : kd) + d) = w;
-            }
-        }
-        else {
-            if (tid < kD / 8) {
-                const int d = tid * 8;  // 16 bytes of K and of V per thread
-                *reinterpret_cast<uint4*>(kd + d * 2) = *reinterpret_cast<const uint4*>(knew_s + d);
-                *reinterpret_cast<uint4*>(vd + d * 2) = *reinterpret_cast<const uint4*>(vnew_s + d);
-            }
-        }
-    }
+    MMHA_TRACE(11);  // sums done
     __syncthreads();
 
     // ---------------------------------------------------------------- Q fragments, softmax state
@@ -364,9 +416,11 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     }
 
     // ---------------------------------------------------------------- main loop over this warp's blocks
+    MMHA_TRACE(2);   // prologue done
     for (int blk = 0; blk < my_blocks; ++blk) {
-        cp_async_wait<NSTAGE - 2>();
+        cp_async_wait<NSTAGE - 1>();   // block blk has landed; the NSTAGE - 1 blocks after it may still be on their way
         __syncwarp();
+        if (blk == 0) MMHA_TRACE(3);   // first block landed
         const int            stage = blk % NSTAGE;
         const unsigned char* ks    = my_ring + stage * 2 * TILEB;
         const unsigned char* vs    = ks + TILEB;
@@ -515,14 +569,17 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
             psum[0] = psum[1] = psum[2] = psum[3] = 0.f;
         }
 
+        // every lane is done with this stage: refill it at once (NSTAGE - 1 blocks stay in flight during the math)
         __syncwarp();
-        if (blk + NSTAGE - 1 < my_blocks) {
-            issue_block(blk + NSTAGE - 1, (blk + NSTAGE - 1) % NSTAGE);
+        if (blk + NSTAGE < my_blocks) {
+            issue_block(blk + NSTAGE, stage);
         }
         cp_async_commit();
     }
     cp_async_wait<0>();
+    MMHA_TRACE(4);   // warp 0 done with its blocks
     __syncthreads();
+    MMHA_TRACE(5);   // all warps done
 
     // ---------------------------------------------------------------- merge the warps (ring is free now)
     // part[w]: m[8] | l[8] | o[8 heads][128]   (fp32, real units)
@@ -553,10 +610,14 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
             // row mapping of accumulator a: int8: d = 4(g + 8(a/2)) + 2(a&1) + {0,1}; fp16: d = 2(g + 8a) + {0,1}
             const int d = INT8 ? 4 * (g + 8 * (a >> 1)) + 2 * (a & 1) : 2 * (g + 8 * a);
             float*    o = mine + 16;
-            o[(2 * c) * kD + d]         = fmaf(vs0, acc[a][0] - off0, vz * l0);
-            o[(2 * c + 1) * kD + d]     = fmaf(vs0, acc[a][1] - off1, vz * l1);
-            o[(2 * c) * kD + d + 1]     = fmaf(vs0, acc[a][2] - off0, vz * l0);
-            o[(2 * c + 1) * kD + d + 1] = fmaf(vs0, acc[a][3] - off1, vz * l1);
+            if (2 * c < nheads) {
+                o[(2 * c) * kD + d]     = fmaf(vs0, acc[a][0] - off0, vz * l0);
+                o[(2 * c) * kD + d + 1] = fmaf(vs0, acc[a][2] - off0, vz * l0);
+            }
+            if (2 * c + 1 < nheads) {
+                o[(2 * c + 1) * kD + d]     = fmaf(vs0, acc[a][1] - off1, vz * l1);
+                o[(2 * c + 1) * kD + d + 1] = fmaf(vs0, acc[a][3] - off1, vz * l1);
+            }
         }
     }
     __syncthreads();
@@ -597,6 +658,47 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
             }
         }
     }
+    // The new token goes into the cache (one CTA per sequence and KV head does it).  Last, off the path to the first
+    // block: nothing in this launch reads the slot, and the copies in shared memory are still intact.
+    if (last_split && hb == 0) {
+        const size_t   slot = (size_t)(tlength % p.S_max) * ROWB;
+        unsigned char* kd   = const_cast<unsigned char*>(kc) + slot;
+        unsigned char* vd   = const_cast<unsigned char*>(vc) + slot;
+        if (INT8) {
+            for (int t2 = tid; t2 < 64; t2 += kThreads) {
+                const bool          is_v = t2 >= 32;
+                const int           d    = (t2 & 31) * 4;
+                const __half*       src  = is_v ? vnew_s : knew_s;
+                const float         sc   = is_v ? p.v_scale : p.k_scale;
+                const float         zp   = is_v ? p.v_zp : p.k_zp;
+                uint32_t            w    = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // template.cuh:976-981: round(clamp((x - zp) / scale)), round = half away from zero
+                    float v = __fdiv_rn(__half2float(src[d + i]) - zp, sc);
+                    v       = fmaxf(-128.f, fminf(127.f, v));
+                    w |= ((uint32_t)(int)roundf(v) & 0xffu) << (8 * i);
+                }
+                *reinterpret_cast<uint32_t*>((is_v ? vd : kd) + d) = w;
+            }
+        }
+        else {
+            if (tid < kD / 8) {
+                const int d = tid * 8;  // 16 bytes of K and of V per thread
+                *reinterpret_cast<uint4*>(kd + d * 2) = *reinterpret_cast<const uint4*>(knew_s + d);
+                *reinterpret_cast<uint4*>(vd + d * 2) = *reinterpret_cast<const uint4*>(vnew_s + d);
+            }
+        }
+    }
+#ifdef TM_B200_GEMM_TRACE
+    MMHA_TRACE(6);
+    if (trace_on && tid == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_mmha_trace[trace_id][7] = ((unsigned long long)smid << 32) | (unsigned)tlength;
+    }
+    if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) atomicAdd(&g_mmha_launch, 1);
+#endif
     if (n_split == 1) {
         return;
     }

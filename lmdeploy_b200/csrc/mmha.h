@@ -7,6 +7,17 @@
 
 namespace tmb {
 
+// What the kernel needs to know about the sequence of grid row z, gathered into one 32-byte record by the decode
+// driver (two 16-byte loads instead of a chain of dependent ones through order -> lengths / pointers).
+struct MmhaSeqDesc {
+    const void* k_cache;   // per-sequence base pointers (before the layer offset)
+    const void* v_cache;
+    int         length;    // tokens already cached
+    int         seq;       // index of the sequence in the batch
+    int         finished;
+    int         reserved;
+};
+
 struct MmhaParams {
     __half*              out;       // [B, H*128]
     const __half*        qkv;       // [B, stride]: q heads | k heads | v heads
@@ -18,6 +29,8 @@ struct MmhaParams {
     const unsigned char* finished;  // [B] or null
     const int*           padding;   // [B] or null (total_padding_tokens)
     const int*           order;     // [B] or null: sequence handled by grid row z (longest first evens out the tail)
+    const MmhaSeqDesc*   desc;      // [B] or null: the same in launch order with lengths, pointers and flags gathered
+    const float2*        rope_table;  // [B][64] {cos, sin} of every sequence's position, or null (computed in the kernel)
     int                  B, H, Hkv, stride, S_max, timestep, rot_dim, max_pos, use_dynamic_ntk, use_logn;
     int                  pos_from_length;  // RoPE position = cached length (the decode driver; lets a CUDA graph be replayed)
     float                rope_base, inv_sqrt_dh, k_scale, k_zp, v_scale, v_zp;
