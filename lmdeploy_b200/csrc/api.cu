@@ -76,6 +76,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->pdl           = env_int("TM_B200_PDL", 1);
+    h->p2p_allreduce = env_int("TM_B200_P2P_ALLREDUCE", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->mmha_warps  = env_int("TM_B200_MMHA_WARPS", 0);
@@ -125,6 +126,10 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     }
     else if (n == "pdl" && (value == 0 || value == 1)) {
         h->pdl = value;
+    }
+    else if (n == "p2p_allreduce" && (value == 0 || value == 1)) {
+        // 0: the tensor-parallel decode step reduces with NCCL even where the peer-memory path is set up
+        h->p2p_allreduce = value;
     }
     else if (n == "pdl_direct" && (value == 0 || value == 1)) {
         // GEMM and attention calls made DIRECTLY through this handle also launch with programmatic stream

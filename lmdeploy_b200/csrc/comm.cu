@@ -47,6 +47,14 @@ extern "C" int tm_comm_create(tm_comm** out, int world_size, int rank, const voi
 extern "C" int tm_comm_destroy(tm_comm* c)
 {
     if (!c) return TM_OK;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(c->device);
+    for (int j = 0; j < tmb::kMaxP2pRanks; ++j) {
+        if (c->p2p_peer[j]) cudaIpcCloseMemHandle(c->p2p_peer[j]);
+    }
+    if (c->p2p_local) cudaFree(c->p2p_local);
+    cudaSetDevice(prev);
     if (c->comm) ncclCommDestroy(c->comm);
     delete c;
     return TM_OK;

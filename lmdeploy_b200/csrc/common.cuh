@@ -13,6 +13,7 @@ namespace tmb {
 enum : unsigned {
     kStatusGemmPipeWait  = 1u << 2,  // tcgen05 GEMM: a pipeline barrier (copies, expanded weight, MMA completion)
     kStatusGemmTmemWait  = 1u << 3,  // tcgen05 GEMM: accumulator hand-over or the partners of a split tile
+    kStatusCommWait      = 1u << 6,  // peer-memory all-reduce: a peer's slot did not become ready in time
     kStatusPrefillOverflow = 1u << 5,  // prefill: a sequence's history + new tokens exceed the cache (session_len) or
                                        // its new tokens exceed max_q_len: the surplus rows were dropped
 };

@@ -25,6 +25,7 @@ struct tm_handle {
     int                gemm_tc_min_n   = 17; // token count from which the tcgen05 kernel is used; TM_B200_GEMM_TC_MIN overrides
     int                gemm_wait_cycles = 0; // 0 = default bound of the split-tile wait of the tcgen05 GEMM (option "gemm_wait_cycles")
     int                pdl_direct      = 0;  // option "pdl_direct": direct GEMM / attention calls launch with programmatic serialization too
+    int                p2p_allreduce   = 1;  // TM_B200_P2P_ALLREDUCE / option "p2p_allreduce": peer-memory all-reduce + norm in the decode step
     int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
 };
 

@@ -213,6 +213,29 @@ int run_step(StepCtx& c)
     if (!c.ok(tm_rmsnorm(m.hbuf, m.x, m.layers[0].self_attn_norm_weights, cfg.norm_eps, B, m.hidden, s))) return c.rc;
     ++c.launches;
 
+    // Tensor parallel: the row-split GEMMs write their partial sums into a slot that the peers have mapped, and one
+    // kernel sums the ranks, adds the residual and normalises (allreduce.cu); otherwise NCCL + the plain fused norm.
+    const bool tp_on  = m.comm && m.comm->world > 1;
+    const bool p2p    = tp_on && m.comm->p2p_ready && m.h->p2p_allreduce && (size_t)B * m.hidden * 2 <= m.comm->p2p_slot_bytes;
+    __half*    part_o = p2p ? (__half*)tm_comm_p2p_slot(m.comm, 0) : m.hbuf;
+    __half*    part_f = p2p ? (__half*)tm_comm_p2p_slot(m.comm, 1) : m.hbuf;
+    auto reduce_add_norm = [&](int slot, const void* norm_w) {
+        if (p2p) {
+            ++c.launches;
+            return c.ok(allreduce_add_rmsnorm_launch(m.comm, slot, m.x, m.hbuf, (const __half*)norm_w, cfg.norm_eps, B, m.hidden,
+                                                     m.h->status, s, g_pdl != 0)
+                                == cudaSuccess ?
+                            TM_OK :
+                            TM_ERR_CUDA);
+        }
+        if (tp_on) {
+            if (!c.ok(tm_allreduce_sum_f16(m.comm, m.hbuf, (size_t)B * m.hidden, s))) return false;  // :292-297, LlamaFfnLayer.cc:106-110
+            ++c.launches;
+        }
+        ++c.launches;
+        return c.ok(tm_add_residual_rmsnorm(m.x, m.hbuf, nullptr, norm_w, cfg.norm_eps, B, m.hidden, s));
+    };
+
     for (int l = 0; l < cfg.num_layer; ++l) {
         const LlamaDecoderLayerWeight& w = m.layers[l];
         // ---- self attention (LlamaDecoderSelfAttentionLayer.cc:193-304)
@@ -249,24 +272,14 @@ int run_step(StepCtx& c)
         a.attention_v_scale          = w.past_kv_scale[2];
         a.attention_v_zp             = w.past_kv_scale[3];
         if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order, m.seq_desc, m.rope_table))) return c.rc;
-        if (!c.ok(linear.forward(m.hbuf, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
-        if (m.comm && m.comm->world > 1) {
-            if (!c.ok(tm_allreduce_sum_f16(m.comm, m.hbuf, (size_t)B * m.hidden, s))) return c.rc;  // :292-297
-            ++c.launches;
-        }
-        // ---- x += attn ; h = RMSNorm(x) * ffn_norm   (LlamaDecoder.cc:212-220)
-        if (!c.ok(tm_add_residual_rmsnorm(m.x, m.hbuf, nullptr, w.ffn_norm_weights, cfg.norm_eps, B, m.hidden, s))) return c.rc;
-        ++c.launches;
+        if (!c.ok(linear.forward(part_o, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
+        // ---- [sum over ranks] ; x += attn ; h = RMSNorm(x) * ffn_norm   (LlamaDecoder.cc:212-220)
+        if (!reduce_add_norm(0, w.ffn_norm_weights)) return c.rc;
         // ---- feed forward (LlamaFfnLayer.cc:66-116): fused w1|w3 GEMM with the SiLU epilogue, then w2
         if (!c.ok(linear.forward(m.ffn, m.hbuf, B, w.fused_gating_intermediate, LlamaLinear::kFusedSiluFfn, s))) return c.rc;
-        if (!c.ok(linear.forward(m.hbuf, m.ffn, B, w.ffn_output, LlamaLinear::kGemm, s))) return c.rc;
-        if (m.comm && m.comm->world > 1) {
-            if (!c.ok(tm_allreduce_sum_f16(m.comm, m.hbuf, (size_t)B * m.hidden, s))) return c.rc;  // LlamaFfnLayer.cc:106-110
-            ++c.launches;
-        }
+        if (!c.ok(linear.forward(part_f, m.ffn, B, w.ffn_output, LlamaLinear::kGemm, s))) return c.rc;
         const void* next_norm = l + 1 < cfg.num_layer ? m.layers[l + 1].self_attn_norm_weights : m.output_norm;
-        if (!c.ok(tm_add_residual_rmsnorm(m.x, m.hbuf, nullptr, next_norm, cfg.norm_eps, B, m.hidden, s))) return c.rc;
-        ++c.launches;
+        if (!reduce_add_norm(1, next_norm)) return c.rc;
     }
     if (st.hidden_out) {
         c.ok(cudaMemcpyAsync(st.hidden_out, m.hbuf, (size_t)B * m.hidden * 2, cudaMemcpyDeviceToDevice, s) == cudaSuccess ?

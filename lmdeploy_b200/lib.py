@@ -152,6 +152,12 @@ SIGNATURES = {
     "tm_comm_destroy": (_i, [_vp]),
     "tm_allreduce_sum_f16": (_i, [_vp, _vp, _sz, _vp]),
     "tm_allgather": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "tm_comm_p2p_export": (_i, [_vp, _sz, _vp]),
+    "tm_comm_p2p_import": (_i, [_vp, _vp]),
+    "tm_comm_set_option": (_i, [_vp, C.c_char_p, C.c_longlong]),
+    "tm_comm_p2p_slot": (_vp, [_vp, _i]),
+    "tm_comm_p2p_slot_bytes": (_sz, [_vp]),
+    "tm_allreduce_add_residual_rmsnorm": (_i, [_vp, _i, _vp, _vp, _vp, C.c_float, _i, _i, _vp, _vp]),
     "tm_llama_create": (_i, [C.POINTER(_vp), _vp, _vp, C.POINTER(TmLlamaConfig)]),
     "tm_llama_destroy": (_i, [_vp]),
     "tm_llama_set_layer": (_i, [_vp, _i, C.POINTER(TmLlamaLayerWeights)]),

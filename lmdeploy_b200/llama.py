@@ -41,7 +41,7 @@ LLAMA2_70B = LlamaConfig(64, 8, 28672, 80, name="llama-2-70b")
 class Comm:
     """tm_comm: one rank of the tensor-parallel group (NCCL)."""
 
-    def __init__(self, world: int, rank: int, device: int):
+    def __init__(self, world: int, rank: int, device: int, p2p_slot_bytes: int = 4 << 20):
         import torch.distributed as dist
         ident = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
@@ -56,6 +56,23 @@ class Comm:
         self._c = C.c_void_p()
         _l.check(_l.lib.tm_comm_create(C.byref(self._c), world, rank, raw, device), "tm_comm_create")
         self.world, self.rank = world, rank
+        self.p2p = False
+        if 1 < world <= 8 and p2p_slot_bytes > 0:
+            # peer-memory all-reduce of the decode step: every rank exports a region, all ranks map all of them
+            mine = (C.c_ubyte * 64)()
+            ok = _l.lib.tm_comm_p2p_export(self._c, p2p_slot_bytes, mine) == _l.TM_OK
+            t = torch.tensor(list(mine) + [int(ok)], dtype=torch.uint8)
+            t = t.cuda(device) if dist.get_backend() == "nccl" else t
+            every = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(every, t)
+            every = torch.stack(every).cpu()
+            if bool(every[:, 64].all()):
+                raw_all = (C.c_ubyte * (64 * world))(*every[:, :64].reshape(-1).tolist())
+                ok = _l.lib.tm_comm_p2p_import(self._c, raw_all) == _l.TM_OK
+                flag = torch.tensor([int(ok)], dtype=torch.uint8)
+                flag = flag.cuda(device) if dist.get_backend() == "nccl" else flag
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                self.p2p = bool(flag.item())
 
     @property
     def ptr(self):

@@ -51,6 +51,17 @@ def run_model(llama, mcfg, wdir, comm, local, tokens, prompts, S):
     return np.stack(out), k, pre
 
 
+class _DevMem:
+    """a zero-copy torch view of device memory that the library owns"""
+
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = dict(shape=shape, typestr="<f2", data=(int(ptr), False), version=2, strides=None)
+
+
+def slot_view(ptr, rows, cols):
+    return torch.as_tensor(_DevMem(ptr, (rows, cols)), device="cuda")
+
+
 def close(a, b):
     err = np.abs(a - b)
     return float(err.max()), float(err.mean() / max(np.abs(b).mean(), 1e-9))
@@ -97,6 +108,70 @@ def main():
         ok = ok and good
         report.append(f"{name}: decode max_abs={a[0]:.2e} mean_rel={a[1]:.2e}; prefill max_abs={b[0]:.2e} mean_rel={b[1]:.2e}; "
                       f"k rows max_abs={kerr:.2e} {'ok' if good else 'FAIL'}")
+    # (c) the peer-memory all-reduce + residual add + RMSNorm by itself, against the same arithmetic in torch on the
+    #     gathered partial sums (rank order, fp16 rounding of the sum, fp32 add, fp16 residual, norm)
+    if comm.p2p:
+        h = l.default_handle(local)
+        status = torch.zeros(64, dtype=torch.int32, device="cuda")
+        for it, (m_rows, n) in enumerate([(5, 1024), (64, 4096), (128, 8192), (3, 16384), (1, 256)]):
+            slot = it % 2
+            g = torch.Generator(device="cuda").manual_seed(100 + 7 * it + rank)
+            part = torch.randn(m_rows, n, device="cuda", generator=g).half()
+            g0 = torch.Generator(device="cuda").manual_seed(55 + it)
+            resid = torch.randn(m_rows, n, device="cuda", generator=g0).half()
+            scale = (1 + 0.1 * torch.randn(n, device="cuda", generator=g0)).half()
+            ptr = l.lib.tm_comm_p2p_slot(comm.ptr, slot)
+            # the partial goes into the slot (in the model the GEMM writes there directly)
+            slot_view(ptr, m_rows, n).copy_(part)
+            torch.cuda.synchronize()
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            out = torch.empty_like(resid)
+            r_in = resid.clone()
+            st = torch.cuda.current_stream().cuda_stream
+            assert l.lib.tm_allreduce_add_residual_rmsnorm(comm.ptr, slot, r_in.data_ptr(), out.data_ptr(), scale.data_ptr(), 1e-6,
+                                                           m_rows, n, status.data_ptr(), st) == l.TM_OK
+            torch.cuda.synchronize()
+            total = torch.zeros(m_rows, n, device="cuda")
+            for pj in parts:
+                total += pj.float()
+            want_r = (resid.float() + total.half().float()).half()
+            inv = torch.rsqrt((resid.float() + total.half().float()).pow(2).mean(dim=-1, keepdim=True) + 1e-6)
+            want_o = (want_r.float() * scale.float() * inv).half()
+            good = torch.equal(r_in, want_r) and (out.float() - want_o.float()).abs().max().item() <= 2e-3 * max(1.0, want_o.float().abs().max().item())
+            good = good and int(status[0].item()) == 0
+            ok = ok and good
+            report.append(f"all-reduce + add + norm [{m_rows}, {n}] slot {slot}: residual bit-exact {torch.equal(r_in, want_r)}, "
+                          f"out max_abs {(out.float() - want_o.float()).abs().max().item():.2e} {'ok' if good else 'FAIL'}")
+        # (d) the decode step with NCCL instead of the peer-memory path gives the same logits within tolerance
+        h.set_option("p2p_allreduce", 0)
+        mcfg = read_cfg(b_1, l, llama)
+        tokens = rng.integers(0, mcfg.vocab_size, size=(4, 3)).astype(np.int32)
+        prompts = [list(rng.integers(0, mcfg.vocab_size, size=n)) for n in (4, 6, 2)]
+        lg_nccl, _, _ = run_model(llama, mcfg, b_tp, comm, local, tokens, prompts, S)
+        h.set_option("p2p_allreduce", 1)
+        lg_p2p, _, _ = run_model(llama, mcfg, b_tp, comm, local, tokens, prompts, S)
+        a = close(lg_p2p, lg_nccl)
+        good = a[0] <= 3e-2 and a[1] <= 5e-3
+        ok = ok and good
+        report.append(f"decode, peer-memory all-reduce vs NCCL: max_abs={a[0]:.2e} mean_rel={a[1]:.2e} {'ok' if good else 'FAIL'}")
+        # (e) last: a peer that does not show up.  Rank 0 alone calls, with a wait bound of a few microseconds: the kernel
+        #     gives up, sets the status bit and returns; nothing hangs.  No all-reduce follows (the call counts now differ).
+        dist.barrier()
+        if rank == 0:
+            assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_wait_cycles", 20000) == l.TM_OK
+            x = torch.zeros(2, 256, dtype=torch.float16, device="cuda")
+            y = torch.ones(256, dtype=torch.float16, device="cuda")
+            status.zero_()
+            assert l.lib.tm_allreduce_add_residual_rmsnorm(comm.ptr, 0, x.data_ptr(), x.clone().data_ptr(), y.data_ptr(), 1e-6, 2, 256,
+                                                           status.data_ptr(), torch.cuda.current_stream().cuda_stream) == l.TM_OK
+            torch.cuda.synchronize()
+            good = int(status[0].item()) == (1 << 6)
+            ok = ok and good
+            report.append(f"absent peer: status word 0x{int(status[0].item()):x} {'ok' if good else 'FAIL'}")
+        dist.barrier()
+    else:
+        report.append("peer-memory all-reduce not set up on this machine: NCCL path only")
     flag = torch.tensor([int(ok)], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
