@@ -856,6 +856,7 @@ def run_decode_workload(args, rank, world, device, name):
         # the metric's second half, "W4 GEMM HBM GB/s vs peak": the GEMV at one token on the same weights
         m1 = time_layer_gemms(model, cfg, 1, stream, tm, st.lengths.device, chained=False)
         m1c = time_layer_gemms(model, cfg, 1, stream, tm, st.lengths.device, chained=True)
+        m1_large = time_large_gemv(stream, tm, st.lengths.device) if world == 1 else None
         h.check_device_status(stream.cuda_stream)
 
     ms_step = max_over_ranks(ms / K, world)
@@ -892,6 +893,11 @@ def run_decode_workload(args, rank, world, device, name):
         "per_kernel_m1_note": "gemm_s4_f16_small_kernel at 1 token on this model's weights (per-rank shapes); us / gbs / frac: launches "
                               "back to back, each waiting for the one before it; *_chained: with programmatic dependent launch, as "
                               "inside the decode step",
+        "per_kernel_m1_large": None if m1_large is None else {
+            k: dict(v, frac=round(v["gbs"] / peaks["hbm_gbs"], 4)) for k, v in m1_large.items()},
+        "per_kernel_m1_large_note": "same kernel at 1 token on the un-sharded Llama-2-70B projection shapes (seeded random nibbles and "
+                                    "scales; copies of each weight alternate so that every launch reads HBM): the launch's fixed cost "
+                                    "weighs less there",
         "per_kernel": per,
         "per_kernel_note": "each kernel timed alone (no overlap with its neighbours), a different layer's weights / cache every "
                            "launch (L2-cold): the sum exceeds ms_per_step, where programmatic dependent launch overlaps them",
@@ -938,6 +944,47 @@ def time_layer_gemms(model, cfg, tokens, stream, tm, dev, chained):
             out[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), bytes=int(nb))
     finally:
         h.set_option("pdl_direct", 0)
+    return out
+
+
+def time_large_gemv(stream, tm, dev):
+    """The 1-token GEMM on the four projection shapes of the un-sharded Llama-2-70B (k, n as LlamaDecoderLayerWeight.cc:49-77
+    gives them at tp 1): the weights of one launch are 34..235 MB, so the launch's fixed cost weighs less than on the 7B
+    shapes.  Any nibbles are a weight; launches wait for one another (no programmatic dependent launch)."""
+    g = torch.Generator(device=dev).manual_seed(70)
+    op = tm.LlamaLinear(dev.index)
+    out = {}
+    for nm, n, k, fused in (("qkv 10240x8192", 10240, 8192, False), ("o 8192x8192", 8192, 8192, False),
+                            ("w13+silu 57344x8192", 57344, 8192, True), ("w2 8192x28672", 8192, 28672, False)):
+        nbytes = n * k // 2
+        copies = max(2, -(-400_000_000 // nbytes))        # at least 400 MB in rotation: three times L2
+        ws = []
+        for _ in range(copies):
+            A = torch.randint(-2 ** 31, 2 ** 31 - 1, (k, n // 8), dtype=torch.int32, device=dev, generator=g)
+            z = torch.randint(64, 80, (k // 128, n, 1), device=dev, generator=g).half()
+            sc = (torch.rand(k // 128, n, 1, device=dev, generator=g) * 0.01 + 0.002).half()
+            ws.append(tm.LlamaDenseWeight(k, n, A, tm.WeightType.kINT4, None, torch.cat([z, sc], dim=-1).contiguous(), 128))
+        x = torch.randn(1, k, device=dev, generator=g).half()
+        y = torch.empty(1, n // (2 if fused else 1), dtype=torch.float16, device=dev)
+        launch = lambda i: op.forward(y, x, 1, ws[i % copies], op.kFusedSiluFfn if fused else op.kGemm)
+        n_it = 4 * copies
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=stream):
+            for i in range(n_it):
+                launch(i)
+        gr.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        gr.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / n_it
+        nb = gemm_bytes(n, k, 1, fused)
+        out[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), bytes=int(nb))
+        del ws
     return out
 
 

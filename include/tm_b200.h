@@ -269,17 +269,23 @@ TM_API int tm_allreduce_sum_f16(tm_comm* c, void* buf, size_t count, void* strea
 /* Peer-memory all-reduce for the decode step (no counterpart in the reference, whose custom all-reduce,
  * src/turbomind/kernels/custom_ar_kernels.cu:138-199, is not used by the LLaMA layers): the sum over the tensor-parallel
  * ranks fused with the residual add and RMSNorm that follow it (LlamaDecoder.cc:212-236).
- *   tm_comm_p2p_export   allocates this rank's region (two slots of slot_bytes each + counters) and returns its CUDA IPC
+ *   tm_comm_p2p_export   allocates this rank's region (three buffers of slot_bytes each + counters) and returns its CUDA IPC
  *                        handle (64 bytes); every rank passes the handles of all ranks, in rank order, to
  *   tm_comm_p2p_import   which maps the peers' regions.  One process per GPU, all on one node, world <= 8.
  *   tm_comm_p2p_slot     device address of slot 0 / 1 of THIS rank: the row-split GEMM writes its partial sums there.
  *   tm_allreduce_add_residual_rmsnorm   residual[m, n] += sum over ranks of slot rows (rounded to fp16 first, as an fp16
  *                        all-reduce delivers it); out[m, n] = RMSNorm(residual) * scale.  Ranks are read in rank order.
+ *                        With token rows dealt to owner ranks ("p2p_mode" below; rank r owns rows
+ *                        [r * ceil(m / world), (r + 1) * ceil(m / world))) every rank gets all of `out`, but `residual`
+ *                        is updated for the rank's own rows only: it must be fed back to this call alone, as the
+ *                        decode step does.  The region then holds a third buffer of slot_bytes for the handed-on rows.
  *                        Calls must alternate between the two slots on every rank alike.  `status_word` is a device
  *                        word (a handle's): a peer that does not show up within the bound sets a bit there and the
  *                        kernel finishes on what it has, it never hangs. */
 TM_API int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64);
-/* "p2p_wait_cycles": bound, in SM clock cycles, of the wait for the peers' slots (0 = default, about a quarter of a second) */
+/* "p2p_wait_cycles": bound, in SM clock cycles, of the wait for the peers' slots (0 = default, about a quarter of a second);
+ * "p2p_mode": 0 automatic (two ranks: each reads the other's whole slot; more: token rows dealt to owner ranks, which
+ * finish them and hand them on), 1 / 2 force either (environment: TM_B200_P2P_MODE, read by tm_comm_p2p_export). */
 TM_API int tm_comm_set_option(tm_comm* c, const char* name, long long value);
 TM_API int tm_comm_p2p_import(tm_comm* c, const void* handles);
 TM_API void* tm_comm_p2p_slot(tm_comm* c, int slot);

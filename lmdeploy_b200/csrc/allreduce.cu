@@ -10,6 +10,10 @@
 //   3. reads the row from every rank's slot with ordinary 128-bit loads over NVLink, in rank order (the sum is the
 //      same on every rank and from run to run), rounds it to fp16 like the all-reduce it replaces,
 //   4. adds the residual, stores it, normalises and stores the input of the next GEMM.
+// With more than two ranks the rows are dealt to the ranks instead (allreduce_rows_kernel): the owner of a row does
+// steps 1-4 for it, parks the normalised row in a third mapped buffer and raises a per-row counter in every peer's
+// memory; the other ranks wait for that counter and fetch the finished row.  Every rank then reads (w - 1) / w of the
+// tensor twice instead of (w - 1) times, and the residual is only ever touched by the owner of a row.
 // Nothing is multicast and no rank writes another rank's data: peers only ever write each other's counters.
 // The two slots alternate (o_proj -> 0, w2 -> 1).  A rank overwrites a slot two calls after its peers read it: by then
 // it has itself passed the wait of the call in between, for which every peer had to finish the earlier one first.
@@ -18,6 +22,8 @@
 #include "common.cuh"
 #include "tm_b200.h"
 
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 namespace tmb {
@@ -37,6 +43,11 @@ struct ArParams {
     long long            max_wait_cycles;
     float                eps;
     int                  n, world, rank;
+    // row-owner variant
+    unsigned char*       h_slot[kMaxP2pRanks];     // finished rows of every rank (own rank: local address)
+    unsigned*            row_flags[kMaxP2pRanks];  // per-row counters of every rank; the owner of a row writes them all
+    unsigned*            my_row_flags;
+    int                  rows_per_rank;
 };
 
 __device__ __forceinline__ uint4 ld_peer(const unsigned char* p)
@@ -161,10 +172,150 @@ __global__ void __launch_bounds__(kArThreadsMax) allreduce_add_rmsnorm_kernel(Ar
     }
 }
 
+
+// Row-owner variant (more than two ranks).  One CTA per token row on every rank.  Row t belongs to rank t / rows_per_rank.
+__global__ void __launch_bounds__(kArThreadsMax) allreduce_rows_kernel(ArParams p)
+{
+    __shared__ float    red[kArThreadsMax / 32];
+    __shared__ unsigned s_epoch;
+    const int tid = threadIdx.x;
+    pdl_wait();  // the slot is written by the GEMM before this kernel
+    pdl_launch_dependents();
+    if (tid == 0) s_epoch = *(volatile unsigned*)&p.state[0] + 1u;
+    __syncthreads();
+    const unsigned epoch = s_epoch;
+    if (blockIdx.x == 0 && tid < p.world && tid != p.rank) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[tid] + p.rank), "r"(epoch) : "memory");
+    }
+    const int    t     = blockIdx.x;
+    const int    owner = min(t / p.rows_per_rank, p.world - 1);
+    const size_t row   = (size_t)t * p.n;
+    const int    nvec  = p.n / 8;
+    auto bounded_wait = [&](const unsigned* flag) {
+        const long long t0 = clock64();
+        unsigned        seen;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if ((int)(seen - epoch) >= 0) break;
+            if (clock64() - t0 > p.max_wait_cycles) {
+                atomicOr(p.status, kStatusCommWait);
+                break;
+            }
+            __nanosleep(40);
+        }
+    };
+    if (owner == p.rank) {
+        // ---- this rank finishes the row: partial sums of every rank -> residual -> normalised row
+        if (tid < p.world && tid != p.rank) bounded_wait(p.my_flags + tid);
+        __syncthreads();
+        float ss = 0.f;
+        auto reduce_piece = [&](int v) {
+            uint4 part[kMaxP2pRanks];
+#pragma unroll
+            for (int j = 0; j < kMaxP2pRanks; ++j) {
+                if (j < p.world) part[j] = ld_peer(p.slot[j] + (row + (size_t)v * 8) * 2);
+            }
+            uint4 r = reinterpret_cast<const uint4*>(p.residual + row)[v];
+            float sum[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+#pragma unroll
+            for (int j = 0; j < kMaxP2pRanks; ++j) {
+                if (j < p.world) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&part[j]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = __half22float2(h[e]);
+                        sum[2 * e] += f.x, sum[2 * e + 1] += f.y;
+                    }
+                }
+            }
+            __half2* rh = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 x = __half22float2(__floats2half2_rn(sum[2 * e], sum[2 * e + 1]));
+                const float2 a = __half22float2(rh[e]);
+                const float2 u = make_float2(a.x + x.x, a.y + x.y);
+                ss += u.x * u.x + u.y * u.y;
+                rh[e] = __float22half2_rn(u);
+            }
+            reinterpret_cast<uint4*>(p.residual + row)[v] = r;
+            return r;
+        };
+        auto scaled = [&](uint4 o, int v, float inv) {
+            const uint4    sc = reinterpret_cast<const uint4*>(p.scale)[v];
+            const __half2* sh = reinterpret_cast<const __half2*>(&sc);
+            __half2*       oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __half22float2(oh[e]), w = __half22float2(sh[e]);
+                oh[e]          = __float22half2_rn(make_float2(a.x * w.x * inv, a.y * w.y * inv));
+            }
+            return o;
+        };
+        auto block_total = [&]() {
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+            if ((tid & 31) == 0) red[tid >> 5] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w) tot += red[w];
+            return tot;
+        };
+        uint4* mine_h = reinterpret_cast<uint4*>(p.h_slot[p.rank] + row * 2);
+        if (nvec <= (int)blockDim.x) {
+            uint4 piece = make_uint4(0, 0, 0, 0);
+            if (tid < nvec) piece = reduce_piece(tid);
+            const float inv = rsqrtf(block_total() / (float)p.n + p.eps);
+            if (tid < nvec) {
+                const uint4 o = scaled(piece, tid, inv);
+                reinterpret_cast<uint4*>(p.out + row)[tid] = o;
+                mine_h[tid]                                = o;
+            }
+        }
+        else {
+            for (int v = tid; v < nvec; v += blockDim.x) reinterpret_cast<uint4*>(p.out + row)[v] = reduce_piece(v);
+            const float inv = rsqrtf(block_total() / (float)p.n + p.eps);
+            for (int v = tid; v < nvec; v += blockDim.x) {
+                const uint4 o = scaled(reinterpret_cast<const uint4*>(p.out + row)[v], v, inv);
+                reinterpret_cast<uint4*>(p.out + row)[v] = o;
+                mine_h[v]                                = o;
+            }
+        }
+        // the finished row is in this rank's mapped buffer: tell every peer (the barrier orders every thread's stores
+        // before the fence of the threads that raise the counters)
+        __syncthreads();
+        if (tid < p.world && tid != p.rank) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.row_flags[tid] + t), "r"(epoch) : "memory");
+        }
+    }
+    else {
+        // ---- another rank finishes the row: wait for its counter, fetch the row
+        if (tid == 0) bounded_wait(p.my_row_flags + t);
+        __syncthreads();
+        const unsigned char* src = p.h_slot[owner] + row * 2;
+        for (int v = tid; v < nvec; v += blockDim.x) reinterpret_cast<uint4*>(p.out + row)[v] = ld_peer(src + (size_t)v * 16);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&p.state[1], 1u) == gridDim.x - 1) {
+            p.state[1] = 0u;
+            __threadfence();
+            *(volatile unsigned*)&p.state[0] = epoch;
+        }
+    }
+}
+
 }  // namespace
 
-// layout of a rank's exported region: [0, 1 KB) counters written by the peers | [1 KB, 2 KB) own call state | slots
-constexpr size_t kP2pHeader = 2048;
+// layout of a rank's exported region: [0, 1 KB) counters written by the peers | [1 KB, 2 KB) own call state |
+// [2 KB, 8 KB) per-row counters written by the row owners | partial-sum slots 0, 1 | finished rows
+constexpr size_t kP2pRowFlags = 2048;
+constexpr int    kP2pMaxRows  = 1536;
+constexpr size_t kP2pHeader   = 8192;
 
 cudaError_t allreduce_add_rmsnorm_launch(tm_comm* c, int slot, __half* residual, __half* out, const __half* scale, float eps, int m,
                                          int n, unsigned* status, cudaStream_t st, bool pdl)
@@ -186,9 +337,19 @@ cudaError_t allreduce_add_rmsnorm_launch(tm_comm* c, int slot, __half* residual,
     p.n               = n;
     p.world           = c->world;
     p.rank            = c->rank;
+    for (int j = 0; j < c->world; ++j) {
+        unsigned char* base = (unsigned char*)(j == c->rank ? c->p2p_local : c->p2p_peer[j]);
+        p.h_slot[j]         = base + kP2pHeader + 2 * c->p2p_slot_bytes;
+        p.row_flags[j]      = (unsigned*)(base + kP2pRowFlags);
+    }
+    p.my_row_flags  = (unsigned*)((unsigned char*)c->p2p_local + kP2pRowFlags);
+    p.rows_per_rank = (m + c->world - 1) / c->world;
     int threads = n / 8;
     if (threads > kArThreadsMax) threads = kArThreadsMax;
     threads = (threads + 31) / 32 * 32;
+    // two ranks: each reads the other's whole slot; more: rows dealt to owners (less traffic, one more hand-over)
+    const bool rows = (c->p2p_mode == 2 || (c->p2p_mode == 0 && c->world > 2)) && m <= kP2pMaxRows;
+    if (rows) return launch_kernel(allreduce_rows_kernel, dim3(m), dim3(threads), 0, st, pdl, p);
     return launch_kernel(allreduce_add_rmsnorm_kernel, dim3(m), dim3(threads), 0, st, pdl, p);
 }
 
@@ -206,7 +367,7 @@ extern "C" int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64)
     cudaGetDevice(&prev);
     cudaSetDevice(c->device);
     slot_bytes         = (slot_bytes + 255) / 256 * 256;
-    const size_t bytes = kP2pHeader + 2 * slot_bytes;
+    const size_t bytes = kP2pHeader + 3 * slot_bytes;
     cudaError_t  e     = cudaMalloc(&c->p2p_local, bytes);
     if (e == cudaSuccess) e = cudaMemset(c->p2p_local, 0, bytes);
     cudaIpcMemHandle_t h;
@@ -215,6 +376,7 @@ extern "C" int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64)
     cudaSetDevice(prev);
     if (e != cudaSuccess) return TM_ERR_CUDA;
     c->p2p_slot_bytes = slot_bytes;
+    if (const char* e = std::getenv("TM_B200_P2P_MODE")) c->p2p_mode = std::max(0, std::min(2, std::atoi(e)));
     std::memcpy(handle64, &h, 64);
     return TM_OK;
 }
@@ -240,6 +402,10 @@ extern "C" int tm_comm_p2p_import(tm_comm* c, const void* handles)
 extern "C" int tm_comm_set_option(tm_comm* c, const char* name, long long value)
 {
     if (!c || !name) return TM_ERR_INVALID_ARG;
+    if (std::strcmp(name, "p2p_mode") == 0 && value >= 0 && value <= 2) {
+        c->p2p_mode = (int)value;  // 0 automatic, 1 every rank reads every slot, 2 rows dealt to owners
+        return TM_OK;
+    }
     if (std::strcmp(name, "p2p_wait_cycles") == 0 && value >= 0) {
         c->p2p_wait_cycles = value;  // bound of the wait for the peers' slots, SM clock cycles; 0 = default
         return TM_OK;

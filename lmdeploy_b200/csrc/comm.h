@@ -25,6 +25,7 @@ struct tm_comm {
     size_t    p2p_slot_bytes  = 0;
     int       p2p_ready       = 0;
     long long p2p_wait_cycles = 0;  // 0 = the default bound of the wait for the peers
+    int       p2p_mode        = 0;  // 0 automatic; 1 every rank reads every slot; 2 rows dealt to owners
 };
 
 namespace tmb {

@@ -205,8 +205,9 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
         }
     };
     // The weights of the first ST - 1 units are requested before the kernel ahead of this one in the
-    // stream is known to be complete (nothing writes them); their activations follow after the wait,
-    // in one more group, and the first unit waits for all of it.
+    // stream is known to be complete (nothing writes them).  Their activations follow after the wait as
+    // plain loads and shared-memory stores, which the first barrier of the loop publishes: the first unit
+    // then waits for its own 16 KB of weights only, not for the whole window of requests behind it.
     const int x_k0 = i_k;
 #pragma unroll
     for (int sidx = 0; sidx < ST - 1; ++sidx) {
@@ -216,14 +217,19 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
     pdl_wait();
     pdl_launch_dependents();
     if (x_loader) {
-        int xk = x_k0;
+        int   xk = x_k0;
+        uint4 xv[ST - 1];
 #pragma unroll
         for (int sidx = 0; sidx < ST - 1; ++sidx) {
-            if (sidx < n_units) cp_async16(x_dst + sidx * kXUnit, x_base + (size_t)xk * (kUnitRows * 2));
+            xv[sidx] = make_uint4(0, 0, 0, 0);
+            if (sidx < n_units) xv[sidx] = __ldcg(reinterpret_cast<const uint4*>(x_base + (size_t)xk * (kUnitRows * 2)));
             if (++xk == G) xk = 0;
         }
+#pragma unroll
+        for (int sidx = 0; sidx < ST - 1; ++sidx) {
+            if (sidx < n_units) *reinterpret_cast<uint4*>(smem_raw + (x_dst - smem_s) + sidx * kXUnit) = xv[sidx];
+        }
     }
-    cp_async_commit();
 
     // per (tile, 16-row half): Z = offset + zero (rows r / r + 8) and the scale (s, s / 16)
     float zl[kTilesPerWarp][2], zh[kTilesPerWarp][2], sl[kTilesPerWarp][2], sh[kTilesPerWarp][2];
@@ -259,13 +265,8 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
     for (int it = 0; it < n_units; it += 2) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            if (it == 0 && u == 0) {
-                cp_async_wait<0>();  // everything requested so far: the first units and their activations
-                SMALL_TRACE(1);
-            }
-            else {
-                cp_async_wait<ST - 2>();
-            }
+            cp_async_wait<ST - 2>();
+            if (it == 0 && u == 0) SMALL_TRACE(1);
             // every thread's copies for this unit have landed, and every warp is done with the unit before
             __syncthreads();
             if (to_issue > 0) issue_unit(s_fill, true);

@@ -113,8 +113,12 @@ def main():
     if comm.p2p:
         h = l.default_handle(local)
         status = torch.zeros(64, dtype=torch.int32, device="cuda")
-        for it, (m_rows, n) in enumerate([(5, 1024), (64, 4096), (128, 8192), (3, 16384), (1, 256)]):
+        # both hand-over schemes: 1 = every rank reads every slot, 2 = token rows dealt to owner ranks (the default
+        # beyond two ranks), where a rank updates the residual of its own rows only
+        cases = [(mode, shape) for mode in (1, 2) for shape in [(5, 1024), (64, 4096), (128, 8192), (3, 16384), (1, 256), (130, 4096)]]
+        for it, (mode, (m_rows, n)) in enumerate(cases):
             slot = it % 2
+            assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_mode", mode) == l.TM_OK
             g = torch.Generator(device="cuda").manual_seed(100 + 7 * it + rank)
             part = torch.randn(m_rows, n, device="cuda", generator=g).half()
             g0 = torch.Generator(device="cuda").manual_seed(55 + it)
@@ -138,10 +142,15 @@ def main():
             want_r = (resid.float() + total.half().float()).half()
             inv = torch.rsqrt((resid.float() + total.half().float()).pow(2).mean(dim=-1, keepdim=True) + 1e-6)
             want_o = (want_r.float() * scale.float() * inv).half()
+            if mode == 2:   # rows of other owners keep the residual they had
+                per = (m_rows + world - 1) // world
+                mine = torch.zeros(m_rows, 1, dtype=torch.bool, device="cuda")
+                mine[rank * per:(rank + 1) * per] = True
+                want_r = torch.where(mine, want_r, resid)
             good = torch.equal(r_in, want_r) and (out.float() - want_o.float()).abs().max().item() <= 2e-3 * max(1.0, want_o.float().abs().max().item())
             good = good and int(status[0].item()) == 0
             ok = ok and good
-            report.append(f"all-reduce + add + norm [{m_rows}, {n}] slot {slot}: residual bit-exact {torch.equal(r_in, want_r)}, "
+            report.append(f"all-reduce + add + norm [{m_rows}, {n}] slot {slot} scheme {mode}: residual bit-exact {torch.equal(r_in, want_r)}, "
                           f"out max_abs {(out.float() - want_o.float()).abs().max().item():.2e} {'ok' if good else 'FAIL'}")
         # (d) the decode step with NCCL instead of the peer-memory path gives the same logits within tolerance
         h.set_option("p2p_allreduce", 0)
@@ -150,11 +159,14 @@ def main():
         prompts = [list(rng.integers(0, mcfg.vocab_size, size=n)) for n in (4, 6, 2)]
         lg_nccl, _, _ = run_model(llama, mcfg, b_tp, comm, local, tokens, prompts, S)
         h.set_option("p2p_allreduce", 1)
-        lg_p2p, _, _ = run_model(llama, mcfg, b_tp, comm, local, tokens, prompts, S)
-        a = close(lg_p2p, lg_nccl)
-        good = a[0] <= 3e-2 and a[1] <= 5e-3
-        ok = ok and good
-        report.append(f"decode, peer-memory all-reduce vs NCCL: max_abs={a[0]:.2e} mean_rel={a[1]:.2e} {'ok' if good else 'FAIL'}")
+        for mode in (1, 2):
+            assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_mode", mode) == l.TM_OK
+            lg_p2p, _, _ = run_model(llama, mcfg, b_tp, comm, local, tokens, prompts, S)
+            a = close(lg_p2p, lg_nccl)
+            good = a[0] <= 3e-2 and a[1] <= 5e-3
+            ok = ok and good
+            report.append(f"decode, peer-memory all-reduce (scheme {mode}) vs NCCL: max_abs={a[0]:.2e} mean_rel={a[1]:.2e} {'ok' if good else 'FAIL'}")
+        assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_mode", 0) == l.TM_OK
         # (e) last: a peer that does not show up.  Rank 0 alone calls, with a wait bound of a few microseconds: the kernel
         #     gives up, sets the status bit and returns; nothing hangs.  No all-reduce follows (the call counts now differ).
         dist.barrier()
@@ -167,6 +179,12 @@ def main():
                                                            status.data_ptr(), torch.cuda.current_stream().cuda_stream) == l.TM_OK
             torch.cuda.synchronize()
             good = int(status[0].item()) == (1 << 6)
+            assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_mode", 2) == l.TM_OK     # same with rows dealt to owners
+            status.zero_()
+            assert l.lib.tm_allreduce_add_residual_rmsnorm(comm.ptr, 1, x.data_ptr(), x.clone().data_ptr(), y.data_ptr(), 1e-6, 2, 256,
+                                                           status.data_ptr(), torch.cuda.current_stream().cuda_stream) == l.TM_OK
+            torch.cuda.synchronize()
+            good = good and int(status[0].item()) == (1 << 6)
             ok = ok and good
             report.append(f"absent peer: status word 0x{int(status[0].item()):x} {'ok' if good else 'FAIL'}")
         dist.barrier()
