@@ -44,11 +44,16 @@ typedef struct tm_handle tm_handle;
 /* Per-device state: SM count, split-K scratch, split-KV scratch, device status word.
  * One handle is used by one host thread at a time (the reference runs one engine thread per
  * GPU: src/turbomind/models/llama/LlamaV2.cc:435-438); handles of different devices may be
- * used concurrently.  No process-global mutable state, with two exceptions: the per-device table behind
- * tm_gemm_s4_f16_noalloc (guarded by a mutex) and a thread-local switch the decode driver sets around its
+ * used concurrently.  No process-global mutable state, with three exceptions: the per-device table behind
+ * tm_gemm_s4_f16_noalloc (guarded by a mutex), the shared handles of tm_handle_of_current_device and a thread-local switch the decode driver sets around its
  * own launches. */
 TM_API int tm_create(tm_handle** out, int device);
 TM_API int tm_destroy(tm_handle* h);
+/* A handle shared by everything in the process that runs on the current CUDA device, created on first use and kept
+ * until the process exits (NULL if it cannot be created).  For callers that must keep a signature of the reference
+ * and so cannot carry a handle: the header shims under include/compat.  A third piece of process-global state, guarded
+ * by a mutex; the one-host-thread-at-a-time rule above applies to everyone who shares it. */
+TM_API tm_handle* tm_handle_of_current_device(void);
 TM_API const char* tm_status_string(int status);
 /* cudaError_t of the most recent failing CUDA call made through this handle (0 if none). */
 TM_API int tm_last_cuda_error(const tm_handle* h);
@@ -284,8 +289,9 @@ TM_API int tm_allreduce_sum_f16(tm_comm* c, void* buf, size_t count, void* strea
  *                        kernel finishes on what it has, it never hangs. */
 TM_API int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64);
 /* "p2p_wait_cycles": bound, in SM clock cycles, of the wait for the peers' slots (0 = default, about a quarter of a second);
- * "p2p_mode": 0 automatic (two ranks: each reads the other's whole slot; more: token rows dealt to owner ranks, which
- * finish them and hand them on), 1 / 2 force either (environment: TM_B200_P2P_MODE, read by tm_comm_p2p_export). */
+ * "p2p_mode": 1 every rank reads every rank's whole slot, 2 token rows dealt to owner ranks, which finish them and
+ * hand them on, 0 (default) picks 1 up to four ranks and 2 beyond (environment: TM_B200_P2P_MODE, read by
+ * tm_comm_p2p_export). */
 TM_API int tm_comm_set_option(tm_comm* c, const char* name, long long value);
 TM_API int tm_comm_p2p_import(tm_comm* c, const void* handles);
 TM_API void* tm_comm_p2p_slot(tm_comm* c, int slot);

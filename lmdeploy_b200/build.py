@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     os.makedirs(OUT_DIR, exist_ok=True)
     srcs = sources()
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
-    hdrs += [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
+    hdrs += [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include")) if f.endswith(".h")]
     nccl_c, nccl_l = _nccl_flags()
     flags = NVCC_FLAGS + nccl_c + (["-Xptxas", "-v"] if ptxas_info else [])
     stamp = os.path.join(OUT_DIR, "build.sha256")

@@ -1,4 +1,5 @@
 // C ABI: handle management and the GEMM entry point.
+#include <mutex>
 #include "handle.h"
 #include "tm_b200.h"
 
@@ -88,6 +89,19 @@ extern "C" int tm_create(tm_handle** out, int device)
     }
     *out = h;
     return TM_OK;
+}
+
+// One shared handle per device for callers that have nowhere to keep one (the header shims under include/compat, whose
+// classes and free functions must keep the reference's signatures).  Created on first use, kept until the process exits.
+extern "C" tm_handle* tm_handle_of_current_device(void)
+{
+    static std::mutex mu;
+    static tm_handle* table[64] = {};
+    int               dev       = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!table[dev] && tm_create(&table[dev], dev) != TM_OK) table[dev] = nullptr;
+    return table[dev];
 }
 
 extern "C" int tm_destroy(tm_handle* h)

@@ -133,6 +133,7 @@ class TmLlamaPrefillState(C.Structure):
 SIGNATURES = {
     "tm_create": (_i, [C.POINTER(_vp), _i]),
     "tm_destroy": (_i, [_vp]),
+    "tm_handle_of_current_device": (_vp, []),
     "tm_status_string": (C.c_char_p, [_i]),
     "tm_last_cuda_error": (_i, [_vp]),
     "tm_check_device_status": (_i, [_vp, _vp, C.POINTER(C.c_uint)]),

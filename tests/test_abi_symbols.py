@@ -9,6 +9,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared():
     names = set()
     for fn in os.listdir(os.path.join(ROOT, "include")):
+        if not fn.endswith(".h"):
+            continue   # include/compat holds header shims that only call what tm_b200.h declares
         src = open(os.path.join(ROOT, "include", fn)).read()
         names |= set(re.findall(r"TM_API\s+[\w\s\*]+?\b(tm_\w+)\s*\(", src))
     return names
