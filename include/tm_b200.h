@@ -67,6 +67,8 @@ TM_API unsigned long long tm_launch_count(const tm_handle* h);
  * "pdl_direct" (1: GEMM / attention calls made directly through the handle launch with programmatic stream
  * serialization, as the decode driver's do; only where no kernel ahead in the stream writes weights or cached rows),
  * "gemm_wait_cycles" (bound of the tcgen05 GEMM's wait for the partners of a split tile, 0 = default; tests),
+ * "lm_head_cublas" (1: the decode driver computes the lm-head with cuBLAS, as the reference does, instead of this
+ * library's kernel; for comparison),
  * "mmha_chunk" (cached tokens per KV split, 0 = automatic), "mmha_warps" (warps per attention CTA: 1, 2,
  * 4 or 0 = automatic), "pdl" (1 = tm_llama_decode launches with programmatic dependent launch).
  * Returns TM_ERR_INVALID_ARG for an unknown name or value. */
@@ -177,6 +179,68 @@ typedef struct tm_mmha_params {
 } tm_mmha_params;
 
 TM_API int tm_mmha_decode(tm_handle* h, const tm_mmha_params* params, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * lm-head: logits[tokens][ld] (fp32) = x[tokens][hidden] (half) . w[vocab][hidden]^T (half), ld >= vocab.
+ * Replaces the cublas_wrapper_->Gemm call of LlamaV2::postDecodeEmbedding
+ *   (src/turbomind/models/llama/LlamaV2.cc:312-372) for one rank's slice of the vocabulary (its
+ *   all-gather and transpose stay with the caller: tm_allgather, and the decode driver's own gather).
+ * hidden % 64 == 0; x and w 16-byte aligned.  A tcgen05 kernel of this library, no cuBLAS.
+ */
+TM_API int tm_lm_head_f16(tm_handle* h, float* logits, int ld, const void* x, const void* w, int tokens, int vocab, int hidden,
+                   void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Sampling of the next token from fp32 logits: temperature, repetition penalty, minimum length, then top-k
+ * sampling with the top-p cut inside the k candidates - one kernel in place of the reference's
+ *   invokeBatchApplyTemperaturePenalty / invokeBatchApplyRepetitionPenalty / invokeMinLengthPenalty
+ *       (src/turbomind/kernels/sampling_penalty_kernels.cu:118-146, 386-465, 486-517), in the order of
+ *       BaseSamplingLayer<T>::forward (src/turbomind/layers/sampling_layers/BaseSamplingLayer.cc:300-353), and
+ *   invokeBatchTopKSampling (src/turbomind/kernels/sampling_topk_kernels.cu:380-441)
+ * with the same draw: u = curand_uniform(state of the sequence); target = u * top_p * sum of exp(l_i - l_max) over
+ * the k candidates; candidates are walked in descending order.  Pointers are device pointers; optional ones may be
+ * NULL (that step is then skipped).  The logits are rewritten with the penalised values, as the reference's kernels do.
+ *   logits [batch][ld] fp32, vocab_size <= ld; the row must fit shared memory (vocab_size up to about 55 000)
+ *   output_ids [step][batch]: the tokens so far (prompt and generated), rows input_lengths[b] .. max_input_length - 1
+ *       of sequence b are padding and not penalised; repetition penalty is multiplicative (l < 0 ? l * p : l / p),
+ *       applied once per distinct token
+ *   min_lengths / sequence_lengths: the end id is masked while sequence_lengths[b] + 1 - max_input_length < min_lengths[b]
+ *   top_ks [batch] (else max_top_k for all), 1..1024; top_ps [batch] (else top_p), in (0, 1]
+ *   rng_states: curandState_t per sequence (tm_sampling_rng_state_bytes each, set by tm_sampling_rng_init, which is
+ *       curand_init(seed, 0, 0) as invokeCurandBatchInitialize does); or uniforms [batch] in (0, 1] supplied by the caller
+ *   finished [batch] (bytes): a finished sequence gets end_ids[b]; with sequence_lengths_out also set, both are
+ *       updated after the draw as topk_stage2_sampling does (length + 1, finished = drew the end id)
+ *   skip_decode [batch] (bytes): sequences left alone (the reference's per-request top_k == 0)
+ */
+typedef struct tm_sampling_params {
+    float*               logits;
+    int                  ld;
+    int                  vocab_size;
+    int                  batch_size;
+    const int*           output_ids;
+    int                  step;
+    const int*           input_lengths;
+    int                  max_input_length;
+    const float*         temperatures;
+    const float*         repetition_penalties;
+    const int*           min_lengths;
+    const int*           sequence_lengths;
+    const int*           end_ids;
+    const int*           top_ks;
+    int                  max_top_k;
+    const float*         top_ps;
+    float                top_p;
+    void*                rng_states;
+    const float*         uniforms;
+    int*                 ids;
+    int*                 sequence_lengths_out;
+    unsigned char*       finished;
+    const unsigned char* skip_decode;
+} tm_sampling_params;
+TM_API size_t tm_sampling_rng_state_bytes(void);
+/* seeds [batch] on the device, or NULL: every sequence starts from `seed` */
+TM_API int tm_sampling_rng_init(void* states, int batch_size, const unsigned long long* seeds, unsigned long long seed, void* stream);
+TM_API int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * RMSNorm of the decoder loop (half data, fp32 math).  Replace

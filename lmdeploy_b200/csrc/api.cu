@@ -75,9 +75,12 @@ extern "C" int tm_create(tm_handle** out, int device)
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, 256);
     if (e == cudaSuccess) e = gemm_small_prepare(h->max_smem);
     if (e == cudaSuccess) e = gemm_tc_prepare(h->max_smem);
+    if (e == cudaSuccess) e = lm_head_prepare(h->max_smem);
+    if (e == cudaSuccess) e = sampling_prepare(h->max_smem);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     h->pdl           = env_int("TM_B200_PDL", 1);
     h->p2p_allreduce = env_int("TM_B200_P2P_ALLREDUCE", 1);
+    h->lm_head_cublas = env_int("TM_B200_LM_HEAD_CUBLAS", 0);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->mmha_warps  = env_int("TM_B200_MMHA_WARPS", 0);
@@ -144,6 +147,9 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     else if (n == "p2p_allreduce" && (value == 0 || value == 1)) {
         // 0: the tensor-parallel decode step reduces with NCCL even where the peer-memory path is set up
         h->p2p_allreduce = value;
+    }
+    else if (n == "lm_head_cublas" && (value == 0 || value == 1)) {
+        h->lm_head_cublas = value;
     }
     else if (n == "pdl_direct" && (value == 0 || value == 1)) {
         // GEMM and attention calls made DIRECTLY through this handle also launch with programmatic stream
@@ -314,6 +320,15 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
 
 int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order,
                         const tmb::MmhaSeqDesc* desc = nullptr, const float2* rope_table = nullptr);
+
+extern "C" int tm_lm_head_f16(tm_handle* h, float* logits, int ld, const void* x, const void* w, int tokens, int vocab, int hidden,
+                              void* stream)
+{
+    if (!h) return TM_ERR_INVALID_ARG;
+    if (ld < vocab) return TM_ERR_INVALID_ARG;
+    return lm_head_launch(logits, ld, (const __half*)x, (const __half*)w, tokens, vocab, hidden, h->status, h->gemm_wait_cycles,
+                          h->max_smem, (cudaStream_t)stream, g_pdl != 0 || h->pdl_direct != 0, &h->launches);
+}
 
 extern "C" int tm_mmha_decode(tm_handle* h, const tm_mmha_params* a, void* stream)
 {

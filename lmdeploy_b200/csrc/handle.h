@@ -1,5 +1,6 @@
 // Per-device state behind the opaque tm_handle of the C ABI.
 #pragma once
+#include <cuda_fp16.h>
 
 #include "gemm_s4_f16.h"
 #include "mmha.h"
@@ -26,10 +27,16 @@ struct tm_handle {
     int                gemm_wait_cycles = 0; // 0 = default bound of the split-tile wait of the tcgen05 GEMM (option "gemm_wait_cycles")
     int                pdl_direct      = 0;  // option "pdl_direct": direct GEMM / attention calls launch with programmatic serialization too
     int                p2p_allreduce   = 1;  // TM_B200_P2P_ALLREDUCE / option "p2p_allreduce": peer-memory all-reduce + norm in the decode step
+    int                lm_head_cublas  = 0;  // TM_B200_LM_HEAD_CUBLAS=1 / option "lm_head_cublas": the decode step's lm-head through cuBLAS (comparison only)
     int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
 };
 
 namespace tmb {
+// lm_head.cu: logits[tokens][ld] (fp32) = x[tokens][hidden] . w[vocab][hidden]^T, fp16 operands, tcgen05
+cudaError_t lm_head_prepare(int max_smem);
+cudaError_t sampling_prepare(int max_smem);  // sampling.cu
+int lm_head_launch(float* logits, int ld, const __half* x, const __half* w, int tokens, int vocab, int hidden, unsigned* status,
+                   long long max_wait_cycles, int max_smem, cudaStream_t st, bool pdl, unsigned long long* launches);
 // Set by the decode driver around its launches (per host thread): the kernel launches made through
 // the C ABI on this thread carry the programmatic-dependent-launch attribute.  Off for direct callers,
 // who may put any kernel in front of ours.

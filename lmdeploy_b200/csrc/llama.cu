@@ -292,13 +292,20 @@ int run_step(StepCtx& c)
     const int   tp  = cfg.tensor_para_size;
     cublasSetStream(m.cublas, s);
     float* dst = tp > 1 ? m.logits_local : m.logits;
-    if (cublasGemmEx(m.cublas, CUBLAS_OP_T, CUBLAS_OP_N, m.local_vocab, B, m.hidden, &one, m.output_weight, CUDA_R_16F,
-                     m.hidden, m.hbuf, CUDA_R_16F, m.hidden, &zero, dst, CUDA_R_32F, m.local_vocab, CUBLAS_COMPUTE_32F,
-                     CUBLAS_GEMM_DEFAULT)
-        != CUBLAS_STATUS_SUCCESS) {
-        return c.rc = TM_ERR_CUDA;
+    if (m.h->lm_head_cublas) {
+        // comparison only: the library GEMM the reference uses
+        if (cublasGemmEx(m.cublas, CUBLAS_OP_T, CUBLAS_OP_N, m.local_vocab, B, m.hidden, &one, m.output_weight, CUDA_R_16F,
+                         m.hidden, m.hbuf, CUDA_R_16F, m.hidden, &zero, dst, CUDA_R_32F, m.local_vocab, CUBLAS_COMPUTE_32F,
+                         CUBLAS_GEMM_DEFAULT)
+            != CUBLAS_STATUS_SUCCESS) {
+            return c.rc = TM_ERR_CUDA;
+        }
+        ++c.launches;
     }
-    ++c.launches;
+    else if (!c.ok(lm_head_launch(dst, m.local_vocab, m.hbuf, (const __half*)m.output_weight, B, m.local_vocab, m.hidden, m.h->status,
+                                  m.h->gemm_wait_cycles, m.h->max_smem, s, g_pdl != 0, &c.launches))) {
+        return c.rc;
+    }
     if (tp > 1) {
         if (!c.ok(tm_allgather(m.comm, m.logits_local, m.logits, (size_t)B * m.local_vocab * sizeof(float), s))) return c.rc;
         ++c.launches;

@@ -1,0 +1,208 @@
+// Token sampling of the decode step: temperature, repetition penalty, minimum length, then top-k sampling with a
+// top-p cut inside the k candidates.  One kernel, one CTA per sequence, the logits row held in shared memory.
+//
+// Restates, for fp32 logits, what the reference runs as five launches per step
+//   batchApplyTemperaturePenalty   src/turbomind/kernels/sampling_penalty_kernels.cu:118-146   logit *= 1 / (T + 1e-6)
+//   batchApplyRepetitionPenalty    sampling_penalty_kernels.cu:386-430   multiplicative, every distinct token once
+//   batchApplyMinLengthPenalty     sampling_penalty_kernels.cu:486-500   end id masked while too short
+//   topk_stage1 / topk_stage2_sampling   src/turbomind/kernels/sampling_topk_kernels.cu:125-312
+// in the order of BaseSamplingLayer<T>::forward (src/turbomind/layers/sampling_layers/BaseSamplingLayer.cc:300-353).
+// The draw is the reference's: u = curand_uniform(state of the sequence), target = u * top_p * sum_k exp(l_i - l_max),
+// walk the candidates in descending order until the running sum reaches the target.  Equal logits are ordered by
+// token id (the reference leaves that to the reduction tree).
+#include "common.cuh"
+#include "handle.h"
+#include "tm_b200.h"
+
+#include <cfloat>
+#include <curand_kernel.h>
+
+namespace tmb {
+namespace {
+
+constexpr int kSampleThreads = 512;
+constexpr int kSampleMaxK    = 1024;  // TopKSamplingLayer.cu clamps top_k to 1024 as well
+
+struct Best {
+    float v;
+    int   i;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b)
+{
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling_params p)
+{
+    extern __shared__ float s_dyn[];
+    float*    s_row  = s_dyn;                                             // [vocab]
+    unsigned* s_seen = reinterpret_cast<unsigned*>(s_row + p.vocab_size); // bitmap of tokens to penalise
+    float*    s_cand = reinterpret_cast<float*>(s_seen + (p.vocab_size + 31) / 32);  // [k] exp(l_i - l_max)
+    int*      s_cid  = reinterpret_cast<int*>(s_cand + kSampleMaxK);                 // [k] token ids
+    __shared__ Best s_warp[kSampleThreads / 32];
+    __shared__ Best s_pick;
+
+    const int b   = blockIdx.x;
+    const int tid = threadIdx.x;
+    if (p.skip_decode && p.skip_decode[b]) return;
+    const int V = p.vocab_size;
+    if (p.finished && p.finished[b]) {
+        // topk_stage2_sampling: a finished sequence keeps emitting its end id and nothing else changes
+        if (tid == 0) p.ids[b] = p.end_ids[b];
+        return;
+    }
+    float*      row   = p.logits + (size_t)b * p.ld;
+    const float inv_t = p.temperatures ? 1.0f / (p.temperatures[b] + 1e-6f) : 1.0f;
+    const bool  scale = p.temperatures != nullptr;
+    for (int v = tid; v < V; v += kSampleThreads) s_row[v] = scale ? row[v] * inv_t : row[v];
+    const bool rep = p.repetition_penalties && p.output_ids && p.step > 0;
+    if (rep) {
+        for (int w = tid; w < (V + 31) / 32; w += kSampleThreads) s_seen[w] = 0u;
+    }
+    __syncthreads();
+    if (rep) {
+        const int in_len = p.input_lengths ? p.input_lengths[b] : p.max_input_length;
+        for (int s = tid; s < p.step; s += kSampleThreads) {
+            if (s >= in_len && s < p.max_input_length) continue;  // padding rows of the prompt block
+            const int tok = p.output_ids[(size_t)s * p.batch_size + b];
+            if (tok >= 0 && tok < V) atomicOr(&s_seen[tok >> 5], 1u << (tok & 31));
+        }
+        __syncthreads();
+        const float pen = p.repetition_penalties[b];
+        for (int v = tid; v < V; v += kSampleThreads) {
+            if (s_seen[v >> 5] >> (v & 31) & 1u) {
+                const float l = s_row[v];
+                s_row[v]      = l < 0.f ? l * pen : l / pen;
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0 && p.min_lengths && p.sequence_lengths && p.sequence_lengths[b] + 1 - p.max_input_length < p.min_lengths[b]) {
+        s_row[p.end_ids[b]] = -FLT_MAX;
+    }
+    __syncthreads();
+    // the reference's penalty kernels rewrite the logits: leave the same values behind
+    if (scale || rep || p.min_lengths) {
+        for (int v = tid; v < V; v += kSampleThreads) row[v] = s_row[v];
+    }
+
+    int k = p.top_ks ? p.top_ks[b] : p.max_top_k;
+    k     = max(1, min(k, min(kSampleMaxK, V)));
+    // every thread keeps the best of the elements it owns; an iteration takes the best of those, and only the owner
+    // of the element taken looks through its elements again
+    auto scan = [&]() {
+        Best m{-FLT_MAX, 0x7fffffff};
+        for (int v = tid; v < V; v += kSampleThreads) m = better(m, Best{s_row[v], v});
+        return m;
+    };
+    Best mine = scan();
+    for (int it = 0; it < k; ++it) {
+        Best w = mine;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, w.v, o), __shfl_xor_sync(0xffffffffu, w.i, o)};
+            w = better(w, other);
+        }
+        if ((tid & 31) == 0) s_warp[tid >> 5] = w;
+        __syncthreads();
+        if (tid < 32) {
+            Best t = tid < kSampleThreads / 32 ? s_warp[tid] : Best{-FLT_MAX, 0x7fffffff};
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                Best other{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
+                t = better(t, other);
+            }
+            if (tid == 0) {
+                s_pick     = t;
+                s_cand[it] = t.v;
+                s_cid[it]  = t.i;
+            }
+        }
+        __syncthreads();
+        const int taken = s_pick.i;
+        if (taken < V && (taken % kSampleThreads) == tid) {
+            s_row[taken] = -FLT_MAX;
+            mine         = scan();
+        }
+    }
+    if (tid == 0) {
+        const float l_max = s_cand[0];
+        float       sum   = 0.f;
+        for (int i = 0; i < k; ++i) {
+            const float e = __expf(s_cand[i] - l_max);
+            s_cand[i]     = e;
+            sum += e;
+        }
+        const float top_p = p.top_ps ? p.top_ps[b] : p.top_p;
+        float       u;
+        if (p.uniforms) {
+            u = p.uniforms[b];
+        }
+        else {
+            curandState_t* st = reinterpret_cast<curandState_t*>(p.rng_states) + b;
+            u                 = curand_uniform(st);
+        }
+        float r    = u * top_p * sum;
+        int   pick = s_cid[k - 1];
+        for (int i = 0; i < k; ++i) {
+            r -= s_cand[i];
+            if (r <= 0.f || i == k - 1) {
+                pick = s_cid[i];
+                break;
+            }
+        }
+        if (pick < 0 || pick >= V) pick = s_cid[0];
+        p.ids[b] = pick;
+        if (p.sequence_lengths_out && p.finished) {
+            p.sequence_lengths_out[b] += 1;
+            p.finished[b] = pick == p.end_ids[b] ? 1 : 0;
+        }
+    }
+}
+
+__global__ void rng_init_kernel(curandState_t* states, int n, const unsigned long long* seeds, unsigned long long seed)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) curand_init(seeds ? seeds[i] : seed, 0, 0, &states[i]);  // sampling_topk_kernels.cu:32-58
+}
+
+}  // namespace
+
+cudaError_t sampling_prepare(int max_smem)
+{
+    // the kernel also has a few static words: leave room for them
+    return cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 1024);
+}
+
+}  // namespace tmb
+
+using namespace tmb;
+
+extern "C" size_t tm_sampling_rng_state_bytes(void)
+{
+    return sizeof(curandState_t);
+}
+
+extern "C" int tm_sampling_rng_init(void* states, int batch_size, const unsigned long long* seeds, unsigned long long seed, void* stream)
+{
+    if (!states || batch_size <= 0) return TM_ERR_INVALID_ARG;
+    rng_init_kernel<<<(batch_size + 255) / 256, 256, 0, (cudaStream_t)stream>>>((curandState_t*)states, batch_size, seeds, seed);
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+extern "C" int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, void* stream)
+{
+    if (!h || !params) return TM_ERR_INVALID_ARG;
+    const tm_sampling_params& p = *params;
+    if (!p.logits || !p.ids || p.batch_size <= 0 || p.vocab_size <= 0 || p.ld < p.vocab_size) return TM_ERR_INVALID_ARG;
+    if (!p.uniforms && !p.rng_states) return TM_ERR_INVALID_ARG;
+    if ((p.finished || p.min_lengths) && !p.end_ids) return TM_ERR_INVALID_ARG;
+    if (!p.top_ks && (p.max_top_k < 1 || p.max_top_k > kSampleMaxK)) return TM_ERR_INVALID_ARG;
+    if (!p.top_ps && !(p.top_p > 0.f && p.top_p <= 1.f)) return TM_ERR_INVALID_ARG;
+    const size_t smem = (size_t)p.vocab_size * 4 + (size_t)((p.vocab_size + 31) / 32) * 4 + (size_t)kSampleMaxK * 8;
+    if (smem > (size_t)h->max_smem - 1024) return TM_ERR_UNSUPPORTED;  // the row must fit shared memory (about 55 000 tokens)
+    sample_topk_kernel<<<p.batch_size, kSampleThreads, smem, (cudaStream_t)stream>>>(p);
+    ++h->launches;
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}

@@ -74,6 +74,18 @@ class TmMmhaParams(C.Structure):
     ]
 
 
+class TmSamplingParams(C.Structure):
+    """ctypes mirror of ``tm_sampling_params`` (include/tm_b200.h), field for field."""
+    _fields_ = [
+        ("logits", C.c_void_p), ("ld", C.c_int), ("vocab_size", C.c_int), ("batch_size", C.c_int),
+        ("output_ids", C.c_void_p), ("step", C.c_int), ("input_lengths", C.c_void_p), ("max_input_length", C.c_int),
+        ("temperatures", C.c_void_p), ("repetition_penalties", C.c_void_p), ("min_lengths", C.c_void_p),
+        ("sequence_lengths", C.c_void_p), ("end_ids", C.c_void_p), ("top_ks", C.c_void_p), ("max_top_k", C.c_int),
+        ("top_ps", C.c_void_p), ("top_p", C.c_float), ("rng_states", C.c_void_p), ("uniforms", C.c_void_p),
+        ("ids", C.c_void_p), ("sequence_lengths_out", C.c_void_p), ("finished", C.c_void_p), ("skip_decode", C.c_void_p),
+    ]
+
+
 class TmContextAttentionParams(C.Structure):
     """ctypes mirror of ``tm_context_attention_params`` (include/tm_b200.h), field for field."""
     _fields_ = [
@@ -147,6 +159,10 @@ SIGNATURES = {
     "tm_transpose_qk_s4_k_m8_hf": (_i, [_u32p, _u32p, _i, _i, _i, _vp]),
     "tm_fuse_w1_w3_s4_k_m8": (_i, [_u32p, _u32p, _i, _i, _vp]),
     "tm_dequantize_s4": (_i, [_vp, _u32p, _sz, _vp]),
+    "tm_sampling_rng_state_bytes": (_sz, []),
+    "tm_sampling_rng_init": (_i, [_vp, _i, _vp, C.c_ulonglong, _vp]),
+    "tm_sample_topk": (_i, [_vp, C.POINTER(TmSamplingParams), _vp]),
+    "tm_lm_head_f16": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "tm_mmha_decode": (_i, [_vp, C.POINTER(TmMmhaParams), _vp]),
     "tm_comm_unique_id": (_i, [_vp]),
     "tm_comm_create": (_i, [C.POINTER(_vp), _i, _i, _vp, _i]),

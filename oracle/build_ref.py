@@ -28,6 +28,8 @@ REFERENCE_SOURCES = [
     "src/turbomind/models/llama/llama_kernels.cu",
     "src/turbomind/kernels/unfused_attention_kernels.cu",
     "src/turbomind/models/llama/LlamaCacheManager.cc",
+    "src/turbomind/kernels/sampling_penalty_kernels.cu",
+    "src/turbomind/kernels/sampling_topk_kernels.cu",
     "src/turbomind/utils/logger.cc",
     "src/turbomind/utils/Tensor.cc",
 ]

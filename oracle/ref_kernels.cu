@@ -370,3 +370,46 @@ REF_API int ref_cache_contains(void* h, unsigned long long id)
 {
     return ((RefCacheManager*)h)->mgr->contains(id) ? 1 : 0;
 }
+
+// ---- token sampling: the reference's penalty and top-k sampling kernels, as BaseSamplingLayer::forward and
+// ---- TopKSamplingLayer::runSampling call them (fp32 logits)
+#include "src/turbomind/kernels/sampling_penalty_kernels.h"
+#include "src/turbomind/kernels/sampling_topk_kernels.h"
+
+REF_API size_t ref_curand_state_bytes()
+{
+    return sizeof(curandState_t);
+}
+
+REF_API int ref_curand_batch_init(void* states, int batch, const unsigned long long* seeds, cudaStream_t st)
+{
+    turbomind::invokeCurandBatchInitialize((curandState_t*)states, (size_t)batch, seeds, st);
+    return finish(st);
+}
+
+// temperature -> repetition penalty (multiplicative) -> minimum length; any of the three pointers may be null
+REF_API int ref_sampling_penalties(float* logits, int batch, int vocab, const float* temperatures, const float* rep_penalties,
+                                   const int* output_ids, const int* input_lengths, int max_input_length, int step,
+                                   const int* min_lengths, const int* end_ids, const int* sequence_lengths, cudaStream_t st)
+{
+    if (temperatures) turbomind::invokeBatchApplyTemperaturePenalty(logits, (const float*)nullptr, temperatures, batch, vocab, vocab, st);
+    if (rep_penalties && step > 0) {
+        turbomind::invokeBatchApplyRepetitionPenalty(logits, rep_penalties, output_ids, batch, batch, vocab, input_lengths,
+                                                     max_input_length, step, turbomind::RepetitionPenaltyType::Multiplicative, st);
+    }
+    if (min_lengths) turbomind::invokeMinLengthPenalty(logits, min_lengths, end_ids, sequence_lengths, max_input_length, batch, vocab, st);
+    return finish(st);
+}
+
+// workspace == null: returns the bytes needed in *workspace_bytes
+REF_API int ref_batch_topk_sampling(void* workspace, size_t* workspace_bytes, const float* logits, int* ids, int* sequence_length,
+                                    bool* finished, void* curand_states, int max_top_k, const int* top_ks, const float* top_ps,
+                                    int vocab, const int* end_ids, int batch, const bool* skip_decode, cudaStream_t st)
+{
+    size_t ws = *workspace_bytes;
+    turbomind::invokeBatchTopKSampling(workspace, ws, logits, ids, sequence_length, finished, (float*)nullptr, (float*)nullptr,
+                                       (curandState_t*)curand_states, max_top_k, top_ks, 1.0f, top_ps, vocab, end_ids, st, batch,
+                                       skip_decode);
+    *workspace_bytes = ws;
+    return workspace ? finish(st) : 0;
+}

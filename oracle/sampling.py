@@ -1,0 +1,78 @@
+"""CPU restatement of the reference's token sampling for fp32 logits.  Test infrastructure only: nothing under
+``lmdeploy_b200/`` may import this.
+
+Follows, in the order of ``BaseSamplingLayer<T>::forward``
+(src/turbomind/layers/sampling_layers/BaseSamplingLayer.cc:300-353):
+
+* ``batchApplyTemperaturePenalty``  (src/turbomind/kernels/sampling_penalty_kernels.cu:118-146)
+* ``batchApplyRepetitionPenalty``   (sampling_penalty_kernels.cu:386-430, multiplicative; a token that occurs several
+  times is penalised once, because every occurrence writes the value computed from the unpenalised logit)
+* ``batchApplyMinLengthPenalty``    (sampling_penalty_kernels.cu:486-500)
+* ``topk_stage1`` + ``topk_stage2_sampling`` (src/turbomind/kernels/sampling_topk_kernels.cu:125-312): the k largest
+  logits in descending order, ``e_i = exp(l_i - l_max)``, target ``u * top_p * sum(e)``, first i whose running sum
+  reaches the target (the last one otherwise).
+
+Pinned on a GPU against those kernels compiled unmodified into ``oracle/_ref`` (tests/test_gpu_sampling.py), where the
+uniform numbers come from the same curand states.  Here the uniform number is an input.
+"""
+import numpy as np
+
+FLT_MAX = np.float32(3.4028234663852886e38)
+
+
+def apply_penalties(logits, temperatures=None, repetition_penalties=None, output_ids=None, input_lengths=None,
+                    max_input_length=0, min_lengths=None, end_ids=None, sequence_lengths=None):
+    """logits [batch, vocab] float32 -> penalised copy.  output_ids [step, batch]."""
+    x = np.array(logits, dtype=np.float32, copy=True)
+    B = x.shape[0]
+    if temperatures is not None:
+        inv = (np.float32(1.0) / (np.asarray(temperatures, np.float32) + np.float32(1e-6))).astype(np.float32)
+        x = (x * inv[:, None]).astype(np.float32)
+    if repetition_penalties is not None and output_ids is not None and len(output_ids) > 0:
+        ids = np.asarray(output_ids)
+        for b in range(B):
+            in_len = max_input_length if input_lengths is None else int(input_lengths[b])
+            keep = [s for s in range(ids.shape[0]) if not (in_len <= s < max_input_length)]
+            toks = np.unique(ids[keep, b])
+            pen = np.float32(repetition_penalties[b])
+            old = x[b, toks]
+            x[b, toks] = np.where(old < 0, old * pen, old / pen).astype(np.float32)
+    if min_lengths is not None:
+        for b in range(B):
+            if int(sequence_lengths[b]) + 1 - max_input_length < int(min_lengths[b]):
+                x[b, int(end_ids[b])] = -FLT_MAX
+    return x
+
+
+def topk_sample(logits, top_k, top_p, u):
+    """One row.  Returns (token id, margin): margin is the distance of the target from the nearest boundary of the
+    chosen candidate's interval, relative to the sum - a test can skip draws that sit on a boundary."""
+    x = np.asarray(logits, dtype=np.float32)
+    k = max(1, min(int(top_k), x.shape[0]))
+    order = np.lexsort((np.arange(x.shape[0]), -x.astype(np.float64)))[:k]      # descending value, then ascending id
+    e = np.exp((x[order] - x[order[0]]).astype(np.float32)).astype(np.float32)
+    total = np.float32(0)
+    for v in e:
+        total = np.float32(total + v)
+    r = np.float32(np.float32(np.float32(u) * np.float32(top_p)) * total)
+    target = float(r)
+    run = 0.0
+    for i in range(k):
+        r = np.float32(r - e[i])
+        lo, run = run, run + float(e[i])
+        if r <= 0 or i == k - 1:
+            margin = min(abs(target - lo), abs(run - target)) / float(total)
+            return int(order[i]), margin
+    raise AssertionError("unreachable")
+
+
+def sample(logits, top_ks, top_ps, uniforms, finished=None, end_ids=None):
+    """Batch version: ids [batch], margins [batch]."""
+    B = len(logits)
+    ids, margins = np.zeros(B, np.int32), np.ones(B)
+    for b in range(B):
+        if finished is not None and finished[b]:
+            ids[b] = end_ids[b]
+            continue
+        ids[b], margins[b] = topk_sample(logits[b], top_ks[b], top_ps[b], uniforms[b])
+    return ids, margins

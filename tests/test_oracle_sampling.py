@@ -1,0 +1,37 @@
+"""CPU: known answers for the sampling oracle (oracle/sampling.py)."""
+import numpy as np
+
+from oracle import sampling as osamp
+
+
+def test_topk_sample_known_answers():
+    x = np.array([0.0, 2.0, 1.0, -1.0, 2.0], np.float32)
+    # candidates in descending order, ties by id: 1, 4, 2 ; e = 1, 1, e^-1
+    tot = 2 + np.exp(-1.0)
+    assert osamp.topk_sample(x, 3, 1.0, 0.2)[0] == 1            # target 0.2 * tot < 1
+    assert osamp.topk_sample(x, 3, 1.0, 1.5 / tot)[0] == 4      # 1 < target < 2
+    assert osamp.topk_sample(x, 3, 1.0, 1.0)[0] == 2            # target = whole sum: last candidate
+    assert osamp.topk_sample(x, 3, 0.4, 1.0)[0] == 1            # top_p shrinks the target: 0.4 * tot < 1
+    assert osamp.topk_sample(x, 1, 1.0, 0.99)[0] == 1           # k = 1 is greedy
+    assert osamp.topk_sample(x, 99, 1.0, 1e-9)[0] == 1          # k larger than the vocabulary
+
+
+def test_penalties_known_answers():
+    x = np.array([[1.0, -2.0, 4.0, 8.0]], np.float32)
+    y = osamp.apply_penalties(x, temperatures=[0.5])
+    np.testing.assert_allclose(y, x / np.float32(0.5 + 1e-6), rtol=1e-6)
+    # token 2 twice and token 1 once in the history; row 1 is prompt padding (input length 1 of 2)
+    ids = np.array([[2], [3], [1], [2]])
+    y = osamp.apply_penalties(x, repetition_penalties=[2.0], output_ids=ids, input_lengths=[1], max_input_length=2)
+    np.testing.assert_array_equal(y, np.array([[1.0, -4.0, 2.0, 8.0]], np.float32))
+    # generated so far = sequence_length + 1 - max_input_length = 1 < 3: the end id is masked
+    y = osamp.apply_penalties(x, min_lengths=[3], end_ids=[3], sequence_lengths=[2], max_input_length=2)
+    assert y[0, 3] == -osamp.FLT_MAX and (y[0, :3] == x[0, :3]).all()
+    y = osamp.apply_penalties(x, min_lengths=[1], end_ids=[3], sequence_lengths=[2], max_input_length=2)
+    assert (y == x).all()
+
+
+def test_finished_rows_emit_the_end_id():
+    x = np.random.default_rng(0).standard_normal((3, 50)).astype(np.float32)
+    ids, _ = osamp.sample(x, [5, 5, 5], [1.0, 1.0, 1.0], [0.5, 0.5, 0.5], finished=[0, 1, 0], end_ids=[2, 2, 2])
+    assert ids[1] == 2
