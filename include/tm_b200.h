@@ -236,6 +236,7 @@ typedef struct tm_sampling_params {
     int*                 sequence_lengths_out;
     unsigned char*       finished;
     const unsigned char* skip_decode;
+    int                  output_ids_stride; /* ints between the rows of output_ids; 0 = batch_size */
 } tm_sampling_params;
 TM_API size_t tm_sampling_rng_state_bytes(void);
 /* seeds [batch] on the device, or NULL: every sequence starts from `seed` */
@@ -542,6 +543,45 @@ TM_API unsigned long long tm_llama_last_launches(const tm_llama* m);
  * This call synchronises `stream`, reads and clears that word: TM_OK, or TM_ERR_DEVICE_TIMEOUT with the bits in
  * *word (tm_check_device_status on the model's handle).  Call it wherever the host synchronises anyway. */
 TM_API int tm_llama_check_status(tm_llama* m, void* stream, unsigned* word);
+
+/* ------------------------------------------------------------------------------------------
+ * Persistent-batch scheduler over tm_cache_*, tm_llama_prefill, tm_llama_decode and tm_sample_topk: the part of
+ * LlamaBatch<T> (src/turbomind/models/llama/LlamaBatch.cc: initialize :562-763, contextDecode :765-877, generate
+ * :471-559, finish / finishRequest :930-970, 1056-1118) that decides who runs.  Requests wait in a queue; every
+ * tm_batch_step admits as many as there are free slots (their session's cached tokens come back from the cache
+ * manager, everything without keys / values except the last token is context-decoded, at most
+ * max_context_token_num new tokens per prefill call), runs ONE decoder step for all live sequences, draws one
+ * token for each, and retires the sequences that drew `end_id` or reached their length: their tokens and cache
+ * length go back to the cache manager (tm_cache_update), or the slab is released when end_flag was set.
+ * Live sequences are kept dense in the batch; nothing is padded.  Not thread-safe: one host thread per scheduler.
+ * Sampling fields of a request: top_k 0 and top_p 0 mean greedy, top_p 0 means 1, temperature / repetition_penalty 0
+ * mean 1 (TopKSamplingLayer<T>::setup, src/turbomind/layers/sampling_layers/TopKSamplingLayer.cu:60-112).
+ * With tensor parallelism every rank runs its own scheduler on the same requests and seeds and draws the same tokens.
+ */
+typedef struct tm_batch tm_batch;
+typedef struct tm_request {
+    uint64_t           id;                 /* session id: the key of the cache manager                      */
+    int                start_flag;         /* first request of the session: a new cache slab               */
+    int                end_flag;           /* last request of the session: the slab is released at the end */
+    const int*         input_ids;          /* host memory, copied by tm_batch_submit                        */
+    int                input_length;
+    int                request_output_len; /* new tokens wanted (cut so that the sequence fits session_len) */
+    int                top_k;
+    float              top_p;
+    float              temperature;
+    float              repetition_penalty;
+    unsigned long long random_seed;
+    int                ignore_eos;
+} tm_request;
+enum { TM_REQUEST_QUEUED = 0, TM_REQUEST_RUNNING = 1, TM_REQUEST_FINISHED = 2, TM_REQUEST_FAILED = 3 };
+TM_API int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager* cache, int max_batch_size, int session_len,
+                           int start_id, int end_id, int max_context_token_num);
+TM_API int tm_batch_destroy(tm_batch* b);
+TM_API int tm_batch_submit(tm_batch* b, const tm_request* r);
+TM_API int tm_batch_step(tm_batch* b, void* stream, int use_graph);
+/* tokens generated so far for the session's latest request (first min(capacity, *count) of them) and its state */
+TM_API int tm_batch_output(const tm_batch* b, uint64_t id, int* tokens, size_t capacity, size_t* count, int* state);
+TM_API int tm_batch_counts(const tm_batch* b, int* active, int* pending, unsigned long long* steps, unsigned long long* prefill_tokens);
 
 #ifdef __cplusplus
 }

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling
         const int in_len = p.input_lengths ? p.input_lengths[b] : p.max_input_length;
         for (int s = tid; s < p.step; s += kSampleThreads) {
             if (s >= in_len && s < p.max_input_length) continue;  // padding rows of the prompt block
-            const int tok = p.output_ids[(size_t)s * p.batch_size + b];
+            const int tok = p.output_ids[(size_t)s * (p.output_ids_stride > 0 ? p.output_ids_stride : p.batch_size) + b];
             if (tok >= 0 && tok < V) atomicOr(&s_seen[tok >> 5], 1u << (tok & 31));
         }
         __syncthreads();

@@ -83,7 +83,16 @@ class TmSamplingParams(C.Structure):
         ("sequence_lengths", C.c_void_p), ("end_ids", C.c_void_p), ("top_ks", C.c_void_p), ("max_top_k", C.c_int),
         ("top_ps", C.c_void_p), ("top_p", C.c_float), ("rng_states", C.c_void_p), ("uniforms", C.c_void_p),
         ("ids", C.c_void_p), ("sequence_lengths_out", C.c_void_p), ("finished", C.c_void_p), ("skip_decode", C.c_void_p),
+        ("output_ids_stride", C.c_int),
     ]
+
+
+class TmRequest(C.Structure):
+    """ctypes mirror of ``tm_request``."""
+    _fields_ = [("id", C.c_uint64), ("start_flag", C.c_int), ("end_flag", C.c_int), ("input_ids", C.POINTER(C.c_int)),
+                ("input_length", C.c_int), ("request_output_len", C.c_int), ("top_k", C.c_int), ("top_p", C.c_float),
+                ("temperature", C.c_float), ("repetition_penalty", C.c_float), ("random_seed", C.c_ulonglong),
+                ("ignore_eos", C.c_int)]
 
 
 class TmContextAttentionParams(C.Structure):
@@ -159,6 +168,12 @@ SIGNATURES = {
     "tm_transpose_qk_s4_k_m8_hf": (_i, [_u32p, _u32p, _i, _i, _i, _vp]),
     "tm_fuse_w1_w3_s4_k_m8": (_i, [_u32p, _u32p, _i, _i, _vp]),
     "tm_dequantize_s4": (_i, [_vp, _u32p, _sz, _vp]),
+    "tm_batch_create": (_i, [C.POINTER(_vp), _vp, _vp, _i, _i, _i, _i, _i]),
+    "tm_batch_destroy": (_i, [_vp]),
+    "tm_batch_submit": (_i, [_vp, C.POINTER(TmRequest)]),
+    "tm_batch_step": (_i, [_vp, _vp, _i]),
+    "tm_batch_output": (_i, [_vp, C.c_uint64, C.POINTER(C.c_int), _sz, C.POINTER(_sz), C.POINTER(_i)]),
+    "tm_batch_counts": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]),
     "tm_sampling_rng_state_bytes": (_sz, []),
     "tm_sampling_rng_init": (_i, [_vp, _i, _vp, C.c_ulonglong, _vp]),
     "tm_sample_topk": (_i, [_vp, C.POINTER(TmSamplingParams), _vp]),

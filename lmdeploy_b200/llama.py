@@ -285,3 +285,70 @@ def tp_column_index(cfg: LlamaConfig, tp: int, rank: int):
                 w13_cols=np.arange(rank * 2 * inter, (rank + 1) * 2 * inter),
                 w2_rows=np.arange(rank * inter, (rank + 1) * inter),
                 vocab_rows=np.arange(rank * (cfg.vocab_size // tp), (rank + 1) * (cfg.vocab_size // tp)))
+
+
+# -- persistent-batch scheduler ------------------------------------------------------------------------------------
+class Batch:
+    """tm_batch (include/tm_b200.h): requests in, tokens out; a cache manager sized for the model is created with it.
+
+    ``submit`` queues a request, ``step`` runs one scheduling round (intake + context decode + one decoder step + one
+    draw), ``output`` returns the tokens generated so far for a session's latest request and its state."""
+
+    QUEUED, RUNNING, FINISHED, FAILED = 0, 1, 2, 3
+
+    def __init__(self, model: LlamaModel, max_batch_size: int, start_id: int = 1, end_id: int = 2, cache_max_entry_count: int = 0,
+                 cache_chunk_size: int = 1, max_context_token_num: int = 0):
+        cfg = model.cfg
+        self.model = model
+        self._cache = C.c_void_p()
+        entries = cache_max_entry_count or max_batch_size
+        _l.check(_l.lib.tm_cache_manager_create(C.byref(self._cache), cfg.num_layer, cfg.kv_head_num // model.tp, cfg.size_per_head,
+                                                model.session_len, 8 if cfg.quant_policy & 4 else 16, entries, cache_chunk_size,
+                                                model.device), "tm_cache_manager_create")
+        self._b = C.c_void_p()
+        _l.check(_l.lib.tm_batch_create(C.byref(self._b), model._m, self._cache, max_batch_size, model.session_len, start_id, end_id,
+                                        max_context_token_num), "tm_batch_create")
+
+    def submit(self, session_id: int, input_ids, request_output_len: int, start: bool = True, end: bool = True, top_k: int = 0,
+               top_p: float = 0.0, temperature: float = 0.0, repetition_penalty: float = 0.0, random_seed: int = 0,
+               ignore_eos: bool = False) -> int:
+        ids = (C.c_int * max(1, len(input_ids)))(*[int(t) for t in input_ids])
+        r = _l.TmRequest(session_id, int(start), int(end), ids, len(input_ids), request_output_len, top_k, top_p, temperature,
+                         repetition_penalty, random_seed, int(ignore_eos))
+        return _l.lib.tm_batch_submit(self._b, C.byref(r))
+
+    def step(self, use_graph: bool = False, stream=None) -> None:
+        s = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        _l.check(_l.lib.tm_batch_step(self._b, C.c_void_p(s), int(use_graph)), "tm_batch_step")
+
+    def output(self, session_id: int):
+        n, state = C.c_size_t(0), C.c_int(0)
+        _l.check(_l.lib.tm_batch_output(self._b, session_id, None, 0, C.byref(n), C.byref(state)), "tm_batch_output")
+        buf = (C.c_int * max(1, n.value))()
+        _l.check(_l.lib.tm_batch_output(self._b, session_id, buf, n.value, C.byref(n), C.byref(state)), "tm_batch_output")
+        return list(buf[:n.value]), state.value
+
+    def counts(self):
+        a, p, s, t = C.c_int(0), C.c_int(0), C.c_ulonglong(0), C.c_ulonglong(0)
+        _l.check(_l.lib.tm_batch_counts(self._b, C.byref(a), C.byref(p), C.byref(s), C.byref(t)), "tm_batch_counts")
+        return dict(active=a.value, pending=p.value, steps=s.value, prefill_tokens=t.value)
+
+    def has_session(self, session_id: int) -> bool:
+        return bool(_l.lib.tm_cache_contains(self._cache, session_id))
+
+    def run(self, max_rounds: int = 100000, use_graph: bool = False) -> None:
+        """rounds until nothing is queued or running"""
+        for _ in range(max_rounds):
+            c = self.counts()
+            if c["active"] == 0 and c["pending"] == 0:
+                return
+            self.step(use_graph)
+        raise RuntimeError("scheduler did not drain")
+
+    def close(self):
+        if self._b:
+            _l.lib.tm_batch_destroy(self._b)
+            self._b = C.c_void_p()
+        if self._cache:
+            _l.lib.tm_cache_manager_destroy(self._cache)
+            self._cache = C.c_void_p()
