@@ -643,11 +643,6 @@ def run_prefill_workload(args, rank, world, device):
     if reflib is not None:
         mark_reference_kernel_arm(res)
         return res
-    ms_e2e = max_over_ranks(ms_e2e, world)
-    res["e2e"] = {"value": round(nbytes / (ms_e2e * 1e-3) * 1e-9 * world, 1), "unit": "GB/s", "ms_per_step": round(ms_e2e, 4),
-                  "h2d_bytes_per_step": int(qkv.numel() * 2), "d2h_bytes_per_step": int(out.numel() * 2)}
-    if rank == 0 and not args.no_cpu:
-        res["cpu_baseline"] = cpu_mmha_baseline(lengths, H, Hkv, int8)
     return res
 
 

@@ -115,22 +115,6 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr)
            | ((uint64_t)2 << 61);
 }
 
-// D(tmem) (+)= A(tmem) x B(smem descriptor)
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d),
-        "r"(tmem_a),
-        "l"(desc_b),
-        "r"(idesc),
-        "r"(accumulate)
-        : "memory");
-}
-
 // Four MMAs: one 64-wide K block (four 16-wide steps) of a unit, operands precomputed so that an MMA costs the
 // issuing thread three instructions.  `first`: the first MMA overwrites the accumulator.
 __device__ __forceinline__ void umma_f16_ts_x4(uint32_t tmem_d, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi, uint32_t idesc,

@@ -6,8 +6,10 @@
 // (LlamaV2.cc:184-201, 312-372) of lmdeploy v0.0.9.
 #include "llama.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
+#include <nvtx3/nvToolsExt.h>
 
 int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int pos_from_length, const int* order,
                         const tmb::MmhaSeqDesc* desc = nullptr, const float2* rope_table = nullptr);
@@ -167,6 +169,29 @@ __global__ void gather_logits_kernel(float* out, const float* in, int B, int loc
     }
 }
 
+// Named ranges for timeline tools, off unless TM_B200_NVTX=1 (the reference: PUSH_RANGE / POP_RANGE,
+// src/turbomind/utils/nvtx_utils.h:37-49, at LlamaDecoderSelfAttentionLayer.cc:163,239 and LlamaFfnLayer.cc:87).
+// Header-only NVTX: without a tool attached a push is a null call.  Ranges mark host-side enqueue order; inside a
+// replayed CUDA graph they are not re-emitted.
+struct NvtxRange {
+    static bool enabled()
+    {
+        static const bool on = [] {
+            const char* e = std::getenv("TM_B200_NVTX");
+            return e && e[0] == '1';
+        }();
+        return on;
+    }
+    explicit NvtxRange(const char* name)
+    {
+        if (enabled()) nvtxRangePushA(name);
+    }
+    ~NvtxRange()
+    {
+        if (enabled()) nvtxRangePop();
+    }
+};
+
 struct StepCtx {
     tm_llama*                    m;
     const tm_llama_decode_state* st;
@@ -239,7 +264,10 @@ int run_step(StepCtx& c)
     for (int l = 0; l < cfg.num_layer; ++l) {
         const LlamaDecoderLayerWeight& w = m.layers[l];
         // ---- self attention (LlamaDecoderSelfAttentionLayer.cc:193-304)
-        if (!c.ok(linear.forward(m.qkv, m.hbuf, B, w.qkv, LlamaLinear::kGemm, s))) return c.rc;
+        {
+            NvtxRange r("qkv_gemm");
+            if (!c.ok(linear.forward(m.qkv, m.hbuf, B, w.qkv, LlamaLinear::kGemm, s))) return c.rc;
+        }
         tm_mmha_params a;
         std::memset(&a, 0, sizeof(a));
         a.out    = m.ctx;
@@ -271,13 +299,22 @@ int run_step(StepCtx& c)
         a.attention_k_zp             = w.past_kv_scale[1];
         a.attention_v_scale          = w.past_kv_scale[2];
         a.attention_v_zp             = w.past_kv_scale[3];
-        if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order, m.seq_desc, m.rope_table))) return c.rc;
-        if (!c.ok(linear.forward(part_o, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
+        {
+            NvtxRange r("scaled dot-product fusion");
+            if (!c.ok(tm_mmha_decode_impl(m.h, &a, s, 1, m.order, m.seq_desc, m.rope_table))) return c.rc;
+        }
+        {
+            NvtxRange r("o_gemm");
+            if (!c.ok(linear.forward(part_o, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
+        }
         // ---- [sum over ranks] ; x += attn ; h = RMSNorm(x) * ffn_norm   (LlamaDecoder.cc:212-220)
         if (!reduce_add_norm(0, w.ffn_norm_weights)) return c.rc;
         // ---- feed forward (LlamaFfnLayer.cc:66-116): fused w1|w3 GEMM with the SiLU epilogue, then w2
-        if (!c.ok(linear.forward(m.ffn, m.hbuf, B, w.fused_gating_intermediate, LlamaLinear::kFusedSiluFfn, s))) return c.rc;
-        if (!c.ok(linear.forward(part_f, m.ffn, B, w.ffn_output, LlamaLinear::kGemm, s))) return c.rc;
+        {
+            NvtxRange r("ffn");
+            if (!c.ok(linear.forward(m.ffn, m.hbuf, B, w.fused_gating_intermediate, LlamaLinear::kFusedSiluFfn, s))) return c.rc;
+            if (!c.ok(linear.forward(part_f, m.ffn, B, w.ffn_output, LlamaLinear::kGemm, s))) return c.rc;
+        }
         const void* next_norm = l + 1 < cfg.num_layer ? m.layers[l + 1].self_attn_norm_weights : m.output_norm;
         if (!reduce_add_norm(1, next_norm)) return c.rc;
     }
