@@ -57,7 +57,7 @@ def test_small_shapes_all_token_counts(n, k, t):
 
 
 @pytest.mark.parametrize("n,k", [(64, 128), (192, 512), (22016, 4096)])
-@pytest.mark.parametrize("t", [1, 8, 16, 40])
+@pytest.mark.parametrize("t", [1, 2, 8, 16, 40])
 def test_fused_silu(n, k, t):
     lin = _linear(n, k, 11)
     x = _x(t, k, 100 + t)
@@ -75,7 +75,7 @@ LLAMA7B = [("qkv", 12288, 4096), ("o", 4096, 4096), ("gate_up", 22016, 4096), ("
 
 
 @pytest.mark.parametrize("name,n,k", LLAMA7B)
-@pytest.mark.parametrize("t", [1, 8, 16, 17, 64, 128])
+@pytest.mark.parametrize("t", [1, 2, 8, 16, 17, 64, 128])
 def test_llama7b_projections(name, n, k, t):
     lin = _linear(n, k, 0)
     x = _x(t, k, t)
