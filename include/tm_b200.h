@@ -304,6 +304,8 @@ TM_API int tm_transpose_kv_cache(void* key_cache_trans, void* val_cache_trans, c
  * Query i of sequence b sits at position context_lengths[b] - q_len[b] + i and sees keys [0, position];
  * q_len[b] = cu_seqlens[b + 1] - cu_seqlens[b]; its output row is cu_seqlens[b] + i.
  * The new tokens' keys / values must already be in the cache (tm_extend_kv_cache).
+ * Runs on the tcgen05 tensor core (scores and output accumulate in TMEM); TM_B200_CTX_ATTN_LEGACY=1 selects the
+ * earlier mma.sync kernel for comparison.
  */
 typedef struct tm_context_attention_params {
     void*        attn_out;           /* half [token_num, head_num * 128]                           */
@@ -321,8 +323,14 @@ typedef struct tm_context_attention_params {
     int          max_seq_len;        /* rows per head of the cache                                 */
     int          quant_policy;       /* & 4: int8 cache                                            */
     float        kv_scale[4];        /* k_scale, k_zp, v_scale, v_zp                               */
+    unsigned*    status_word;        /* optional device word (a handle's): a bounded wait inside the
+                                        kernel that gives up sets a bit there; NULL = a word kept by
+                                        the library, read with tm_context_attention_last_status      */
 } tm_context_attention_params;
 TM_API int tm_context_attention(const tm_context_attention_params* params, void* stream);
+/* Synchronises the device, then reads and clears the status word the library keeps for calls that passed no
+ * status_word of their own (current device).  0 = no wait gave up. */
+TM_API int tm_context_attention_last_status(unsigned* word);
 
 /* ------------------------------------------------------------------------------------------
  * Tensor-parallel communicator (one process per GPU; NCCL over NVLink).  Replaces

@@ -14,7 +14,10 @@
 // in registers, probabilities rounded to fp16 for the second product.  Tiles above the causal
 // diagonal are never visited; the longest query tiles are scheduled first.
 #include "common.cuh"
+#include "context_attention.h"
 #include "tm_b200.h"
+
+#include <cstdlib>
 
 namespace tmb {
 namespace {
@@ -26,18 +29,6 @@ constexpr int kThreads = 128;
 constexpr int kTileBytes = kBN * kD * 2;                         // 16 KB
 constexpr int kSmemBytes = kBM * kD * 2 + 4 * kTileBytes;        // q + 2 x (k, v) = 80 KB
 
-struct CtxParams {
-    __half*       out;
-    const __half* q;  // [B, H, max_q_len, 128]
-    void* const*  k_cache;
-    void* const*  v_cache;
-    size_t        offset;  // elements
-    const int*    cu_seqlens;
-    const int*    context_length;
-    int           max_q_len, max_seq_len, H, n_rep;
-    float         scale_log2;  // softmax scale * log2(e)
-    float         k_scale, k_zp, v_scale, v_zp;
-};
 
 // byte offset of the 16-byte chunk `chunk` (0..15) of row `row` in a [rows][128] fp16 tile
 __device__ __forceinline__ uint32_t tile_off(int row, int chunk)
@@ -333,6 +324,23 @@ __global__ void __launch_bounds__(kThreads) context_attention_kernel(CtxParams p
 
 using namespace tmb;
 
+namespace {
+unsigned* own_status[64] = {};  // per device: the status word of callers that bring none
+}
+
+extern "C" int tm_context_attention_last_status(unsigned* word)
+{
+    if (!word) return TM_ERR_INVALID_ARG;
+    *word   = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TM_ERR_CUDA;
+    if (!own_status[dev]) return TM_OK;
+    if (cudaDeviceSynchronize() != cudaSuccess) return TM_ERR_CUDA;
+    if (cudaMemcpy(word, own_status[dev], sizeof(unsigned), cudaMemcpyDeviceToHost) != cudaSuccess) return TM_ERR_CUDA;
+    if (*word) cudaMemset(own_status[dev], 0, sizeof(unsigned));
+    return TM_OK;
+}
+
 extern "C" int tm_context_attention(const tm_context_attention_params* a, void* stream)
 {
     if (!a || !a->attn_out || !a->query || !a->key_cache || !a->val_cache || !a->cu_seqlens || !a->context_lengths) {
@@ -354,6 +362,27 @@ extern "C" int tm_context_attention(const tm_context_attention_params* a, void* 
     p.max_q_len = a->max_q_len, p.max_seq_len = a->max_seq_len, p.H = a->head_num, p.n_rep = a->head_num / a->kv_head_num;
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)kD);
     p.k_scale = a->kv_scale[0], p.k_zp = a->kv_scale[1], p.v_scale = a->kv_scale[2], p.v_zp = a->kv_scale[3];
+    // bounded waits of the tcgen05 kernel report into the caller's status word, or into one kept by the library
+    // (tm_context_attention_last_status) when the caller has none
+    p.status = a->status_word;
+    if (!p.status) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TM_ERR_CUDA;
+        if (!own_status[dev]) {
+            if (cudaMalloc((void**)&own_status[dev], sizeof(unsigned)) != cudaSuccess) return TM_ERR_CUDA;
+            cudaMemset(own_status[dev], 0, sizeof(unsigned));
+        }
+        p.status = own_status[dev];
+    }
+    p.max_wait_cycles = kMaxWaitCycles;
+    // TM_B200_CTX_ATTN_LEGACY=1: the mma.sync kernel below instead of the tcgen05 one (comparison)
+    static const bool legacy = [] {
+        const char* e = std::getenv("TM_B200_CTX_ATTN_LEGACY");
+        return e && e[0] == '1';
+    }();
+    if (!legacy) {
+        return context_attention_tc_launch(p, int8, a->batch_size, (cudaStream_t)stream) == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+    }
     auto kernel = int8 ? context_attention_kernel<true> : context_attention_kernel<false>;
     // per call, like every attribute in this library that depends on the current device; cheap next to the kernel
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return TM_ERR_CUDA;

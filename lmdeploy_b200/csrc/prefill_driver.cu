@@ -123,6 +123,7 @@ extern "C" int tm_llama_prefill(tm_llama* m, const tm_llama_prefill_state* st, v
         a.batch_size = B, a.head_num = H, a.kv_head_num = Hkv, a.size_per_head = cfg.size_per_head;
         a.max_q_len = S, a.max_seq_len = cfg.session_len, a.quant_policy = cfg.quant_policy;
         for (int i = 0; i < 4; ++i) a.kv_scale[i] = w.past_kv_scale[i];
+        a.status_word = m->h->status;
         if (!step(tm_context_attention(&a, s))) break;
         if (!step(linear.forward(pb.h, pb.ctx, T, w.output, LlamaLinear::kGemm, s))) break;
         if (m->comm && m->comm->world > 1) {

@@ -102,6 +102,7 @@ class TmContextAttentionParams(C.Structure):
         ("cache_layer_offset", C.c_size_t), ("cu_seqlens", C.c_void_p), ("context_lengths", C.c_void_p),
         ("batch_size", C.c_int), ("head_num", C.c_int), ("kv_head_num", C.c_int), ("size_per_head", C.c_int),
         ("max_q_len", C.c_int), ("max_seq_len", C.c_int), ("quant_policy", C.c_int), ("kv_scale", C.c_float * 4),
+        ("status_word", C.c_void_p),
     ]
 
 
@@ -212,6 +213,7 @@ SIGNATURES = {
     "tm_add_residual_rmsnorm": (_i, [_vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tm_add_fused_qkv_bias_transpose": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                              C.c_float, _i, _i, _i, _vp]),
+    "tm_context_attention_last_status": (_i, [C.POINTER(C.c_uint)]),
     "tm_context_attention": (_i, [C.POINTER(TmContextAttentionParams), _vp]),
     "tm_extend_kv_cache": (_i, [_vp, _vp, _sz, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _vp, _i, C.POINTER(C.c_float)]),
     "tm_transpose_kv_cache": (_i, [_vp, _vp, _vp, _vp, _sz, _i, _vp, _i, _i, _i, _i, _i, _vp, _i, C.POINTER(C.c_float)]),
