@@ -12,6 +12,14 @@ using namespace tmb;
 
 namespace tmb {
 thread_local int g_pdl = 0;
+thread_local const GemmNormFusion* g_gemm_fusion = nullptr;
+
+bool gemm_can_fuse_norm(const tm_handle* h, int m, int n, int k)
+{
+    if (!h || n < h->gemm_tc_min_n || n > 128 || k % 128 || m % 32) return false;
+    const GemmTcPlan pl = gemm_tc_plan(m, n, k, h->sm_count);
+    return gemm_tc_all_tiles_split(pl, k) && pl.workspace_floats * sizeof(float) <= h->scratch_bytes && pl.counter_ints <= h->counter_ints;
+}
 }
 
 namespace {
@@ -81,6 +89,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     h->pdl           = env_int("TM_B200_PDL", 1);
     h->p2p_allreduce = env_int("TM_B200_P2P_ALLREDUCE", 1);
     h->lm_head_cublas = env_int("TM_B200_LM_HEAD_CUBLAS", 0);
+    h->fold_norm      = env_int("TM_B200_FOLD_NORM", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->mmha_warps  = env_int("TM_B200_MMHA_WARPS", 0);
@@ -147,6 +156,9 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     else if (n == "p2p_allreduce" && (value == 0 || value == 1)) {
         // 0: the tensor-parallel decode step reduces with NCCL even where the peer-memory path is set up
         h->p2p_allreduce = value;
+    }
+    else if (n == "fold_norm" && (value == 0 || value == 1)) {
+        h->fold_norm = value;
     }
     else if (n == "lm_head_cublas" && (value == 0 || value == 1)) {
         h->lm_head_cublas = value;
@@ -255,6 +267,10 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
             p.K          = k;
             p.fused_silu = type == TM_GEMM_FUSED_SILU_FFN;
             p.max_wait_cycles = h->gemm_wait_cycles;
+            if (g_gemm_fusion) {
+                if (per != n || workspace || !gemm_tc_all_tiles_split(pl, k)) return TM_ERR_UNSUPPORTED;  // the driver checked
+                p.norm = *g_gemm_fusion;
+            }
             cudaError_t e = gemm_tc_launch(pl, p, (cudaStream_t)stream, g_pdl != 0 || h->pdl_direct != 0);
             h->launches += 1;
             if (e != cudaSuccess) {
@@ -265,6 +281,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
         return TM_OK;
     }
 
+    if (g_gemm_fusion) return TM_ERR_UNSUPPORTED;  // only the tensor-core kernel folds the norm in
     // One launch covers up to `n_launch` tokens; more tokens than the scratch can hold partial
     // tiles for are processed in several launches over consecutive token ranges.
     const size_t n_out = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;

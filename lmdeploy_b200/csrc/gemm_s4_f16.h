@@ -42,6 +42,21 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem);
 cudaError_t   gemm_small_prepare(int max_smem);
 cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st, bool pdl = false);
 
+// Residual add + RMSNorm folded into two consecutive tensor-core GEMMs of the decode step (decode driver only).
+// Producer side (o_proj, w2): the reducers of the output tiles add the residual, store it, write
+// half((residual + y) * norm_weight) as the output and add up every token's sum of squares in 2^-20 fixed point
+// (integer atomics: the order of the additions cannot change the result).
+// Consumer side (qkv, w13): the rows of the accumulator are scaled by rsqrt(ssq[t] * 2^-20 * inv_n + eps) before the
+// output is rounded, which completes the normalisation of its input.
+struct GemmNormFusion {
+    __half*                   residual    = nullptr;  // [T][N], producer
+    const __half*             norm_weight = nullptr;  // [N], producer
+    unsigned long long*       ssq_out     = nullptr;  // [T], producer
+    const unsigned long long* ssq_in      = nullptr;  // [T], consumer
+    float                     inv_n       = 0.f;      // 1 / (length of the normalised row), consumer
+    float                     eps         = 0.f;
+};
+
 // ---- tensor-core (tcgen05) kernel for more than 16 tokens ---------------------------------
 struct GemmTcParams {
     __half*              C;
@@ -56,6 +71,7 @@ struct GemmTcParams {
     // filled in by gemm_tc_launch from the plan
     int units_per_cta, total_units, slots_per_chunk, n_col_tiles, token_tile, x_stages, a_stages, acc_stride, k_split, parts_per_tile;
     long long max_wait_cycles;  // bound of the wait for the partners of a split tile; 0 = the default
+    GemmNormFusion norm;        // all null: a plain GEMM
 };
 
 struct GemmTcPlan {
@@ -74,6 +90,8 @@ struct GemmTcPlan {
 
 size_t      gemm_tc_smem_bytes(int token_tile);
 GemmTcPlan  gemm_tc_plan(int N, int T, int K, int sm_count);
+// true when every output tile of the plan is reduced by reduce_share (the only place that applies GemmNormFusion)
+bool        gemm_tc_all_tiles_split(const GemmTcPlan& plan, int K);
 cudaError_t gemm_tc_prepare(int max_smem);
 cudaError_t gemm_tc_launch(const GemmTcPlan& plan, GemmTcParams p, cudaStream_t st, bool pdl = false);
 

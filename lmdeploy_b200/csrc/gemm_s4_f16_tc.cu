@@ -485,9 +485,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 if (seen < n_split) atomicOr(p.status, kStatusGemmTmemWait);
                 bars->flag = seen >= n_split;
             }
+            // producer side of a folded norm: per-token sums of squares of this CTA's share, in fixed point, kept in the
+            // (by now idle) activation ring until they go out with one atomic per token
+            unsigned long long* s_ssq = reinterpret_cast<unsigned long long*>(x_ring);
+            if (p.norm.ssq_out && dtid < t_rows) s_ssq[dtid] = 0ull;
             named_bar_sync(1, kDqThreads);
             TC_TRACE(trow, 42, tjs);
-            if (bars->flag) {
+            const bool tile_ok = bars->flag != 0;  // read between the barriers: the next call may rewrite the flag
+            if (tile_ok) {
                 const int j      = blockIdx.x - c_first;
                 const int n_cols = min(kSuperN, p.N - col0);  // N % 32 == 0
                 const int f0     = (n_cols * j / n_split) & ~3;
@@ -512,8 +517,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                             acc.x += part[e].x, acc.y += part[e].y, acc.z += part[e].z, acc.w += part[e].w;
                         }
                     }
+                    if (p.norm.ssq_in) {
+                        // consumer side: the row's 1 / rms completes the normalisation of this GEMM's input
+                        const float ssq = (float)__ldcg(p.norm.ssq_in + t0 + t) * (1.f / 1048576.f);
+                        const float inv = rsqrtf(ssq * p.norm.inv_n + p.norm.eps);
+                        acc.x *= inv, acc.y *= inv, acc.z *= inv, acc.w *= inv;
+                    }
                     const __half2 h0 = __floats2half2_rn(acc.x, acc.y), h1 = __floats2half2_rn(acc.z, acc.w);
-                    if (p.fused_silu) {
+                    if (p.norm.ssq_out) {
+                        // producer side (llama_decoder_kernels.cu:104-160 split in two): residual += y in fp32, stored as
+                        // fp16; the sum of squares is taken before that rounding, the norm weight applied to the stored value
+                        __half2*       rp = reinterpret_cast<__half2*>(p.norm.residual + (size_t)(t0 + t) * p.N + col0 + n);
+                        const __half2* gp = reinterpret_cast<const __half2*>(p.norm.norm_weight + col0 + n);
+                        const float2   r0 = __half22float2(rp[0]), r1 = __half22float2(rp[1]);
+                        const float2   y0 = __half22float2(h0), y1 = __half22float2(h1);
+                        const float2   s0 = make_float2(r0.x + y0.x, r0.y + y0.y), s1 = make_float2(r1.x + y1.x, r1.y + y1.y);
+                        const float    ss = (s0.x * s0.x + s0.y * s0.y) + (s1.x * s1.x + s1.y * s1.y);
+                        const __half2  n0 = __float22half2_rn(s0), n1 = __float22half2_rn(s1);
+                        rp[0] = n0, rp[1] = n1;
+                        const float2 a0 = __half22float2(n0), a1 = __half22float2(n1);
+                        const float2 g0 = __half22float2(gp[0]), g1 = __half22float2(gp[1]);
+                        __half2*     dst = reinterpret_cast<__half2*>(p.C + (size_t)(t0 + t) * p.N + col0 + n);
+                        dst[0]           = __floats2half2_rn(a0.x * g0.x, a0.y * g0.y);
+                        dst[1]           = __floats2half2_rn(a1.x * g1.x, a1.y * g1.y);
+                        atomicAdd(s_ssq + t, (unsigned long long)__float2ll_rn(ss * 1048576.f));
+                    }
+                    else if (p.fused_silu) {
                         // kernels/gemm_s_f16/gemm_s4_f16.cu:31-43 on the fp16-rounded pairs (gate, up)
                         const float2 u0 = __half22float2(h0), u1 = __half22float2(h1);
                         const float  s0 = u0.x / (1.f + __expf(-u0.x)), s1 = u1.x / (1.f + __expf(-u1.x));
@@ -528,6 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_s4_f16_tc_kernel(GemmTcParam
                 }
             }
             named_bar_sync(1, kDqThreads);  // everyone is done reading; the flag may be reused
+            if (p.norm.ssq_out && tile_ok && dtid < t_rows && s_ssq[dtid]) atomicAdd(p.norm.ssq_out + t0 + dtid, s_ssq[dtid]);
             if (dtid == 0) {
                 // the last reader of the tile resets both counts for the next launch; a CTA that gave up
                 // on the wait counts as a reader too, so the counts recover after a time-out
@@ -806,6 +836,13 @@ GemmTcPlan gemm_tc_plan(int N, int T, int K, int sm_count)
     pl.workspace_floats = pl.units_per_cta % G == 0 ? 0 : (size_t)pl.t_chunks * pl.slots_per_chunk * pl.token_tile * kSuperN;
     pl.counter_ints     = (size_t)2 * pl.t_chunks * pl.n_col_tiles;  // arrivals and finished readers per tile
     return pl;
+}
+
+bool gemm_tc_all_tiles_split(const GemmTcPlan& pl, int K)
+{
+    if (pl.t_chunks != 1) return false;
+    if (pl.parts_per_tile) return pl.parts_per_tile >= 2;
+    return pl.units_per_cta < K / kGroup && pl.ctas > 1;  // a run of the flat list is shorter than a tile: every tile has several owners
 }
 
 cudaError_t gemm_tc_prepare(int max_smem)

@@ -27,6 +27,7 @@ struct tm_handle {
     int                gemm_wait_cycles = 0; // 0 = default bound of the split-tile wait of the tcgen05 GEMM (option "gemm_wait_cycles")
     int                pdl_direct      = 0;  // option "pdl_direct": direct GEMM / attention calls launch with programmatic serialization too
     int                p2p_allreduce   = 1;  // TM_B200_P2P_ALLREDUCE / option "p2p_allreduce": peer-memory all-reduce + norm in the decode step
+    int                fold_norm       = 1;  // TM_B200_FOLD_NORM=0 / option "fold_norm": the decode step keeps residual add + RMSNorm as kernels of their own
     int                lm_head_cublas  = 0;  // TM_B200_LM_HEAD_CUBLAS=1 / option "lm_head_cublas": the decode step's lm-head through cuBLAS (comparison only)
     int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
 };
@@ -41,5 +42,10 @@ int lm_head_launch(float* logits, int ld, const __half* x, const __half* w, int 
 // the C ABI on this thread carry the programmatic-dependent-launch attribute.  Off for direct callers,
 // who may put any kernel in front of ours.
 extern thread_local int g_pdl;
+// Set by the decode driver around ONE tm_gemm_s4_f16 call whose launch should carry a GemmNormFusion (gemm_s4_f16.h);
+// the driver has checked with gemm_can_fuse_norm that the call is a single tensor-core launch with every tile split.
+struct GemmNormFusion;
+extern thread_local const GemmNormFusion* g_gemm_fusion;
+bool gemm_can_fuse_norm(const tm_handle* h, int m, int n, int k);
 }  // namespace tmb
 

@@ -261,11 +261,45 @@ int run_step(StepCtx& c)
         return c.ok(tm_add_residual_rmsnorm(m.x, m.hbuf, nullptr, norm_w, cfg.norm_eps, B, m.hidden, s));
     };
 
+    // Residual add + RMSNorm folded into the GEMMs on either side (gemm_s4_f16.h, GemmNormFusion): single GPU, a batch
+    // the tensor-core kernel takes in one launch with every output tile split.  The first norm of the step and the
+    // last one (in front of the lm-head) stay kernels of their own.
+    const LlamaDecoderLayerWeight& w0 = m.layers[0];
+    const bool fold = !tp_on && m.h->fold_norm && gemm_can_fuse_norm(m.h, (int)w0.qkv.output_dims, B, (int)w0.qkv.input_dims)
+                      && gemm_can_fuse_norm(m.h, (int)w0.output.output_dims, B, (int)w0.output.input_dims)
+                      && gemm_can_fuse_norm(m.h, (int)w0.fused_gating_intermediate.output_dims, B, (int)w0.fused_gating_intermediate.input_dims)
+                      && gemm_can_fuse_norm(m.h, (int)w0.ffn_output.output_dims, B, (int)w0.ffn_output.input_dims);
+    if (fold) {
+        if (!c.ok(cudaMemsetAsync(m.ssq, 0, (size_t)2 * cfg.num_layer * cfg.max_batch_size * sizeof(unsigned long long), s) == cudaSuccess ?
+                      TM_OK :
+                      TM_ERR_CUDA)) {
+            return c.rc;
+        }
+    }
+    struct FusionScope {
+        explicit FusionScope(const GemmNormFusion* f) { g_gemm_fusion = f; }
+        ~FusionScope() { g_gemm_fusion = nullptr; }
+    };
+    auto ssq_of = [&](int idx) { return m.ssq + (size_t)idx * cfg.max_batch_size; };
+    // consumer: scale rows by the 1 / rms that the sums of squares `idx` give; producer: fold the add + norm-weight in
+    auto consumer = [&](int idx) {
+        GemmNormFusion f;
+        f.ssq_in = ssq_of(idx), f.inv_n = 1.f / (float)m.hidden, f.eps = cfg.norm_eps;
+        return f;
+    };
+    auto producer = [&](int idx, const void* norm_w) {
+        GemmNormFusion f;
+        f.residual = m.x, f.norm_weight = (const __half*)norm_w, f.ssq_out = ssq_of(idx);
+        return f;
+    };
+
     for (int l = 0; l < cfg.num_layer; ++l) {
         const LlamaDecoderLayerWeight& w = m.layers[l];
         // ---- self attention (LlamaDecoderSelfAttentionLayer.cc:193-304)
         {
             NvtxRange r("qkv_gemm");
+            const GemmNormFusion f = consumer(2 * l - 1);
+            FusionScope          fs(fold && l > 0 ? &f : nullptr);
             if (!c.ok(linear.forward(m.qkv, m.hbuf, B, w.qkv, LlamaLinear::kGemm, s))) return c.rc;
         }
         tm_mmha_params a;
@@ -305,18 +339,27 @@ int run_step(StepCtx& c)
         }
         {
             NvtxRange r("o_gemm");
+            const GemmNormFusion f = producer(2 * l, w.ffn_norm_weights);
+            FusionScope          fs(fold ? &f : nullptr);
             if (!c.ok(linear.forward(part_o, m.ctx, B, w.output, LlamaLinear::kGemm, s))) return c.rc;
         }
         // ---- [sum over ranks] ; x += attn ; h = RMSNorm(x) * ffn_norm   (LlamaDecoder.cc:212-220)
-        if (!reduce_add_norm(0, w.ffn_norm_weights)) return c.rc;
+        if (!fold && !reduce_add_norm(0, w.ffn_norm_weights)) return c.rc;
         // ---- feed forward (LlamaFfnLayer.cc:66-116): fused w1|w3 GEMM with the SiLU epilogue, then w2
+        const bool  last      = l + 1 == cfg.num_layer;
+        const void* next_norm = !last ? m.layers[l + 1].self_attn_norm_weights : m.output_norm;
         {
             NvtxRange r("ffn");
-            if (!c.ok(linear.forward(m.ffn, m.hbuf, B, w.fused_gating_intermediate, LlamaLinear::kFusedSiluFfn, s))) return c.rc;
+            {
+                const GemmNormFusion f = consumer(2 * l);
+                FusionScope          fs(fold ? &f : nullptr);
+                if (!c.ok(linear.forward(m.ffn, m.hbuf, B, w.fused_gating_intermediate, LlamaLinear::kFusedSiluFfn, s))) return c.rc;
+            }
+            const GemmNormFusion f = producer(2 * l + 1, next_norm);
+            FusionScope          fs(fold && !last ? &f : nullptr);
             if (!c.ok(linear.forward(part_f, m.ffn, B, w.ffn_output, LlamaLinear::kGemm, s))) return c.rc;
         }
-        const void* next_norm = l + 1 < cfg.num_layer ? m.layers[l + 1].self_attn_norm_weights : m.output_norm;
-        if (!reduce_add_norm(1, next_norm)) return c.rc;
+        if ((!fold || last) && !reduce_add_norm(1, next_norm)) return c.rc;
     }
     if (st.hidden_out) {
         c.ok(cudaMemcpyAsync(st.hidden_out, m.hbuf, (size_t)B * m.hidden * 2, cudaMemcpyDeviceToDevice, s) == cudaSuccess ?
@@ -416,6 +459,7 @@ extern "C" int tm_llama_create(tm_llama** out, tm_handle* h, tm_comm* comm, cons
     alloc((void**)&m->order, (size_t)B * sizeof(int));
     alloc((void**)&m->seq_desc, (size_t)B * sizeof(MmhaSeqDesc));
     alloc((void**)&m->rope_table, (size_t)B * 64 * sizeof(float2));
+    alloc((void**)&m->ssq, (size_t)2 * c.num_layer * B * sizeof(unsigned long long));
     alloc(&m->cublas_ws, 32u << 20);
     if (e == cudaSuccess) e = cudaMemset(m->picked, 0, B * 4);
     bool ok = e == cudaSuccess;
@@ -437,7 +481,7 @@ extern "C" int tm_llama_destroy(tm_llama* m)
     if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
     if (m->cublas) cublasDestroy(m->cublas);
     for (void* p : {(void*)m->x, (void*)m->hbuf, (void*)m->qkv, (void*)m->ctx, (void*)m->ffn, (void*)m->logits_local,
-                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, (void*)m->seq_desc, (void*)m->rope_table, m->cublas_ws}) {
+                    (void*)m->logits, (void*)m->ids_in, (void*)m->picked, (void*)m->inactive, (void*)m->order, (void*)m->seq_desc, (void*)m->rope_table, (void*)m->ssq, m->cublas_ws}) {
         if (p) cudaFree(p);
     }
     for (void* p : m->owned) cudaFree(p);

@@ -66,6 +66,7 @@ struct tm_llama {
     int*    order = nullptr;  // sequences by cached length, longest first (attention launch order)
     tmb::MmhaSeqDesc* seq_desc   = nullptr;  // the same order, with lengths, cache pointers and flags gathered per sequence
     float2*           rope_table = nullptr;  // [batch][64] {cos, sin} of every sequence's position in this step
+    unsigned long long* ssq      = nullptr;  // [2 * num_layer][max batch]: per-token sums of squares of the folded norms (fixed point)
     unsigned char* inactive = nullptr;
 
     // activations of tm_llama_prefill, sized by the largest call so far

@@ -31,9 +31,16 @@ def test_split_tile_wait_that_runs_out_is_reported_and_the_next_call_is_clean():
     args = (h.ptr, out.data_ptr(), A.data_ptr(), xd.data_ptr(), Q.data_ptr(), n, t, k, 128, 0, None, 0, st)
     try:
         h.set_option("gemm_wait_cycles", 1)
-        assert l.lib.tm_gemm_s4_f16(*args) == l.TM_OK   # the launch itself succeeds
         w = C.c_uint(0)
-        assert l.lib.tm_check_device_status(h.ptr, st, C.byref(w)) == l.TM_ERR_DEVICE_TIMEOUT
+        for attempt in range(5):
+            # whether some CTA polls before its last partner has arrived is a matter of timing: practically always,
+            # but a launch in which every CTA happens to find its tile complete at the first look is legal
+            assert l.lib.tm_gemm_s4_f16(*args) == l.TM_OK   # the launch itself succeeds
+            rc = l.lib.tm_check_device_status(h.ptr, st, C.byref(w))
+            if rc == l.TM_ERR_DEVICE_TIMEOUT:
+                break
+            assert rc == l.TM_OK
+        assert rc == l.TM_ERR_DEVICE_TIMEOUT, "no wait ran out in five launches"
         assert w.value & (1 << 3), hex(w.value)
         assert l.lib.tm_check_device_status(h.ptr, st, C.byref(w)) == l.TM_OK   # read and cleared
         h.set_option("gemm_wait_cycles", 0)

@@ -26,14 +26,14 @@ def _linear(n, k, seed):
     return a, q, w_nk.t().contiguous().numpy()
 
 
-def build(int8):
+def build(int8, max_batch=4):
     from lmdeploy_b200 import llama, turbomind as tm
     hid = CFG["head_num"] * 128
     rng = np.random.default_rng(0)
     kvq = oa.KvQuant(8.0 / 127, 0.0, 8.0 / 127, 0.0) if int8 else None
     cfg = llama.LlamaConfig(CFG["head_num"], CFG["kv_head_num"], CFG["inter_size"], CFG["num_layer"], CFG["vocab_size"],
                             quant_policy=4 if int8 else 0)
-    model = llama.LlamaModel(cfg, max_batch_size=4, session_len=CFG["session_len"], device=0)
+    model = llama.LlamaModel(cfg, max_batch_size=max_batch, session_len=CFG["session_len"], device=0)
     layers = []
     for l in range(CFG["num_layer"]):
         an = (1 + 0.1 * rng.standard_normal(hid)).astype(np.float16)
@@ -213,3 +213,42 @@ def test_prefill_then_decode_matches_the_token_by_token_path(int8):
             assert d.max() <= 3e-2, d.max()
         assert not np.any(k_b[b, :, :, len(p):]), "rows past the prompt must stay untouched"
     model.close()
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_folded_norm_matches_separate_norm_kernels(use_graph):
+    """From 17 sequences on (tensor-core GEMMs, one GPU) the decode step folds residual add + RMSNorm into the GEMMs
+    on either side.  Same logits as the step with the norm kernels of their own, within the rounding the fold moves
+    (the norm weight is applied before the GEMM, 1 / rms after it), fewer launches, and bit-identical from run to run
+    (the sums of squares are integer sums)."""
+    model, _, _ = build(True, max_batch=32)
+    B, steps = 24, 5
+    rng = np.random.default_rng(8)
+    forced = np.full((steps, B), -1, np.int32)
+    forced[0] = rng.integers(0, CFG["vocab_size"], B)
+    forced[2, ::3] = rng.integers(0, CFG["vocab_size"], len(forced[2, ::3]))
+    runs = {}
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for name, fold in (("fold", 1), ("plain", 0), ("fold again", 1)):
+            model.handle.set_option("fold_norm", fold)
+            st = model.new_state(B, steps, np.zeros(B, np.int32), forced, keep_logits=True)
+            logits, launches = [], 0
+            for _ in range(steps):
+                model.decode(st, 1, use_graph=use_graph, stream=stream.cuda_stream)
+                stream.synchronize()
+                logits.append(st.logits.cpu().numpy().copy())
+                launches = model.last_launches()
+            model.check_status(stream.cuda_stream)
+            runs[name] = (np.stack(logits), st.output_ids.cpu().numpy().copy(), launches, st.k_cache.cpu().numpy().copy())
+    model.handle.set_option("fold_norm", 1)
+    model.close()
+    a, b = runs["fold"], runs["plain"]
+    assert a[2] < b[2], (a[2], b[2])                            # the fold really happened: fewer launches per step
+    assert b[2] - a[2] == 2 * CFG["num_layer"] - 1
+    err = np.abs(a[0] - b[0])
+    assert err.max() <= 3e-2 and err.mean() / np.abs(b[0]).mean() <= 5e-3, (err.max(), err.mean() / np.abs(b[0]).mean())
+    assert (a[1] == b[1]).mean() > 0.95
+    d = np.abs(a[3].astype(np.int32) - b[3].astype(np.int32))
+    assert d.max() <= 2 and (d != 0).mean() < 0.05
+    assert np.array_equal(a[0], runs["fold again"][0]) and np.array_equal(a[1], runs["fold again"][1])
