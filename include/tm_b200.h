@@ -67,6 +67,8 @@ TM_API unsigned long long tm_launch_count(const tm_handle* h);
  * "pdl_direct" (1: GEMM / attention calls made directly through the handle launch with programmatic stream
  * serialization, as the decode driver's do; only where no kernel ahead in the stream writes weights or cached rows),
  * "gemm_wait_cycles" (bound of the tcgen05 GEMM's wait for the partners of a split tile, 0 = default; tests),
+ * "fold_norm" (0: the single-GPU decode step keeps residual add + RMSNorm as kernels of their own instead of folding
+ * them into the tensor-core GEMMs on either side),
  * "lm_head_cublas" (1: the decode driver computes the lm-head with cuBLAS, as the reference does, instead of this
  * library's kernel; for comparison),
  * "mmha_chunk" (cached tokens per KV split, 0 = automatic), "mmha_warps" (warps per attention CTA: 1, 2,
