@@ -591,6 +591,8 @@ TM_API int tm_batch_submit(tm_batch* b, const tm_request* r);
 TM_API int tm_batch_step(tm_batch* b, void* stream, int use_graph);
 /* tokens generated so far for the session's latest request (first min(capacity, *count) of them) and its state */
 TM_API int tm_batch_output(const tm_batch* b, uint64_t id, int* tokens, size_t capacity, size_t* count, int* state);
+/* forget the output of a finished / failed request (they are kept until then, or until the id is submitted again) */
+TM_API int tm_batch_forget(tm_batch* b, uint64_t id);
 TM_API int tm_batch_counts(const tm_batch* b, int* active, int* pending, unsigned long long* steps, unsigned long long* prefill_tokens);
 
 #ifdef __cplusplus

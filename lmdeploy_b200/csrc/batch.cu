@@ -178,6 +178,17 @@ extern "C" int tm_batch_output(const tm_batch* b, uint64_t id, int* tokens, size
     return TM_OK;
 }
 
+// Drops what the scheduler remembers of a finished (or failed) request; its session's cache entry is not touched.
+extern "C" int tm_batch_forget(tm_batch* b, uint64_t id)
+{
+    if (!b) return TM_ERR_INVALID_ARG;
+    auto it = b->results.find(id);
+    if (it == b->results.end()) return TM_ERR_INVALID_ARG;
+    if (it->second.state != TM_REQUEST_FINISHED && it->second.state != TM_REQUEST_FAILED) return TM_ERR_INVALID_ARG;
+    b->results.erase(it);
+    return TM_OK;
+}
+
 extern "C" int tm_batch_counts(const tm_batch* b, int* active, int* pending, unsigned long long* steps, unsigned long long* prefill_tokens)
 {
     if (!b) return TM_ERR_INVALID_ARG;
@@ -339,7 +350,16 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
         for (size_t i = 0; i <= fresh.size(); ++i) {
             const int n = i < fresh.size() ? std::max(0, (int)b->slots[fresh[i]].tokens.size() - 1 - fresh_cached[i]) : 0;
             if (i == fresh.size() || (!group.empty() && sum + n > b->max_context_tokens)) {
-                if ((rc = prefill_group(b, group, group_cached, s)) != TM_OK) return rc;
+                if ((rc = prefill_group(b, group, group_cached, s)) != TM_OK) {
+                    // the newcomers have no usable context: give their slots and slabs back before reporting
+                    cudaStreamSynchronize(s);
+                    std::sort(fresh.begin(), fresh.end());
+                    for (int k = (int)fresh.size() - 1; k >= 0; --k) {
+                        finish_slot(b, fresh[k], TM_REQUEST_FAILED);
+                        compact(b, fresh[k], s);
+                    }
+                    return rc;
+                }
                 group.clear();
                 group_cached.clear();
                 sum = 0;

@@ -18,6 +18,7 @@
 #include "tm_b200.h"
 
 #include <cstdlib>
+#include <mutex>
 
 namespace tmb {
 namespace {
@@ -368,6 +369,8 @@ extern "C" int tm_context_attention(const tm_context_attention_params* a, void* 
     if (!p.status) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TM_ERR_CUDA;
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lock(mu);
         if (!own_status[dev]) {
             if (cudaMalloc((void**)&own_status[dev], sizeof(unsigned)) != cudaSuccess) return TM_ERR_CUDA;
             cudaMemset(own_status[dev], 0, sizeof(unsigned));

@@ -310,15 +310,19 @@ __global__ void __launch_bounds__(kThreads, 2) context_attention_tc_kernel(CtxPa
             tmem_ld32(lane_base + kColS, s0);
             tmem_ld32(lane_base + kColS + 32, s1);
             const int key0 = t * kBN;
-            float     mx   = -INFINITY;
+            // raw scores stay as they are; the softmax scale goes into the exponent's multiply-add.  Only tiles that
+            // touch the causal diagonal or the end of the keys mask anything (the same for every row of the CTA).
+            float mx = -INFINITY;
+            if (key0 + kBN - 1 > hist + q0 || key0 + kBN > kv_end || !row_live) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float a = __uint_as_float(s0[i]) * p.scale_log2, b = __uint_as_float(s1[i]) * p.scale_log2;
-                if (key0 + i > limit) a = -INFINITY;
-                if (key0 + 32 + i > limit) b = -INFINITY;
-                s0[i] = __float_as_uint(a), s1[i] = __float_as_uint(b);
-                mx = fmaxf(mx, fmaxf(a, b));
+                for (int i = 0; i < 32; ++i) {
+                    if (key0 + i > limit) s0[i] = 0xff800000u;       // -inf
+                    if (key0 + 32 + i > limit) s1[i] = 0xff800000u;
+                }
             }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+            mx *= p.scale_log2;  // the scale is positive
             // the running maximum follows only when it is left behind by more than 2^8: p <= 256 fits fp16, the sums are
             // fp32, and the accumulator needs rescaling a few times per row instead of once per tile
             float alpha = 1.f;
@@ -326,13 +330,13 @@ __global__ void __launch_bounds__(kThreads, 2) context_attention_tc_kernel(CtxPa
                 alpha  = ex2(m_used - mx);  // 0 on the first tile
                 m_used = mx;
             }
-            const float mm  = m_used == -INFINITY ? 0.f : m_used;
+            const float nm  = m_used == -INFINITY ? 0.f : -m_used;
             float       sum = 0.f;
             uint32_t    pr[32];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float a = ex2(__uint_as_float(s0[2 * i]) - mm), b = ex2(__uint_as_float(s0[2 * i + 1]) - mm);
-                const float c = ex2(__uint_as_float(s1[2 * i]) - mm), d = ex2(__uint_as_float(s1[2 * i + 1]) - mm);
+                const float a = ex2(fmaf(__uint_as_float(s0[2 * i]), p.scale_log2, nm)), b = ex2(fmaf(__uint_as_float(s0[2 * i + 1]), p.scale_log2, nm));
+                const float c = ex2(fmaf(__uint_as_float(s1[2 * i]), p.scale_log2, nm)), d = ex2(fmaf(__uint_as_float(s1[2 * i + 1]), p.scale_log2, nm));
                 sum += (a + b) + (c + d);
                 pr[i]      = pack2(a, b);
                 pr[16 + i] = pack2(c, d);

@@ -174,6 +174,7 @@ SIGNATURES = {
     "tm_batch_submit": (_i, [_vp, C.POINTER(TmRequest)]),
     "tm_batch_step": (_i, [_vp, _vp, _i]),
     "tm_batch_output": (_i, [_vp, C.c_uint64, C.POINTER(C.c_int), _sz, C.POINTER(_sz), C.POINTER(_i)]),
+    "tm_batch_forget": (_i, [_vp, C.c_uint64]),
     "tm_batch_counts": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]),
     "tm_sampling_rng_state_bytes": (_sz, []),
     "tm_sampling_rng_init": (_i, [_vp, _i, _vp, C.c_ulonglong, _vp]),

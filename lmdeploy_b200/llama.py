@@ -333,6 +333,9 @@ class Batch:
         _l.check(_l.lib.tm_batch_counts(self._b, C.byref(a), C.byref(p), C.byref(s), C.byref(t)), "tm_batch_counts")
         return dict(active=a.value, pending=p.value, steps=s.value, prefill_tokens=t.value)
 
+    def forget(self, session_id: int) -> int:
+        return _l.lib.tm_batch_forget(self._b, session_id)
+
     def has_session(self, session_id: int) -> bool:
         return bool(_l.lib.tm_cache_contains(self._cache, session_id))
 

@@ -85,6 +85,7 @@ def test_session_continues_from_its_cached_tokens():
     b.run(max_rounds=50)
     g2, state = b.output(1)
     assert state == llama.Batch.FINISHED and len(g2) == 4 and not b.has_session(1)
+    assert b.forget(1) == 0 and b.forget(1) != 0          # the record goes once
     # only what had no keys / values was context-decoded: the last token of round one and the new prompt but its last token
     assert b.counts()["prefill_tokens"] - before == 1 + len(p2) - 1
     b.close()
