@@ -364,6 +364,8 @@ TM_API int tm_allreduce_sum_f16(tm_comm* c, void* buf, size_t count, void* strea
  *                        kernel finishes on what it has, it never hangs. */
 TM_API int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64);
 /* "p2p_wait_cycles": bound, in SM clock cycles, of the wait for the peers' slots (0 = default, about a quarter of a second);
+ * "p2p_bulk": 1 a peer's rows come to shared memory with one bulk copy per rank and row (no multicast), 0 with 16-byte
+ * loads of the threads, -1 (default) bulk copies beyond two ranks (environment: TM_B200_P2P_BULK);
  * "p2p_mode": 1 every rank reads every rank's whole slot, 2 token rows dealt to owner ranks, which finish them and
  * hand them on, 0 (default) picks 1 up to four ranks and 2 beyond (environment: TM_B200_P2P_MODE, read by
  * tm_comm_p2p_export). */

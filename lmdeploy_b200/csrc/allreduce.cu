@@ -48,7 +48,20 @@ struct ArParams {
     unsigned*            row_flags[kMaxP2pRanks];  // per-row counters of every rank; the owner of a row writes them all
     unsigned*            my_row_flags;
     int                  rows_per_rank;
+    int                  bulk;                     // 1: the peers' rows are staged in shared memory by bulk copies
 };
+
+// Shared memory of the bulk path: an mbarrier, then one row per other rank.
+constexpr int kArStageOff = 128;
+
+// One bulk copy (global -> shared, completion counted on an mbarrier): the copy engine keeps far more of a peer's memory
+// in flight over NVLink than the 16-byte loads of a CTA's threads can.  No multicast; source and destination 16-byte aligned.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 __device__ __forceinline__ uint4 ld_peer(const unsigned char* p)
 {
@@ -59,9 +72,15 @@ __device__ __forceinline__ uint4 ld_peer(const unsigned char* p)
 
 __global__ void __launch_bounds__(kArThreadsMax) allreduce_add_rmsnorm_kernel(ArParams p)
 {
+    extern __shared__ __align__(128) unsigned char ar_smem[];
     __shared__ float    red[kArThreadsMax / 32];
     __shared__ unsigned s_epoch;
     const int tid = threadIdx.x;
+    uint64_t* stage_bar = reinterpret_cast<uint64_t*>(ar_smem);
+    if (p.bulk && tid == 0) {
+        mbar_init(stage_bar, 1);
+        fence_mbar_init();
+    }
     pdl_wait();  // the slot is written by the GEMM before this kernel
     pdl_launch_dependents();
     if (tid == 0) s_epoch = *(volatile unsigned*)&p.state[0] + 1u;
@@ -90,12 +109,33 @@ __global__ void __launch_bounds__(kArThreadsMax) allreduce_add_rmsnorm_kernel(Ar
     const size_t row  = (size_t)blockIdx.x * p.n;
     const int    nvec = p.n / 8;
     float        ss   = 0.f;
+    if (p.bulk) {
+        // the other ranks' pieces of this row come to shared memory with one bulk copy each
+        const uint32_t row_bytes = (uint32_t)p.n * 2;
+        if (tid == 0) {
+            asm volatile("fence.proxy.async;" ::: "memory");  // the counters were read through the generic proxy
+            mbar_arrive_expect_tx(stage_bar, row_bytes * (uint32_t)(p.world - 1));
+            for (int j = 0; j < p.world; ++j) {
+                if (j == p.rank) continue;
+                const int idx = j < p.rank ? j : j - 1;
+                bulk_g2s(smem_u32(ar_smem + kArStageOff) + (uint32_t)idx * row_bytes, p.slot[j] + row * 2, row_bytes, stage_bar);
+            }
+        }
+        if (!mbar_wait(stage_bar, 0, p.max_wait_cycles)) atomicOr(p.status, kStatusCommWait);
+    }
     // sum of one 16-byte piece of the row over the ranks (their loads in flight together) + residual -> fp16 piece
     auto reduce_piece = [&](int v) {
         uint4 part[kMaxP2pRanks];
 #pragma unroll
         for (int j = 0; j < kMaxP2pRanks; ++j) {
-            if (j < p.world) part[j] = ld_peer(p.slot[j] + (row + (size_t)v * 8) * 2);
+            if (j < p.world) {
+                if (p.bulk && j != p.rank) {
+                    part[j] = *reinterpret_cast<const uint4*>(ar_smem + kArStageOff + (size_t)(j < p.rank ? j : j - 1) * p.n * 2 + (size_t)v * 16);
+                }
+                else {
+                    part[j] = ld_peer(p.slot[j] + (row + (size_t)v * 8) * 2);
+                }
+            }
         }
         uint4 r = reinterpret_cast<const uint4*>(p.residual + row)[v];
         float sum[8];
@@ -176,9 +216,15 @@ __global__ void __launch_bounds__(kArThreadsMax) allreduce_add_rmsnorm_kernel(Ar
 // Row-owner variant (more than two ranks).  One CTA per token row on every rank.  Row t belongs to rank t / rows_per_rank.
 __global__ void __launch_bounds__(kArThreadsMax) allreduce_rows_kernel(ArParams p)
 {
+    extern __shared__ __align__(128) unsigned char ar_smem[];
     __shared__ float    red[kArThreadsMax / 32];
     __shared__ unsigned s_epoch;
     const int tid = threadIdx.x;
+    uint64_t* stage_bar = reinterpret_cast<uint64_t*>(ar_smem);
+    if (p.bulk && tid == 0) {
+        mbar_init(stage_bar, 1);
+        fence_mbar_init();
+    }
     pdl_wait();  // the slot is written by the GEMM before this kernel
     pdl_launch_dependents();
     if (tid == 0) s_epoch = *(volatile unsigned*)&p.state[0] + 1u;
@@ -210,11 +256,31 @@ __global__ void __launch_bounds__(kArThreadsMax) allreduce_rows_kernel(ArParams 
         if (tid < p.world && tid != p.rank) bounded_wait(p.my_flags + tid);
         __syncthreads();
         float ss = 0.f;
+        if (p.bulk) {
+            const uint32_t row_bytes = (uint32_t)p.n * 2;
+            if (tid == 0) {
+                asm volatile("fence.proxy.async;" ::: "memory");
+                mbar_arrive_expect_tx(stage_bar, row_bytes * (uint32_t)(p.world - 1));
+                for (int j = 0; j < p.world; ++j) {
+                    if (j == p.rank) continue;
+                    const int idx = j < p.rank ? j : j - 1;
+                    bulk_g2s(smem_u32(ar_smem + kArStageOff) + (uint32_t)idx * row_bytes, p.slot[j] + row * 2, row_bytes, stage_bar);
+                }
+            }
+            if (!mbar_wait(stage_bar, 0, p.max_wait_cycles)) atomicOr(p.status, kStatusCommWait);
+        }
         auto reduce_piece = [&](int v) {
             uint4 part[kMaxP2pRanks];
 #pragma unroll
             for (int j = 0; j < kMaxP2pRanks; ++j) {
-                if (j < p.world) part[j] = ld_peer(p.slot[j] + (row + (size_t)v * 8) * 2);
+                if (j < p.world) {
+                    if (p.bulk && j != p.rank) {
+                        part[j] = *reinterpret_cast<const uint4*>(ar_smem + kArStageOff + (size_t)(j < p.rank ? j : j - 1) * p.n * 2 + (size_t)v * 16);
+                    }
+                    else {
+                        part[j] = ld_peer(p.slot[j] + (row + (size_t)v * 8) * 2);
+                    }
+                }
             }
             uint4 r = reinterpret_cast<const uint4*>(p.residual + row)[v];
             float sum[8];
@@ -296,7 +362,21 @@ __global__ void __launch_bounds__(kArThreadsMax) allreduce_rows_kernel(ArParams 
         if (tid == 0) bounded_wait(p.my_row_flags + t);
         __syncthreads();
         const unsigned char* src = p.h_slot[owner] + row * 2;
-        for (int v = tid; v < nvec; v += blockDim.x) reinterpret_cast<uint4*>(p.out + row)[v] = ld_peer(src + (size_t)v * 16);
+        if (p.bulk) {
+            const uint32_t row_bytes = (uint32_t)p.n * 2;
+            if (tid == 0) {
+                asm volatile("fence.proxy.async;" ::: "memory");
+                mbar_arrive_expect_tx(stage_bar, row_bytes);
+                bulk_g2s(smem_u32(ar_smem + kArStageOff), src, row_bytes, stage_bar);
+            }
+            if (!mbar_wait(stage_bar, 0, p.max_wait_cycles)) atomicOr(p.status, kStatusCommWait);
+            for (int v = tid; v < nvec; v += blockDim.x) {
+                reinterpret_cast<uint4*>(p.out + row)[v] = *reinterpret_cast<const uint4*>(ar_smem + kArStageOff + (size_t)v * 16);
+            }
+        }
+        else {
+            for (int v = tid; v < nvec; v += blockDim.x) reinterpret_cast<uint4*>(p.out + row)[v] = ld_peer(src + (size_t)v * 16);
+        }
     }
     __syncthreads();
     if (tid == 0) {
@@ -350,8 +430,17 @@ cudaError_t allreduce_add_rmsnorm_launch(tm_comm* c, int slot, __half* residual,
     // rows dealt to owners read less over the links but hand every row over once more: measured slower at 4 ranks
     // (14.7 against 13.6 ms per 70B decode step) and faster at 8 (13.0 against 14.0 ms)
     const bool rows = (c->p2p_mode == 2 || (c->p2p_mode == 0 && c->world > 4)) && m <= kP2pMaxRows;
-    if (rows) return launch_kernel(allreduce_rows_kernel, dim3(m), dim3(threads), 0, st, pdl, p);
-    return launch_kernel(allreduce_add_rmsnorm_kernel, dim3(m), dim3(threads), 0, st, pdl, p);
+    // the peers' rows through the copy engine when they fit shared memory (one row of n halves per other rank)
+    const size_t stage = kArStageOff + (size_t)(c->world - 1) * n * 2;
+    // measured on 70B decode steps: no gain at two ranks (17.9 vs 18.0 ms), 13.1 -> 12.7 ms at eight
+    const bool want    = c->p2p_bulk < 0 ? c->world > 2 : c->p2p_bulk != 0;
+    p.bulk             = want && stage <= 200u * 1024u ? 1 : 0;
+    const size_t smem  = p.bulk ? stage : 0;
+    auto kernel        = rows ? allreduce_rows_kernel : allreduce_add_rmsnorm_kernel;
+    if (smem > 48u * 1024u && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_kernel(kernel, dim3(m), dim3(threads), smem, st, pdl, p);
 }
 
 }  // namespace tmb
@@ -378,6 +467,7 @@ extern "C" int tm_comm_p2p_export(tm_comm* c, size_t slot_bytes, void* handle64)
     if (e != cudaSuccess) return TM_ERR_CUDA;
     c->p2p_slot_bytes = slot_bytes;
     if (const char* e = std::getenv("TM_B200_P2P_MODE")) c->p2p_mode = std::max(0, std::min(2, std::atoi(e)));
+    if (const char* e = std::getenv("TM_B200_P2P_BULK")) c->p2p_bulk = std::atoi(e) != 0;
     std::memcpy(handle64, &h, 64);
     return TM_OK;
 }
@@ -403,6 +493,10 @@ extern "C" int tm_comm_p2p_import(tm_comm* c, const void* handles)
 extern "C" int tm_comm_set_option(tm_comm* c, const char* name, long long value)
 {
     if (!c || !name) return TM_ERR_INVALID_ARG;
+    if (std::strcmp(name, "p2p_bulk") == 0 && value >= -1 && value <= 1) {
+        c->p2p_bulk = (int)value;  // 1: peers' rows staged in shared memory by bulk copies; 0: 16-byte loads; -1: by world size
+        return TM_OK;
+    }
     if (std::strcmp(name, "p2p_mode") == 0 && value >= 0 && value <= 2) {
         c->p2p_mode = (int)value;  // 0 automatic, 1 every rank reads every slot, 2 rows dealt to owners
         return TM_OK;

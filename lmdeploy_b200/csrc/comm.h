@@ -26,6 +26,7 @@ struct tm_comm {
     int       p2p_ready       = 0;
     long long p2p_wait_cycles = 0;  // 0 = the default bound of the wait for the peers
     int       p2p_mode        = 0;  // 0 automatic; 1 every rank reads every slot; 2 rows dealt to owners
+    int       p2p_bulk        = -1; // peers' rows fetched by bulk copies into shared memory: 1 yes, 0 16-byte loads, -1 by world size (beyond two ranks)
 };
 
 namespace tmb {

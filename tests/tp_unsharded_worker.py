@@ -115,10 +115,13 @@ def main():
         status = torch.zeros(64, dtype=torch.int32, device="cuda")
         # both hand-over schemes: 1 = every rank reads every slot, 2 = token rows dealt to owner ranks (the default
         # beyond two ranks), where a rank updates the residual of its own rows only
-        cases = [(mode, shape) for mode in (1, 2) for shape in [(5, 1024), (64, 4096), (128, 8192), (3, 16384), (1, 256), (130, 4096)]]
-        for it, (mode, (m_rows, n)) in enumerate(cases):
+        # ... and both ways of fetching a peer's rows: bulk copies into shared memory (the default) or 16-byte loads
+        cases = [(mode, 1, shape) for mode in (1, 2) for shape in [(5, 1024), (64, 4096), (128, 8192), (3, 16384), (1, 256), (130, 4096)]]
+        cases += [(mode, 0, shape) for mode in (1, 2) for shape in [(64, 4096), (3, 16384)]]
+        for it, (mode, bulk, (m_rows, n)) in enumerate(cases):
             slot = it % 2
             assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_mode", mode) == l.TM_OK
+            assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_bulk", bulk) == l.TM_OK
             g = torch.Generator(device="cuda").manual_seed(100 + 7 * it + rank)
             part = torch.randn(m_rows, n, device="cuda", generator=g).half()
             g0 = torch.Generator(device="cuda").manual_seed(55 + it)
@@ -150,8 +153,9 @@ def main():
             good = torch.equal(r_in, want_r) and (out.float() - want_o.float()).abs().max().item() <= 2e-3 * max(1.0, want_o.float().abs().max().item())
             good = good and int(status[0].item()) == 0
             ok = ok and good
-            report.append(f"all-reduce + add + norm [{m_rows}, {n}] slot {slot} scheme {mode}: residual bit-exact {torch.equal(r_in, want_r)}, "
+            report.append(f"all-reduce + add + norm [{m_rows}, {n}] slot {slot} scheme {mode} bulk {bulk}: residual bit-exact {torch.equal(r_in, want_r)}, "
                           f"out max_abs {(out.float() - want_o.float()).abs().max().item():.2e} {'ok' if good else 'FAIL'}")
+        assert l.lib.tm_comm_set_option(comm.ptr, b"p2p_bulk", -1) == l.TM_OK
         # (d) the decode step with NCCL instead of the peer-memory path gives the same logits within tolerance
         h.set_option("p2p_allreduce", 0)
         mcfg = read_cfg(b_1, l, llama)
