@@ -408,7 +408,8 @@ int tm_mmha_decode_impl(tm_handle* h, const tm_mmha_params* a, void* stream, int
     p.order           = order;
     p.desc            = desc;
     // the table holds plain rotary coefficients of the cached length: usable when that is the position asked for
-    p.rope_table      = (pos_from_length && !a->use_dynamic_ntk && a->rotary_embedding_dim == 128) ? rope_table : nullptr;
+    // (and it is laid out in the launch order of `desc`)
+    p.rope_table      = (desc && pos_from_length && !a->use_dynamic_ntk && a->rotary_embedding_dim == 128) ? rope_table : nullptr;
     p.B               = a->batch_size;
     p.H               = a->num_heads;
     p.Hkv             = a->num_kv_heads;

@@ -55,11 +55,25 @@ __global__ void prepare_step_kernel(const int* step, const int* start_step, cons
 {
     const int b    = blockIdx.x;
     const int mine = lengths[b];
+    // attention launch order: longest cached sequence first (rank by length, ties by index)
+    __shared__ int s_rank;
+    if (threadIdx.x == 0) {
+        int rank = 0;
+        for (int j = 0; j < B; ++j) {
+            const int l = lengths[j];
+            rank += (l > mine || (l == mine && j < b)) ? 1 : 0;
+        }
+        s_rank = rank;
+    }
+    __syncthreads();
+    const int rank = s_rank;
+    // the rotation coefficients sit at the sequence's place in the launch order, like its record: the attention CTA
+    // asks for both at once, without first learning which sequence it has
     if (threadIdx.x < 64 && 2 * (int)threadIdx.x < rot_dim) {
         const float inv_freq = (float)mine / powf(rope_base, (float)(2 * threadIdx.x) / (float)rot_dim);
         float       sn, cs;
         sincosf(inv_freq, &sn, &cs);
-        rope_table[(size_t)b * 64 + threadIdx.x] = make_float2(cs, sn);
+        rope_table[(size_t)rank * 64 + threadIdx.x] = make_float2(cs, sn);
     }
     if (threadIdx.x != 0) return;
     const int  s   = *step;
@@ -71,12 +85,6 @@ __global__ void prepare_step_kernel(const int* step, const int* start_step, cons
         if (f >= 0) id = f;
     }
     ids_in[b] = min(max(id, 0), vocab - 1);
-    // attention launch order: longest cached sequence first (rank by length, ties by index)
-    int rank = 0;
-    for (int j = 0; j < B; ++j) {
-        const int l = lengths[j];
-        rank += (l > mine || (l == mine && j < b)) ? 1 : 0;
-    }
     order[rank] = b;
     MmhaSeqDesc d;
     d.k_cache = k_ptrs[b], d.v_cache = v_ptrs[b], d.length = mine, d.seq = b, d.finished = off ? 1 : 0, d.reserved = 0;

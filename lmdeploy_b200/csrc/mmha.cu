@@ -166,6 +166,9 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
     // without waiting would let the kernel after this one start while the one before it still runs.
     int                  bi, tlength, fin = 0;
     const unsigned char *k_base, *v_base;
+    // rotation coefficients of this CTA's sequence (table in launch order): requested together with the record
+    float2 rope_pre = make_float2(1.f, 0.f);
+    if (p.rope_table != nullptr && 2 * (tid % 64) < p.rot_dim) rope_pre = __ldg(p.rope_table + (size_t)blockIdx.z * 64 + tid % 64);
     if (p.desc != nullptr) {
         const uint4 d0 = __ldg(reinterpret_cast<const uint4*>(p.desc + blockIdx.z));
         const uint4 d1 = __ldg(reinterpret_cast<const uint4*>(p.desc + blockIdx.z) + 1);
@@ -286,7 +289,8 @@ __global__ void __launch_bounds__(W * 32, (INT8 ? 16 : 12) / W) mmha_decode_kern
             cs[it] = 1.f, sn[it] = 0.f;
             if (2 * pr < p.rot_dim) {
                 if (p.rope_table != nullptr) {
-                    const float2 t = __ldg(p.rope_table + (size_t)bi * 64 + pr);
+                    // kPairIters == 1 whenever the table is used with 64 or more threads; narrower CTAs fetch the rest here
+                    const float2 t = (it == 0 && kPairThreads == 64) ? rope_pre : __ldg(p.rope_table + (size_t)blockIdx.z * 64 + pr);
                     cs[it] = t.x, sn[it] = t.y;
                 }
                 else {

@@ -30,7 +30,7 @@ struct MmhaParams {
     const int*           padding;   // [B] or null (total_padding_tokens)
     const int*           order;     // [B] or null: sequence handled by grid row z (longest first evens out the tail)
     const MmhaSeqDesc*   desc;      // [B] or null: the same in launch order with lengths, pointers and flags gathered
-    const float2*        rope_table;  // [B][64] {cos, sin} of every sequence's position, or null (computed in the kernel)
+    const float2*        rope_table;  // [B][64] {cos, sin} of every sequence's position, in the order of `desc` (launch order), or null (computed in the kernel)
     int                  B, H, Hkv, stride, S_max, timestep, rot_dim, max_pos, use_dynamic_ntk, use_logn;
     int                  pos_from_length;  // RoPE position = cached length (the decode driver; lets a CUDA graph be replayed)
     float                rope_base, inv_sqrt_dh, k_scale, k_zp, v_scale, v_zp;
