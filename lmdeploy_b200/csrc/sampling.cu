@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling
         __syncthreads();
     }
     if (tid == 0 && p.min_lengths && p.sequence_lengths && p.sequence_lengths[b] + 1 - p.max_input_length < p.min_lengths[b]) {
-        s_row[p.end_ids[b]] = -FLT_MAX;
+        const int e = p.end_ids[b];
+        if (e >= 0 && e < V) s_row[e] = -FLT_MAX;
     }
     __syncthreads();
     // the reference's penalty kernels rewrite the logits: leave the same values behind
