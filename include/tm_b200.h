@@ -244,6 +244,22 @@ TM_API size_t tm_sampling_rng_state_bytes(void);
 /* seeds [batch] on the device, or NULL: every sequence starts from `seed` */
 TM_API int tm_sampling_rng_init(void* states, int batch_size, const unsigned long long* seeds, unsigned long long seed, void* stream);
 TM_API int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, void* stream);
+/* Word lists and stopping, beam width 1.  Replace invokeBanBadWords (src/turbomind/kernels/ban_bad_words.h),
+ * invokeStopWordsCriterion and invokeLengthCriterion (src/turbomind/kernels/stop_criteria_kernels.h) as
+ * DynamicDecodeLayer<T>::forward calls them (src/turbomind/layers/DynamicDecodeLayer.cc:214-236, 303-337).
+ * A word list is the reference's int tensor [2][len] per sequence (or one shared list): row 0 the tokens of all items
+ * back to back, row 1 the exclusive end offset of every item, padded with -1.  output_ids[s * stride + b] is the token of
+ * sequence b at step s (stride 0 = batch_size).
+ *   tm_ban_bad_words         logits[b][last token of an item] = -inf when the item's other tokens are the last ones generated
+ *                            (steps step - size + 1 .. step - 1); single-token items are always banned
+ *   tm_stop_words_criterion  finished[b] = 1 when the tokens up to and including step `step` end with an item
+ *   tm_length_criterion      finished[b] |= step >= sequence_limit_length[b]; *finished_count (device, optional) = how many */
+TM_API int tm_ban_bad_words(float* logits, int ld, int vocab_size, int batch_size, const int* output_ids, int output_ids_stride,
+                     const int* bad_words, int bad_words_len, int share_words, int step, void* stream);
+TM_API int tm_stop_words_criterion(const int* output_ids, int output_ids_stride, const int* stop_words, int stop_words_len,
+                            unsigned char* finished, int batch_size, int step, void* stream);
+TM_API int tm_length_criterion(unsigned char* finished, const unsigned* sequence_limit_length, int batch_size, int step,
+                        int* finished_count, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * RMSNorm of the decoder loop (half data, fp32 math).  Replace
@@ -584,6 +600,8 @@ typedef struct tm_request {
     float              repetition_penalty;
     unsigned long long random_seed;
     int                ignore_eos;
+    const int*         stop_ids;           /* host memory, copied: drawing one of these tokens ends the request too (the   */
+    int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:514-515) */
 } tm_request;
 enum { TM_REQUEST_QUEUED = 0, TM_REQUEST_RUNNING = 1, TM_REQUEST_FINISHED = 2, TM_REQUEST_FAILED = 3 };
 TM_API int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager* cache, int max_batch_size, int session_len,

@@ -26,6 +26,7 @@ namespace {
 
 struct Slot {
     tm_request        req{};
+    std::vector<int>  stop_ids;      // tokens that end the request besides the end id
     tm_cache_sequence seq{};
     std::vector<int>  tokens;        // everything the sequence holds: cached history, prompt, generated
     int               prompt_end = 0;  // tokens.size() when generation started
@@ -57,6 +58,7 @@ struct tm_batch {
 
     std::deque<tm_request>                       pending;
     std::deque<std::vector<int>>                 pending_ids;  // the prompt of pending[i]
+    std::deque<std::vector<int>>                 pending_stop; // its stop tokens
     std::vector<tmb::Slot>                       slots;        // [0, active) are live
     int                                          active = 0;
     std::unordered_map<uint64_t, tmb::Result>    results;
@@ -151,6 +153,7 @@ extern "C" int tm_batch_submit(tm_batch* b, const tm_request* r)
 {
     if (!b || !r || r->input_length < 0 || (r->input_length > 0 && !r->input_ids) || r->request_output_len < 0) return TM_ERR_INVALID_ARG;
     if (r->top_k < 0 || r->top_k > 1024 || r->top_p < 0.f || r->top_p > 1.f) return TM_ERR_INVALID_ARG;
+    if (r->stop_count < 0 || (r->stop_count > 0 && !r->stop_ids)) return TM_ERR_INVALID_ARG;
     for (int i = 0; i < r->input_length; ++i) {
         if (r->input_ids[i] < 0 || r->input_ids[i] >= b->vocab) return TM_ERR_INVALID_ARG;
     }
@@ -161,7 +164,9 @@ extern "C" int tm_batch_submit(tm_batch* b, const tm_request* r)
     if (!r->start_flag && !tm_cache_contains(b->cache, r->id)) return TM_ERR_INVALID_ARG;  // continuing an unknown session
     b->pending.push_back(*r);
     b->pending_ids.emplace_back(r->input_ids, r->input_ids + r->input_length);
+    b->pending_stop.emplace_back(r->stop_ids, r->stop_ids + r->stop_count);
     b->pending.back().input_ids = nullptr;
+    b->pending.back().stop_ids  = nullptr;
     b->results[r->id]           = Result{};
     return TM_OK;
 }
@@ -304,9 +309,11 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
     while (!b->pending.empty() && b->active < b->max_batch) {
         tm_request       r   = b->pending.front();
         std::vector<int> ids = std::move(b->pending_ids.front());
+        Slot sl{};
+        sl.stop_ids = std::move(b->pending_stop.front());
         b->pending.pop_front();
         b->pending_ids.pop_front();
-        Slot sl{};
+        b->pending_stop.pop_front();
         sl.req = r;
         rc     = r.start_flag ? tm_cache_create(b->cache, r.id, s, &sl.seq) : tm_cache_fetch(b->cache, r.id, s, &sl.seq);
         if (rc != TM_OK) {
@@ -456,7 +463,8 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
         const int tok = b->h_ids[i];
         sl.tokens.push_back(tok);
         b->results[sl.req.id].generated.push_back(tok);
-        const bool stop = (tok == b->end_id && !sl.req.ignore_eos) || (int)sl.tokens.size() >= sl.limit;
+        const bool stop = (tok == b->end_id && !sl.req.ignore_eos) || (int)sl.tokens.size() >= sl.limit
+                          || std::find(sl.stop_ids.begin(), sl.stop_ids.end(), tok) != sl.stop_ids.end();
         if (stop) {
             finish_slot(b, i, TM_REQUEST_FINISHED);
             if ((rc = compact(b, i, s)) != TM_OK) return rc;

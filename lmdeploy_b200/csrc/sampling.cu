@@ -14,6 +14,7 @@
 #include "handle.h"
 #include "tm_b200.h"
 
+#include <algorithm>
 #include <cfloat>
 #include <curand_kernel.h>
 
@@ -205,5 +206,107 @@ extern "C" int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, vo
     if (smem > (size_t)h->max_smem - 1024) return TM_ERR_UNSUPPORTED;  // the row must fit shared memory (about 55 000 tokens)
     sample_topk_kernel<<<p.batch_size, kSampleThreads, smem, (cudaStream_t)stream>>>(p);
     ++h->launches;
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+// ---- word lists and stopping (beam width 1): ban_bad_words (src/turbomind/kernels/ban_bad_words.cu:22-84),
+// ---- stop_words_criterion and length_criterion (src/turbomind/kernels/stop_criteria_kernels.cu:25-132), as
+// ---- DynamicDecodeLayer<T>::forward drives them (src/turbomind/layers/DynamicDecodeLayer.cc:214-236, 303-337).
+// A word list is the reference's tensor [2][len]: row 0 the tokens of all items back to back, row 1 the exclusive
+// end offset of every item (-1 pads the row).  History: ids[s * stride + b] for steps s < step (+ the token of `step`
+// itself for the stop check).
+namespace tmb {
+namespace {
+
+__global__ void ban_bad_words_kernel(float* logits, int ld, int vocab, const int* ids, int stride, const int* words, int len,
+                                     int share, int step)
+{
+    const int id = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b  = blockIdx.y;
+    const int* w   = share ? words : words + (size_t)b * 2 * len;
+    const int* off = w + len;
+    if (id >= len || off[id] < 0) return;
+    const int end = off[id], start = id > 0 ? off[id - 1] : 0, size = end - start;
+    bool ban = size == 1;  // a single token is banned whatever came before
+    if (size > 1 && step >= size - 1) {
+        ban = true;  // the item's first size - 1 tokens must be the last ones generated
+        for (int k = size - 2; k >= 0; --k) {
+            if (ids[(size_t)(step - (size - 1) + k) * stride + b] != w[start + k]) {
+                ban = false;
+                break;
+            }
+        }
+    }
+    if (ban) {
+        const int t = w[end - 1];
+        if (0 < t && t < vocab) logits[(size_t)b * ld + t] = -INFINITY;
+    }
+}
+
+__global__ void stop_words_kernel(const int* ids, int stride, const int* words, int len, unsigned char* finished, int step)
+{
+    const int id = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b  = blockIdx.y;
+    const int* w   = words + (size_t)b * 2 * len;
+    const int* off = w + len;
+    if (id >= len || off[id] < 0) return;
+    const int end = off[id], start = id > 0 ? off[id - 1] : 0, size = end - start;
+    if (step + 1 < size) return;  // not enough tokens yet
+    for (int k = size - 1; k >= 0; --k) {
+        if (ids[(size_t)(step - (size - 1) + k) * stride + b] != w[start + k]) return;
+    }
+    finished[b] = 1;
+}
+
+__global__ void length_criterion_kernel(unsigned char* finished, const unsigned* limit, int batch, int step, int* finished_count)
+{
+    __shared__ int s_count;
+    if (threadIdx.x == 0) s_count = 0;
+    __syncthreads();
+    int mine = 0;
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+        if ((unsigned)step >= limit[b]) finished[b] = 1;
+        mine += finished[b] ? 1 : 0;
+    }
+    if (mine) atomicAdd(&s_count, mine);
+    __syncthreads();
+    if (threadIdx.x == 0 && finished_count) *finished_count = s_count;
+}
+
+}  // namespace
+}  // namespace tmb
+
+extern "C" int tm_ban_bad_words(float* logits, int ld, int vocab_size, int batch_size, const int* output_ids, int output_ids_stride,
+                                const int* bad_words, int bad_words_len, int share_words, int step, void* stream)
+{
+    if (!logits || !bad_words || batch_size <= 0 || vocab_size <= 0 || ld < vocab_size || bad_words_len < 0 || step < 0) return TM_ERR_INVALID_ARG;
+    if (bad_words_len == 0) return TM_OK;
+    if (!output_ids && step > 0) return TM_ERR_INVALID_ARG;
+    const int threads = std::min(256, (bad_words_len + 31) / 32 * 32);
+    const dim3 grid((bad_words_len + threads - 1) / threads, batch_size);
+    ban_bad_words_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(logits, ld, vocab_size, output_ids,
+                                                                     output_ids_stride > 0 ? output_ids_stride : batch_size, bad_words,
+                                                                     bad_words_len, share_words, step);
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+extern "C" int tm_stop_words_criterion(const int* output_ids, int output_ids_stride, const int* stop_words, int stop_words_len,
+                                       unsigned char* finished, int batch_size, int step, void* stream)
+{
+    if (!output_ids || !stop_words || !finished || batch_size <= 0 || stop_words_len < 0 || step < 0) return TM_ERR_INVALID_ARG;
+    if (stop_words_len == 0) return TM_OK;
+    const int threads = std::min(256, (stop_words_len + 31) / 32 * 32);
+    const dim3 grid((stop_words_len + threads - 1) / threads, batch_size);
+    stop_words_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>(output_ids, output_ids_stride > 0 ? output_ids_stride : batch_size,
+                                                                  stop_words, stop_words_len, finished, step);
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+extern "C" int tm_length_criterion(unsigned char* finished, const unsigned* sequence_limit_length, int batch_size, int step,
+                                   int* finished_count, void* stream)
+{
+    if (!finished || !sequence_limit_length || batch_size <= 0 || step < 0) return TM_ERR_INVALID_ARG;
+    length_criterion_kernel<<<1, std::min(512, (batch_size + 31) / 32 * 32), 0, (cudaStream_t)stream>>>(finished, sequence_limit_length,
+                                                                                                       batch_size, step, finished_count);
     return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
 }

@@ -92,7 +92,7 @@ class TmRequest(C.Structure):
     _fields_ = [("id", C.c_uint64), ("start_flag", C.c_int), ("end_flag", C.c_int), ("input_ids", C.POINTER(C.c_int)),
                 ("input_length", C.c_int), ("request_output_len", C.c_int), ("top_k", C.c_int), ("top_p", C.c_float),
                 ("temperature", C.c_float), ("repetition_penalty", C.c_float), ("random_seed", C.c_ulonglong),
-                ("ignore_eos", C.c_int)]
+                ("ignore_eos", C.c_int), ("stop_ids", C.POINTER(C.c_int)), ("stop_count", C.c_int)]
 
 
 class TmContextAttentionParams(C.Structure):
@@ -178,6 +178,9 @@ SIGNATURES = {
     "tm_batch_counts": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong)]),
     "tm_sampling_rng_state_bytes": (_sz, []),
     "tm_sampling_rng_init": (_i, [_vp, _i, _vp, C.c_ulonglong, _vp]),
+    "tm_ban_bad_words": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "tm_stop_words_criterion": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp]),
+    "tm_length_criterion": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "tm_sample_topk": (_i, [_vp, C.POINTER(TmSamplingParams), _vp]),
     "tm_lm_head_f16": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "tm_mmha_decode": (_i, [_vp, C.POINTER(TmMmhaParams), _vp]),

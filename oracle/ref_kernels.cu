@@ -413,3 +413,22 @@ REF_API int ref_batch_topk_sampling(void* workspace, size_t* workspace_bytes, co
     *workspace_bytes = ws;
     return workspace ? finish(st) : 0;
 }
+
+// ---- word lists and stopping: the reference's kernels as DynamicDecodeLayer::forward calls them (beam width 1)
+#include "src/turbomind/kernels/ban_bad_words.h"
+#include "src/turbomind/kernels/stop_criteria_kernels.h"
+
+REF_API int ref_ban_bad_words(float* logits, const int* output_ids, int batch, const int* bad_words, int share_words, int bad_words_len,
+                              int vocab, int step, cudaStream_t st)
+{
+    turbomind::invokeBanBadWords(logits, output_ids, (const int*)nullptr, batch, batch, 1, bad_words, share_words != 0,
+                                 (size_t)bad_words_len, 0, vocab, (size_t)step, st);
+    return finish(st);
+}
+
+REF_API int ref_stop_words_criterion(const int* output_ids, const int* stop_words, bool* finished, int stop_words_len, int batch, int step,
+                                     cudaStream_t st)
+{
+    turbomind::invokeStopWordsCriterion(output_ids, (const int*)nullptr, stop_words, finished, 0, (size_t)stop_words_len, batch, 1, step, st);
+    return finish(st);
+}

@@ -76,3 +76,52 @@ def sample(logits, top_ks, top_ps, uniforms, finished=None, end_ids=None):
             continue
         ids[b], margins[b] = topk_sample(logits[b], top_ks[b], top_ps[b], uniforms[b])
     return ids, margins
+
+
+def _items(words):
+    """words: int array [2, len] (tokens back to back | exclusive end offsets, -1 padded) -> list of token lists."""
+    toks, offs = np.asarray(words[0]), np.asarray(words[1])
+    out, start = [], 0
+    for i, end in enumerate(offs):
+        if end < 0:
+            out.append(None)        # padding entry: the kernels skip it but keep using its offset as the next start
+            continue
+        out.append(list(toks[start:end]))
+        start = int(end)
+    # the reference takes the start of item i from offs[i - 1] whatever its sign; with -1 padding only at the tail that is
+    # the running `start` above
+    return [o for o in out if o is not None]
+
+
+def ban_bad_words(logits, output_ids, bad_words, share_words, step):
+    """src/turbomind/kernels/ban_bad_words.cu:22-84, beam width 1.  logits [batch, vocab] float32 -> copy with the banned
+    tokens at -inf; output_ids [steps, batch]; bad_words [batch, 2, len] or [2, len] when shared."""
+    x = np.array(logits, dtype=np.float32, copy=True)
+    B, V = x.shape
+    for b in range(B):
+        for item in _items(bad_words if share_words else bad_words[b]):
+            n = len(item)
+            ban = n == 1
+            if n > 1 and step >= n - 1:
+                ban = all(int(output_ids[step - (n - 1) + k, b]) == int(item[k]) for k in range(n - 1))
+            if ban and 0 < int(item[-1]) < V:
+                x[b, int(item[-1])] = -np.inf
+    return x
+
+
+def stop_words_criterion(output_ids, stop_words, finished, step):
+    """src/turbomind/kernels/stop_criteria_kernels.cu:25-84, beam width 1: finished[b] set when the tokens up to and
+    including `step` end with one of the sequence's items."""
+    f = np.array(finished, dtype=bool, copy=True)
+    for b in range(len(f)):
+        for item in _items(stop_words[b]):
+            n = len(item)
+            if step + 1 >= n and all(int(output_ids[step - (n - 1) + k, b]) == int(item[k]) for k in range(n)):
+                f[b] = True
+    return f
+
+
+def length_criterion(finished, limits, step):
+    """stop_criteria_kernels.cu:107-132: finished |= step >= limit; also how many are finished."""
+    f = np.array(finished, dtype=bool, copy=True) | (step >= np.asarray(limits))
+    return f, int(f.sum())

@@ -60,6 +60,12 @@ def test_end_id_zero_length_and_failures():
     res, _ = _run(model, 2, [(sid, prompt, 8), (sid + 1, prompt, 0)], llama, end_id=stop, ignore_eos=False)
     assert res[sid][0] == toks[:first + 1] and res[sid][1] == llama.Batch.FINISHED       # the end id is the last token out
     assert res[sid + 1] == ([], llama.Batch.FINISHED)
+    # a stop token of the request's own ends it the same way, with the end id left alone
+    b = llama.Batch(model, 2)
+    assert b.submit(sid, prompt, 8, ignore_eos=True, stop_ids=[toks[4], 999999]) == 0
+    b.run(max_rounds=50)
+    assert b.output(sid) == (toks[:toks.index(toks[4]) + 1], llama.Batch.FINISHED)
+    b.close()
     b = llama.Batch(model, 2)
     assert b.submit(7, [1, 2, 3], 4, start=False) != 0                                   # continuing a session nobody started
     assert b.submit(8, [CFG["vocab_size"]], 4) != 0                                      # token outside the vocabulary

@@ -160,3 +160,75 @@ def test_lm_head_matches_fp32_matmul(T, V, H, ld):
     assert err <= 2e-3 * max(1.0, want.abs().max().item()), err
     if ld > V:
         assert bool((out[:, V:] == 123.0).all())
+
+
+def _word_lists(rng, B, V, length):
+    """per sequence a [2, length] list: a few items of 1..3 tokens, offsets padded with -1"""
+    out = np.zeros((B, 2, length), np.int32)
+    out[:, 1, :] = -1
+    for b in range(B):
+        pos, i = 0, 0
+        while True:
+            n = int(rng.integers(1, 4))
+            if pos + n > length or i >= length:
+                break
+            out[b, 0, pos:pos + n] = rng.integers(1, V, n)
+            pos += n
+            out[b, 1, i] = pos
+            i += 1
+    return out
+
+
+@pytest.mark.parametrize("share", [False, True])
+def test_word_lists_match_the_reference_kernels_and_the_oracle(share):
+    from lmdeploy_b200 import lib as l
+    rng = np.random.default_rng(21 + int(share))
+    B, V, steps, L = 9, 500, 7, 12
+    words = _word_lists(rng, 1 if share else B, V, L)
+    ids = rng.integers(1, V, (steps, B)).astype(np.int32)
+    # plant matches: the history of sequence b ends with the head of one of its items at some steps
+    for b in range(B):
+        w = words[0 if share else b]
+        ends = [e for e in w[1] if e >= 0]
+        if len(ends) >= 2:
+            s0, e0 = int(ends[0]), int(ends[1])
+            item = w[0, s0:e0]
+            ids[steps - 1 - len(item) + 1: steps, b] = item          # whole item ends at the last step
+            if len(item) > 1:
+                ids[2: 2 + len(item) - 1, b] = item[:-1]               # head of the item ends at step 2 + len - 2
+    d_ids, d_words = torch.from_numpy(ids).cuda(), torch.from_numpy(words if not share else words[0]).cuda().contiguous()
+    ref = C.CDLL(_REF) if os.path.exists(_REF) else None
+    if ref is not None and not hasattr(ref, "ref_ban_bad_words"):
+        ref = None
+    vp = C.c_void_p
+    for step in range(steps):
+        x = (rng.standard_normal((B, V))).astype(np.float32)
+        xa = torch.from_numpy(x).cuda()
+        assert l.lib.tm_ban_bad_words(xa.data_ptr(), V, V, B, d_ids.data_ptr(), 0, d_words.data_ptr(), L, int(share), step, _stream()) == l.TM_OK
+        torch.cuda.synchronize()
+        want = osamp.ban_bad_words(x, ids, words[0] if share else words, share, step)
+        np.testing.assert_array_equal(xa.cpu().numpy(), want)
+        if ref is not None:
+            xb = torch.from_numpy(x).cuda()
+            assert ref.ref_ban_bad_words(vp(xb.data_ptr()), vp(d_ids.data_ptr()), B, vp(d_words.data_ptr()), int(share), L, V, step, _stream()) == 0
+            assert torch.equal(xa, xb), f"step {step}"
+    if not share:
+        for step in range(steps):
+            fa = torch.zeros(B, dtype=torch.uint8, device="cuda")
+            assert l.lib.tm_stop_words_criterion(d_ids.data_ptr(), 0, d_words.data_ptr(), L, fa.data_ptr(), B, step, _stream()) == l.TM_OK
+            torch.cuda.synchronize()
+            want = osamp.stop_words_criterion(ids, words, np.zeros(B, bool), step)
+            np.testing.assert_array_equal(fa.cpu().numpy().astype(bool), want)
+            if ref is not None:
+                fb = torch.zeros(B, dtype=torch.bool, device="cuda")
+                assert ref.ref_stop_words_criterion(vp(d_ids.data_ptr()), vp(d_words.data_ptr()), vp(fb.data_ptr()), L, B, step, _stream()) == 0
+                assert torch.equal(fa.bool(), fb), f"step {step}"
+        assert want.any()                                  # the planted endings were found at the last step
+        limits = torch.tensor(rng.integers(0, 10, B), dtype=torch.int32, device="cuda")
+        fin = torch.from_numpy(want.astype(np.uint8)).cuda()
+        count = torch.zeros(1, dtype=torch.int32, device="cuda")
+        assert l.lib.tm_length_criterion(fin.data_ptr(), limits.data_ptr(), B, 5, count.data_ptr(), _stream()) == l.TM_OK
+        torch.cuda.synchronize()
+        f2, n2 = osamp.length_criterion(want, limits.cpu().numpy(), 5)
+        np.testing.assert_array_equal(fin.cpu().numpy().astype(bool), f2)
+        assert int(count.item()) == n2

@@ -35,3 +35,22 @@ def test_finished_rows_emit_the_end_id():
     x = np.random.default_rng(0).standard_normal((3, 50)).astype(np.float32)
     ids, _ = osamp.sample(x, [5, 5, 5], [1.0, 1.0, 1.0], [0.5, 0.5, 0.5], finished=[0, 1, 0], end_ids=[2, 2, 2])
     assert ids[1] == 2
+
+
+def test_word_lists_known_answers():
+    # two items for sequence 0: [5] and [7, 8]; one for sequence 1: [9, 9, 4]; padded with -1 offsets
+    words = np.array([[[5, 7, 8, 0], [1, 3, -1, -1]], [[9, 9, 4, 0], [3, -1, -1, -1]]])
+    ids = np.array([[1, 9], [7, 9], [3, 2]])                 # steps 0..2
+    x = np.zeros((2, 12), np.float32)
+    y = osamp.ban_bad_words(x, ids, words, False, 2)         # about to draw step 2: history = steps 0, 1
+    assert y[0, 5] == -np.inf and y[0, 8] == -np.inf        # single token always; [7, 8] because 7 was drawn last
+    assert y[1, 4] == -np.inf and np.isinf(y).sum() == 3    # [9, 9, 4]: the last two were 9, 9
+    y = osamp.ban_bad_words(x, ids, words, False, 1)         # one step earlier: 7 not drawn yet, only one 9
+    assert y[0, 5] == -np.inf and np.isinf(y).sum() == 1
+    ids2 = np.array([[7, 9], [8, 9], [5, 4]])
+    f = osamp.stop_words_criterion(ids2, words, [False, False], 1)
+    assert list(f) == [True, False]                          # sequence 0 ends with 7, 8
+    f = osamp.stop_words_criterion(ids2, words, [False, False], 2)
+    assert list(f) == [True, True]                           # 5 ; 9, 9, 4
+    f, n = osamp.length_criterion([False, True, False], [5, 9, 3], 4)
+    assert list(f) == [False, True, True] and n == 2
