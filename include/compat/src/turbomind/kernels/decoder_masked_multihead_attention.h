@@ -42,64 +42,47 @@
     } while (0)
 #endif
 
-/* B sequences, H query heads, Dh = 128 values per head. */
+/* B sequences, H query heads, Dh = 128 values per head.  Members are grouped by kind here (the call site assigns them
+ * by name after a memset of the whole struct, so their order is free). */
 template<typename T>
 struct Multihead_attention_params_base {
-    T* out = nullptr;  // [B, H * Dh]
+    // ---- tensors the LLaMA path uses
+    T*       out = nullptr;                                      // [B, H * Dh]
+    const T *q = nullptr, *k = nullptr, *v = nullptr;            // new token; one fused buffer for LLaMA, `stride` apart per sequence
+    const T *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;
+    const int* total_padding_tokens = nullptr;                   // rotary position of sequence b = timestep - total_padding_tokens[b]
 
-    // q | k | v of the new token and their biases; for LLaMA the three live in one buffer, `stride` apart per sequence
-    const T *q = nullptr, *q_bias = nullptr;
-    const T *k = nullptr, *k_bias = nullptr;
-    const T *v = nullptr, *v_bias = nullptr;
-
-    // int8-activation scales of other models: must stay null here
-    const float* query_weight_output_scale               = nullptr;
-    const float* attention_qk_scale                      = nullptr;
-    const float* attention_output_weight_input_scale_inv = nullptr;
-
-    int stride               = 0;
-    int batch_size           = 0;
-    int beam_width           = 0;  // 0 or 1 only
-    int memory_max_len       = 0;  // rows of every sequence's cache (a ring once the sequence is longer)
-    int num_heads            = 0;
-    int hidden_size_per_head = 0;
-    int rotary_embedding_dim = 0;
-    int max_input_length     = 0;
-    int timestep             = 0;  // >= every length_per_sample[b]
-
+    // ---- sizes and scalars the LLaMA path uses
+    int   stride = 0, batch_size = 0, num_heads = 0, hidden_size_per_head = 0, rotary_embedding_dim = 0;
+    int   memory_max_len = 0;                                    // rows of every sequence's cache (a ring once the sequence is longer)
+    int   timestep = 0;                                          // >= every length_per_sample[b]
+    int   max_input_length = 0;
     float inv_sqrt_dh = 0.0f;
+    int   int8_mode = 0;                                         // bit 2 (QuantPolicy::kCacheKVInt8): the cache holds int8
+    float attention_k_scale = 0.f, attention_k_zp = 0.f, attention_v_scale = 0.f, attention_v_zp = 0.f;
 
-    const int* total_padding_tokens = nullptr;  // rotary position of sequence b = timestep - total_padding_tokens[b]
-
-    const bool* masked_tokens            = nullptr;  // ignored, as the reference's LLaMA kernel ignores it
-    const int*  prefix_prompt_lengths    = nullptr;  // must stay null
-    int         max_prefix_prompt_length = 0;        // must stay 0
-
-    const T* relative_attention_bias        = nullptr;  // must stay null
-    int      relative_attention_bias_stride = 0;
-    const T* linear_bias_slopes             = nullptr;  // must stay null
-
-    const float* qkv_scale_out       = nullptr;  // must stay null
-    const float* attention_out_scale = nullptr;  // must stay null
-    int          int8_mode           = 0;        // bit 2 (QuantPolicy::kCacheKVInt8): the cache holds int8
-    float        attention_k_scale   = 0.f;
-    float        attention_k_zp      = 0.f;
-    float        attention_v_scale   = 0.f;
-    float        attention_v_zp      = 0.f;
+    // ---- carried for source compatibility: must stay 0 / null (a call that sets one is refused), except masked_tokens,
+    // ---- which the reference's LLaMA kernel ignores as well
+    int          beam_width = 0;                                 // 0 or 1 only
+    const bool*  masked_tokens = nullptr;
+    const int*   prefix_prompt_lengths = nullptr;
+    int          max_prefix_prompt_length = 0;
+    const T*     relative_attention_bias = nullptr;
+    int          relative_attention_bias_stride = 0;
+    const T*     linear_bias_slopes = nullptr;
+    const float *query_weight_output_scale = nullptr, *attention_qk_scale = nullptr, *attention_output_weight_input_scale_inv = nullptr;
+    const float *qkv_scale_out = nullptr, *attention_out_scale = nullptr;
 };
 
 template<typename T>
 struct Multihead_attention_params: public Multihead_attention_params_base<T> {
-    bool*      finished                   = nullptr;  // [B] or null: finished sequences are skipped
-    const int* length_per_sample          = nullptr;  // [B] tokens already cached
-    T**        k_cache_per_sample         = nullptr;  // [B] base pointers; this layer starts kv_cache_per_sample_offset elements in
-    T**        v_cache_per_sample         = nullptr;
-    size_t     kv_cache_per_sample_offset = 0;
-    int        num_kv_heads               = 0;
-    int        max_position_embeddings    = 0;
-    bool       use_dynamic_ntk            = false;
-    bool       use_logn_attn              = false;
-    float      rotary_embedding_base      = 10000.0f;
+    T **       k_cache_per_sample = nullptr, **v_cache_per_sample = nullptr;  // [B] base pointers
+    size_t     kv_cache_per_sample_offset = 0;                                // elements from a base pointer to this layer
+    const int* length_per_sample = nullptr;                                   // [B] tokens already cached
+    bool*      finished = nullptr;                                            // [B] or null: finished sequences are skipped
+    int        num_kv_heads = 0, max_position_embeddings = 0;
+    float      rotary_embedding_base = 10000.0f;
+    bool       use_dynamic_ntk = false, use_logn_attn = false;
 };
 
 template<class T>
