@@ -124,6 +124,23 @@ REF_API int ref_gemm_s4_f16(void* C, const void* A, const void* B, const void* Q
     return finish((cudaStream_t)stream);
 }
 
+// The same with the tile configuration named by the caller: algo_id indexes the list of
+// src/turbomind/kernels/gemm_s_f16/gemm_s4_f16.cu:72-93 (0 = 256x128x32 ... 15 = 64x16x256, 16 = 64x8x256).
+REF_API int ref_gemm_s4_f16_algo(void* C, const void* A, const void* B, const void* Q, int m, int n, int k, int group_size, int type,
+                                 int algo_id, void* stream)
+{
+    static turbomind::GemmS4F16 gemm;
+    try {
+        gemm.Run((half*)C, (const uint*)A, (const half*)B, (const half2*)Q, m, n, k, group_size,
+                 type ? turbomind::GemmS4F16::kFusedSiluFfn : turbomind::GemmS4F16::kGemm, algo_id, (cudaStream_t)stream);
+    }
+    catch (const std::exception& e) {
+        std::fprintf(stderr, "ref_gemm_s4_f16_algo: %s\n", e.what());
+        return -1;
+    }
+    return finish((cudaStream_t)stream);
+}
+
 // masked_multihead_attention for fp16 (src/turbomind/kernels/decoder_masked_multihead_attention.h:50-133), with the
 // members LlamaDecoderSelfAttentionLayer.cc:44-166 sets for LLaMA.
 REF_API int ref_mmha_decode(void* out, const void* q, const void* k, const void* v, const void* q_bias, const void* k_bias,

@@ -33,6 +33,7 @@ def ref():
     lib.ref_fuse_w1_w3_s4_k_m8.argtypes = [vp, vp, i, i, vp]
     lib.ref_dequantize_s4.argtypes = [vp, vp, C.c_size_t, vp]
     lib.ref_gemm_s4_f16.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp]
+    lib.ref_gemm_s4_f16_algo.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, vp]
     lib.ref_mmha_decode.argtypes = [vp] * 7 + [i] * 5 + [i, f32, i, vp, vp, vp, vp, vp, C.c_size_t, i, f32, f32, f32, f32, i, i,
                                                           i, vp]
     lib.ref_add_residual_rmsnorm.argtypes = [vp, vp, vp, vp, f32, i, i, vp]
@@ -145,19 +146,43 @@ def test_gemm_matches_reference_kernel(ref, n, k, fused, tokens):
     assert_close(y_lib, y_cpu, f"library vs CPU oracle {n}x{k} T={tokens} fused={fused}", rel_slack=slack)
 
 
+@pytest.mark.parametrize("n,k,tokens,algo", [(4096, 4096, 12, 15), (4096, 4096, 16, 15), (4096, 4096, 12, 13), (1536, 2048, 24, 15),
+                                             (1536, 2048, 24, 13), (4096, 4096, 8, 16)])
+def test_gemm_matches_reference_kernel_with_a_named_tile(ref, n, k, tokens, algo):
+    """Where the reference's own estimate picks its 64 x 8 x 256 tile (index 16 of gemm_s4_f16.cu:72-93) for more than
+    8 tokens (on 148 SMs: 9..16 tokens on 4096 x 4096 and 4096 x 11008, every count above 8 on 1536 x 2048), that kernel
+    returns wrong rows.  Its activation iterator (cta_iterator.h:452-457) deals the tile's rows to
+    kWarpN = WARPS / kWarpK = 2 warps although one warp's footprint (8 rows) already covers the tile (kIterN is clamped
+    to 1), and masks a row only by the global token count (`is_valid_n_`, :547,591,611; the copy is predicated on it, :616-617).  With at most 8 tokens the
+    second warp's rows 8..15 are masked; with more they are real tokens, and their copies land 8 rows further down in
+    shared memory, which is rows 0..7 of the next pipeline stage, racing with that stage's own copies.  The same
+    arithmetic gives the 256 x 8 x 256 tile (index 5) twice as many warps as rows.  The other tiles deal the rows
+    exactly, so the comparison names one of them: 15 = 64 x 16 x 256, 13 = 128 x 8 x 512; 16 itself up to 8 tokens."""
+    from lmdeploy_b200 import turbomind as tm
+    lin = make_linear(n, k, 21)
+    x = (np.random.default_rng(5).standard_normal((tokens, k)) * 1.0).astype(np.float16)
+    A, Q, X = dev(lin["A"], torch.int32), dev(lin["Q"]), dev(x)
+    y_ref = torch.zeros((tokens, n), dtype=torch.float16, device="cuda")
+    y_lib = torch.zeros_like(y_ref)
+    assert ref.ref_gemm_s4_f16_algo(_p(y_ref), _p(A), _p(X), _p(Q), n, tokens, k, 128, 0, algo, None) == 0
+    w = tm.LlamaDenseWeight(k, n, A, tm.WeightType.kINT4, None, Q, 128)
+    op = tm.LlamaLinear(0)
+    op.forward(y_lib, X, tokens, w, op.kGemm)
+    torch.cuda.synchronize()
+    y_lib, y_ref, y_cpu = y_lib.cpu().numpy(), y_ref.cpu().numpy(), og.gemm_s4_f16(x, lin["w_kn"], False)
+    assert_close(y_lib, y_ref, f"library vs reference tile {algo}, {n}x{k} T={tokens}")
+    assert_close(y_ref, y_cpu, f"reference tile {algo} vs CPU oracle {n}x{k} T={tokens}")
+    assert_close(y_lib, y_cpu, f"library vs CPU oracle {n}x{k} T={tokens}")
+
+
 @pytest.mark.parametrize("n,k,tokens", [(4096, 4096, 12), (4096, 4096, 16), (1536, 2048, 24)])
-def test_where_the_reference_kernel_leaves_its_own_definition(ref, n, k, tokens):
-    """Built for sm_100a, the reference's GEMM kernels that tile more than 8 tokens with sliced K
-    return wrong rows for some token counts (9..16 on every shape tried; every count above 8 on
-    1536 x 2048): they disagree with the reference's own CPU definition of the operation
-    (pseudo-quantised weight x activations), which the CPU oracle restates.  The library must follow
-    the definition there; the comparison with the reference kernel is reported, not asserted."""
+def test_library_follows_the_definition_where_the_reference_estimate_picks_the_broken_tile(ref, n, k, tokens):
+    """The cases above through GemmS4F16::Run's own choice (algo_id = -1): the library must agree with the CPU
+    definition; how far the reference's pick is from it is printed, not asserted (a race decides it)."""
     y_lib, y_ref, y_cpu = _gemm_three_ways(ref, n, k, tokens, False, 21)
     assert_close(y_lib, y_cpu, f"library vs CPU oracle {n}x{k} T={tokens}")
     err = float(np.abs(y_ref.astype(np.float32) - y_cpu.astype(np.float32)).max())
-    if err > 2e-2:
-        pytest.skip(f"reference kernel differs from the reference's CPU definition by {err:.2f} here; the library agrees with the definition")
-    assert_close(y_lib, y_ref, f"library vs reference kernel {n}x{k} T={tokens}")
+    print(f"reference's own pick vs its CPU definition, {n}x{k} T={tokens}: max abs difference {err:.3f}")
 
 
 # ------------------------------------------------------------------------------------------ norm
