@@ -244,6 +244,21 @@ TM_API size_t tm_sampling_rng_state_bytes(void);
 /* seeds [batch] on the device, or NULL: every sequence starts from `seed` */
 TM_API int tm_sampling_rng_init(void* states, int batch_size, const unsigned long long* seeds, unsigned long long seed, void* stream);
 TM_API int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, void* stream);
+/* Top-p sampling over the whole vocabulary, for the sequences the reference hands to its TopPSamplingLayer (per-request
+ * top_k == 0; mark the others in skip_decode, and the other way round for tm_sample_topk).  Same parameter block
+ * (top_ks / max_top_k are not read) and the same penalties first.  Replaces, in one kernel and without sorting,
+ *   invokeAddBiasSoftMax       (src/turbomind/kernels/sampling_topp_kernels.cu:1295-1361)  p = exp(l - max) / (sum + 1e-6)
+ *   invokeBatchTopPSampling    (sampling_topp_kernels.cu:1007-1161; topp_beam_topk_kernel :802-858, topp_sampling :878-1004)
+ * as TopPSamplingLayer<T>::runSampling calls them (src/turbomind/layers/sampling_layers/TopPSamplingLayer.cu:254-346):
+ * u = curand_uniform(state of the sequence) is drawn for every sequence that is not skipped; when the largest
+ * probability alone reaches top_p that token is taken; otherwise the tokens are walked by descending probability
+ * (equal ones in token order) until the running sum reaches u * top_p (the most probable token if it never does).
+ * Unlike the reference the logits keep the penalised values, not the probabilities.
+ * tm_top_p_decay is invokeComputeToppDecay (sampling_topp_kernels.cu:1381-1426), run by the layer after every draw:
+ *   top_p[b] = output_ids[b] == reset_ids[b] ? initial[b] : max(top_p[b] * decay[b], min[b]). */
+TM_API int tm_sample_topp(tm_handle* h, const tm_sampling_params* params, void* stream);
+TM_API int tm_top_p_decay(float* runtime_top_p, const float* initial_top_p, const int* output_ids, const float* top_p_decay,
+                   const float* top_p_min, const int* top_p_reset_ids, int batch_size, void* stream);
 /* Word lists and stopping, beam width 1.  Replace invokeBanBadWords (src/turbomind/kernels/ban_bad_words.h),
  * invokeStopWordsCriterion and invokeLengthCriterion (src/turbomind/kernels/stop_criteria_kernels.h) as
  * DynamicDecodeLayer<T>::forward calls them (src/turbomind/layers/DynamicDecodeLayer.cc:214-236, 303-337).

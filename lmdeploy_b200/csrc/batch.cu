@@ -69,6 +69,7 @@ struct tm_batch {
     int *  d_topk = nullptr, *d_hist_len = nullptr;
     float *d_logits = nullptr, *d_topp = nullptr, *d_temp = nullptr, *d_rep = nullptr;
     void*  d_rng = nullptr;
+    unsigned char*      d_skip = nullptr;  // [2][max batch]: rows the top-k draw leaves alone | rows the top-p draw leaves alone
     unsigned long long* d_seed = nullptr;
     // prefill staging (grown on demand)
     int*   d_pf_ids = nullptr;
@@ -95,7 +96,7 @@ void batch_free(tm_batch* b)
 {
     void* ptrs[] = {b->d_k,    b->d_v,    b->d_len,  b->d_forced, b->d_out,    b->d_step,  b->d_ids,   b->d_hist, b->d_topk, b->d_hist_len,
                     b->d_logits, b->d_topp, b->d_temp, b->d_rep,    b->d_rng,    b->d_seed,  b->d_pf_ids, b->d_pf_cu, b->d_pf_hist, b->d_pf_ctx,
-                    b->d_pf_k, b->d_pf_v};
+                    b->d_pf_k, b->d_pf_v, b->d_skip};
     for (void* p : ptrs) {
         if (p) cudaFree(p);
     }
@@ -129,7 +130,7 @@ extern "C" int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager
               && dev_alloc(&b->d_hist, B * session_len) && dev_alloc(&b->d_topk, B) && dev_alloc(&b->d_hist_len, B)
               && dev_alloc(&b->d_logits, B * b->vocab) && dev_alloc(&b->d_topp, B) && dev_alloc(&b->d_temp, B) && dev_alloc(&b->d_rep, B)
               && dev_alloc(&b->d_seed, B) && dev_alloc(&b->d_pf_cu, B + 1) && dev_alloc(&b->d_pf_hist, B) && dev_alloc(&b->d_pf_ctx, B)
-              && dev_alloc(&b->d_pf_k, B) && dev_alloc(&b->d_pf_v, B);
+              && dev_alloc(&b->d_pf_k, B) && dev_alloc(&b->d_pf_v, B) && dev_alloc(&b->d_skip, 2 * B);
     ok = ok && cudaMalloc(&b->d_rng, B * tm_sampling_rng_state_bytes()) == cudaSuccess;
     ok = ok && cudaMallocHost((void**)&b->h_ids, B * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(b->d_hist, 0, B * session_len * sizeof(int)) == cudaSuccess;
@@ -394,7 +395,8 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
     std::vector<void*> kp(B), vp(B);
     std::vector<int>   len(B), last(B), hist_len(B), topk(B);
     std::vector<float> topp(B), temp(B), rep(B);
-    int                longest = 0;
+    std::vector<unsigned char> skip(2 * (size_t)b->max_batch, 0);
+    int                longest = 0, n_topk = 0;
     bool               any_rep = false;
     for (int i = 0; i < B; ++i) {
         const Slot& sl = b->slots[i];
@@ -403,9 +405,15 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
         last[i]     = sl.tokens.back();
         hist_len[i] = (int)sl.tokens.size();
         longest     = std::max(longest, hist_len[i]);
-        // TopKSamplingLayer<T>::setup (TopKSamplingLayer.cu:60-76): neither k nor p given means greedy
-        topk[i] = sl.req.top_k > 0 ? sl.req.top_k : (sl.req.top_p > 0.f ? std::min(1024, b->vocab) : 1);
+        // The reference's two sampling layers share the batch (DynamicDecodeLayer.cc:305-312): a request with a top_k is
+        // drawn by the top-k layer (top_p 0 there means 1: TopKSamplingLayer.cu:60-76), one with only a top_p by the
+        // top-p layer (TopPSamplingLayer.cu:70-81), one with neither is greedy (k = 1).
+        const bool only_p = sl.req.top_k == 0 && sl.req.top_p > 0.f;
+        topk[i] = sl.req.top_k > 0 ? sl.req.top_k : 1;
         topp[i] = sl.req.top_p > 0.f ? sl.req.top_p : 1.f;
+        skip[i]                = only_p ? 1 : 0;
+        skip[b->max_batch + i] = only_p ? 0 : 1;
+        n_topk += only_p ? 0 : 1;
         temp[i] = sl.req.temperature > 0.f ? sl.req.temperature : 1.f;
         rep[i]  = sl.req.repetition_penalty > 0.f ? sl.req.repetition_penalty : 1.f;
         any_rep = any_rep || rep[i] != 1.f;
@@ -414,6 +422,7 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
     if (!(up(b->d_k, kp.data(), B * sizeof(void*)) && up(b->d_v, vp.data(), B * sizeof(void*)) && up(b->d_len, len.data(), B * 4)
           && up(b->d_forced, last.data(), B * 4) && up(b->d_hist_len, hist_len.data(), B * 4) && up(b->d_topk, topk.data(), B * 4)
           && up(b->d_topp, topp.data(), B * 4) && up(b->d_temp, temp.data(), B * 4) && up(b->d_rep, rep.data(), B * 4)
+          && up(b->d_skip, skip.data(), skip.size())
           && cudaMemsetAsync(b->d_step, 0, sizeof(int), s) == cudaSuccess)) {
         return TM_ERR_CUDA;
     }
@@ -448,7 +457,14 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
     sp.top_ps     = b->d_topp;
     sp.rng_states = b->d_rng;
     sp.ids        = b->d_ids;
-    if ((rc = tm_sample_topk(b->model->h, &sp, s)) != TM_OK) return rc;
+    if (n_topk > 0) {
+        sp.skip_decode = n_topk < B ? b->d_skip : nullptr;
+        if ((rc = tm_sample_topk(b->model->h, &sp, s)) != TM_OK) return rc;
+    }
+    if (n_topk < B) {
+        sp.skip_decode = n_topk > 0 ? b->d_skip + b->max_batch : nullptr;
+        if ((rc = tm_sample_topp(b->model->h, &sp, s)) != TM_OK) return rc;
+    }
     append_history_kernel<<<(B + 127) / 128, 128, 0, s>>>(b->d_hist, b->d_ids, b->d_hist_len, B, b->max_batch, b->session_len);
     if (cudaGetLastError() != cudaSuccess) return TM_ERR_CUDA;
     if (cudaMemcpyAsync(b->h_ids, b->d_ids, B * sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess

@@ -1,5 +1,6 @@
-// Token sampling of the decode step: temperature, repetition penalty, minimum length, then top-k sampling with a
-// top-p cut inside the k candidates.  One kernel, one CTA per sequence, the logits row held in shared memory.
+// Token sampling of the decode step: temperature, repetition penalty, minimum length, then either top-k sampling with
+// a top-p cut inside the k candidates or top-p sampling over the whole vocabulary.  One kernel each, one CTA per
+// sequence, the logits row held in shared memory.
 //
 // Restates, for fp32 logits, what the reference runs as five launches per step
 //   batchApplyTemperaturePenalty   src/turbomind/kernels/sampling_penalty_kernels.cu:118-146   logit *= 1 / (T + 1e-6)
@@ -34,25 +35,12 @@ __device__ __forceinline__ Best better(Best a, Best b)
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
-__global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling_params p)
+// The penalised logits of sequence b -> s_row (and back to the logits, as the reference's penalty kernels rewrite them):
+// temperature, repetition penalty, minimum length.  Every thread of the CTA calls this; ends with a barrier.
+__device__ __forceinline__ void penalised_row(const tm_sampling_params& p, int b, float* s_row, unsigned* s_seen)
 {
-    extern __shared__ float s_dyn[];
-    float*    s_row  = s_dyn;                                             // [vocab]
-    unsigned* s_seen = reinterpret_cast<unsigned*>(s_row + p.vocab_size); // bitmap of tokens to penalise
-    float*    s_cand = reinterpret_cast<float*>(s_seen + (p.vocab_size + 31) / 32);  // [k] exp(l_i - l_max)
-    int*      s_cid  = reinterpret_cast<int*>(s_cand + kSampleMaxK);                 // [k] token ids
-    __shared__ Best s_warp[kSampleThreads / 32];
-    __shared__ Best s_pick;
-
-    const int b   = blockIdx.x;
-    const int tid = threadIdx.x;
-    if (p.skip_decode && p.skip_decode[b]) return;
-    const int V = p.vocab_size;
-    if (p.finished && p.finished[b]) {
-        // topk_stage2_sampling: a finished sequence keeps emitting its end id and nothing else changes
-        if (tid == 0) p.ids[b] = p.end_ids[b];
-        return;
-    }
+    const int   tid   = threadIdx.x;
+    const int   V     = p.vocab_size;
     float*      row   = p.logits + (size_t)b * p.ld;
     const float inv_t = p.temperatures ? 1.0f / (p.temperatures[b] + 1e-6f) : 1.0f;
     const bool  scale = p.temperatures != nullptr;
@@ -84,10 +72,31 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling
         if (e >= 0 && e < V) s_row[e] = -FLT_MAX;
     }
     __syncthreads();
-    // the reference's penalty kernels rewrite the logits: leave the same values behind
     if (scale || rep || p.min_lengths) {
         for (int v = tid; v < V; v += kSampleThreads) row[v] = s_row[v];
     }
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling_params p)
+{
+    extern __shared__ float s_dyn[];
+    float*    s_row  = s_dyn;                                             // [vocab]
+    unsigned* s_seen = reinterpret_cast<unsigned*>(s_row + p.vocab_size); // bitmap of tokens to penalise
+    float*    s_cand = reinterpret_cast<float*>(s_seen + (p.vocab_size + 31) / 32);  // [k] exp(l_i - l_max)
+    int*      s_cid  = reinterpret_cast<int*>(s_cand + kSampleMaxK);                 // [k] token ids
+    __shared__ Best s_warp[kSampleThreads / 32];
+    __shared__ Best s_pick;
+
+    const int b   = blockIdx.x;
+    const int tid = threadIdx.x;
+    if (p.skip_decode && p.skip_decode[b]) return;
+    const int V = p.vocab_size;
+    if (p.finished && p.finished[b]) {
+        // topk_stage2_sampling: a finished sequence keeps emitting its end id and nothing else changes
+        if (tid == 0) p.ids[b] = p.end_ids[b];
+        return;
+    }
+    penalised_row(p, b, s_row, s_seen);
 
     int k = p.top_ks ? p.top_ks[b] : p.max_top_k;
     k     = max(1, min(k, min(kSampleMaxK, V)));
@@ -163,6 +172,197 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(tm_sampling
     }
 }
 
+// ---- top-p sampling over the whole vocabulary -------------------------------------------------------------------
+// The reference softmaxes the row, sorts all of it by probability (cub segmented radix sort, descending, equal values
+// in token order) and walks the sorted row until the running sum reaches u * top_p; when the largest probability alone
+// reaches top_p it takes that token without sorting (sampling_topp_kernels.cu:802-858, 878-1004, 1295-1346).  Here
+// nothing is sorted: the probability at which the walk stops is found by a radix select over the bits of the
+// probabilities, eight bits a pass, with the probability mass of every bucket in 2^-40 fixed point (integer sums:
+// the same answer in any order of arrival).  What is left is which of the tokens with exactly that probability, in
+// token order.
+constexpr float kMassScale = 1099511627776.f;  // 2^40
+
+__device__ __forceinline__ float block_reduce_max(float v, float* s_red)
+{
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();  // s_red may still be read from an earlier reduction
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = s_red[0];
+    for (int w = 1; w < kSampleThreads / 32; ++w) r = fmaxf(r, s_red[w]);
+    return r;
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* s_red)
+{
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int w = 0; w < kSampleThreads / 32; ++w) r += s_red[w];  // fixed order: every thread gets the same sum
+    return r;
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_topp_kernel(tm_sampling_params p)
+{
+    extern __shared__ float s_dyn[];
+    float*              s_row  = s_dyn;                                              // [vocab] logits, then probabilities
+    unsigned*           s_seen = reinterpret_cast<unsigned*>(s_row + p.vocab_size);  // bitmap of tokens to penalise
+    unsigned long long* s_hist = reinterpret_cast<unsigned long long*>(
+        (reinterpret_cast<uintptr_t>(s_seen + (p.vocab_size + 31) / 32) + 7) & ~uintptr_t(7));  // [256] mass per bucket
+    __shared__ float              s_red[kSampleThreads / 32];
+    __shared__ int                s_cnt[kSampleThreads / 32];
+    __shared__ unsigned           s_prefix;   // bits of the stopping probability found so far
+    __shared__ unsigned long long s_above;    // mass of everything above the buckets still in play
+    __shared__ int                s_found;    // 0: the whole row is lighter than the target
+    __shared__ float              s_u;
+
+    const int b   = blockIdx.x;
+    const int tid = threadIdx.x;
+    if (p.skip_decode && p.skip_decode[b]) return;
+    const int V = p.vocab_size;
+    // topp_sampling draws before it looks at anything else, finished sequences included
+    if (tid == 0) s_u = p.uniforms ? p.uniforms[b] : curand_uniform(reinterpret_cast<curandState_t*>(p.rng_states) + b);
+    if (p.finished && p.finished[b]) {
+        // addBiasSoftMax turns the row of a finished sequence into a one-hot of its end id: that id comes out, the
+        // length stays and the sequence stays finished (topp_sampling's bookkeeping, sampling_topp_kernels.cu:996-1000)
+        if (tid == 0) p.ids[b] = p.end_ids[b];
+        return;
+    }
+    penalised_row(p, b, s_row, s_seen);
+
+    // softmax as addBiasSoftMax: exp(l - max) / (sum + 1e-6)
+    float m = -FLT_MAX;
+    for (int v = tid; v < V; v += kSampleThreads) m = fmaxf(m, s_row[v]);
+    m = block_reduce_max(m, s_red);
+    float part = 0.f;
+    for (int v = tid; v < V; v += kSampleThreads) {
+        const float e = __expf(s_row[v] - m);
+        s_row[v]      = e;
+        part += e;
+    }
+    const float denom = block_reduce_sum(part, s_red) + 1e-6f;
+    Best        top{-1.f, 0x7fffffff};
+    for (int v = tid; v < V; v += kSampleThreads) {
+        const float q = s_row[v] / denom;
+        s_row[v]      = q;
+        top           = better(top, Best{q, v});
+    }
+    // the most probable token (the lowest id among equals)
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, top.v, o), __shfl_xor_sync(0xffffffffu, top.i, o)};
+        top = better(top, other);
+    }
+    __shared__ Best s_top[kSampleThreads / 32];
+    if ((tid & 31) == 0) s_top[tid >> 5] = top;
+    __syncthreads();
+    top = s_top[0];
+    for (int w = 1; w < kSampleThreads / 32; ++w) top = better(top, s_top[w]);
+
+    const float top_p = p.top_ps ? p.top_ps[b] : p.top_p;
+    int         pick  = top.i;
+    if (!(top.v >= top_p)) {
+        // target of the walk, in fixed point (at least one unit: a bucket without mass never stops the walk)
+        const float              r_f    = s_u * top_p;
+        const unsigned long long target = max(1ull, (unsigned long long)(r_f * kMassScale));
+        if (tid == 0) {
+            s_prefix = 0u;
+            s_above  = 0ull;
+            s_found  = 1;
+        }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = tid; i < 256; i += kSampleThreads) s_hist[i] = 0ull;
+            __syncthreads();
+            const unsigned prefix = s_prefix;
+            for (int v = tid; v < V; v += kSampleThreads) {
+                const unsigned key = __float_as_uint(s_row[v]);
+                if (pass == 0 || (key >> (shift + 8)) == prefix) {
+                    const unsigned long long w = (unsigned long long)(s_row[v] * kMassScale);
+                    if (w) atomicAdd(&s_hist[(key >> shift) & 255u], w);
+                }
+            }
+            __syncthreads();
+            if (tid == 0 && s_found) {
+                unsigned long long acc = s_above;
+                int                d   = 255;
+                for (; d >= 0; --d) {
+                    const unsigned long long h = s_hist[d];
+                    if (h && acc + h >= target) break;
+                    acc += h;
+                }
+                if (d < 0) {
+                    s_found = 0;  // only in the first pass: the row sums to less than the target
+                }
+                else {
+                    s_prefix = (prefix << 8) | (unsigned)d;
+                    s_above  = acc;
+                }
+            }
+            __syncthreads();
+        }
+        if (s_found) {
+            // all tokens whose probability has exactly these bits weigh the same; the walk passes them in token order
+            const unsigned           key  = s_prefix;
+            const unsigned long long w    = (unsigned long long)(__uint_as_float(key) * kMassScale);
+            const unsigned long long need = target > s_above ? target - s_above : 1ull;
+            const long long          nth  = (long long)((need + w - 1) / w);  // w > 0: its bucket had mass
+            const int chunk = (V + kSampleThreads - 1) / kSampleThreads;
+            const int v0 = tid * chunk, v1 = min(V, v0 + chunk);
+            int       mine = 0;
+            for (int v = v0; v < v1; ++v) mine += __float_as_uint(s_row[v]) == key;
+            // exclusive prefix of the counts over the threads (thread order = token order)
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((tid & 31) >= o) incl += t;
+            }
+            if ((tid & 31) == 31) s_cnt[tid >> 5] = incl;
+            __syncthreads();
+            int before = incl - mine;
+            for (int w2 = 0; w2 < (tid >> 5); ++w2) before += s_cnt[w2];
+            int total = 0;
+            for (int w2 = 0; w2 < kSampleThreads / 32; ++w2) total += s_cnt[w2];
+            const long long want = nth < 1 ? 1 : (nth > total ? total : nth);  // 1-based rank among the equals
+            __shared__ int s_pick_id;
+            if (tid == 0) s_pick_id = top.i;
+            __syncthreads();
+            if (want > before && want <= before + mine) {
+                int seen = before;
+                for (int v = v0; v < v1; ++v) {
+                    if (__float_as_uint(s_row[v]) == key && ++seen == want) {
+                        s_pick_id = v;
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            pick = s_pick_id;
+        }
+    }
+    if (tid == 0) {
+        p.ids[b] = pick;
+        if (p.sequence_lengths_out && p.finished) {
+            p.sequence_lengths_out[b] += 1;
+            p.finished[b] = pick == p.end_ids[b] ? 1 : 0;
+        }
+    }
+}
+
+// invokeComputeToppDecay (sampling_topp_kernels.cu:1381-1426): top_p = token == reset id ? initial : max(top_p * decay, min)
+__global__ void topp_decay_kernel(float* top_p, const float* initial, const int* ids, const float* decay, const float* top_p_min,
+                                  const int* reset_ids, int n)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    top_p[i] = ids[i] == reset_ids[i] ? initial[i] : fmaxf(top_p[i] * decay[i], top_p_min[i]);
+}
+
 __global__ void rng_init_kernel(curandState_t* states, int n, const unsigned long long* seeds, unsigned long long seed)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,7 +374,9 @@ __global__ void rng_init_kernel(curandState_t* states, int n, const unsigned lon
 cudaError_t sampling_prepare(int max_smem)
 {
     // the kernel also has a few static words: leave room for them
-    return cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 1024);
+    cudaError_t e = cudaFuncSetAttribute(sample_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 1024);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(sample_topp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 1024);
 }
 
 }  // namespace tmb
@@ -206,6 +408,32 @@ extern "C" int tm_sample_topk(tm_handle* h, const tm_sampling_params* params, vo
     if (smem > (size_t)h->max_smem - 1024) return TM_ERR_UNSUPPORTED;  // the row must fit shared memory (about 55 000 tokens)
     sample_topk_kernel<<<p.batch_size, kSampleThreads, smem, (cudaStream_t)stream>>>(p);
     ++h->launches;
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+extern "C" int tm_sample_topp(tm_handle* h, const tm_sampling_params* params, void* stream)
+{
+    if (!h || !params) return TM_ERR_INVALID_ARG;
+    const tm_sampling_params& p = *params;
+    if (!p.logits || !p.ids || p.batch_size <= 0 || p.vocab_size <= 0 || p.ld < p.vocab_size) return TM_ERR_INVALID_ARG;
+    if (!p.uniforms && !p.rng_states) return TM_ERR_INVALID_ARG;
+    if ((p.finished || p.min_lengths) && !p.end_ids) return TM_ERR_INVALID_ARG;
+    if (!p.top_ps && !(p.top_p > 0.f && p.top_p <= 1.f)) return TM_ERR_INVALID_ARG;
+    const size_t smem = (size_t)p.vocab_size * 4 + (size_t)((p.vocab_size + 31) / 32) * 4 + 8 + 256 * 8;
+    if (smem > (size_t)h->max_smem - 1024) return TM_ERR_UNSUPPORTED;
+    sample_topp_kernel<<<p.batch_size, kSampleThreads, smem, (cudaStream_t)stream>>>(p);
+    ++h->launches;
+    return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
+}
+
+extern "C" int tm_top_p_decay(float* runtime_top_p, const float* initial_top_p, const int* output_ids, const float* top_p_decay,
+                              const float* top_p_min, const int* top_p_reset_ids, int batch_size, void* stream)
+{
+    if (!runtime_top_p || !initial_top_p || !output_ids || !top_p_decay || !top_p_min || !top_p_reset_ids || batch_size <= 0) {
+        return TM_ERR_INVALID_ARG;
+    }
+    topp_decay_kernel<<<(batch_size + 255) / 256, 256, 0, (cudaStream_t)stream>>>(runtime_top_p, initial_top_p, output_ids, top_p_decay,
+                                                                                   top_p_min, top_p_reset_ids, batch_size);
     return cudaGetLastError() == cudaSuccess ? TM_OK : TM_ERR_CUDA;
 }
 

@@ -182,6 +182,8 @@ SIGNATURES = {
     "tm_stop_words_criterion": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "tm_length_criterion": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "tm_sample_topk": (_i, [_vp, C.POINTER(TmSamplingParams), _vp]),
+    "tm_sample_topp": (_i, [_vp, C.POINTER(TmSamplingParams), _vp]),
+    "tm_top_p_decay": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tm_lm_head_f16": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "tm_mmha_decode": (_i, [_vp, C.POINTER(TmMmhaParams), _vp]),
     "tm_comm_unique_id": (_i, [_vp]),

@@ -30,6 +30,7 @@ REFERENCE_SOURCES = [
     "src/turbomind/models/llama/LlamaCacheManager.cc",
     "src/turbomind/kernels/sampling_penalty_kernels.cu",
     "src/turbomind/kernels/sampling_topk_kernels.cu",
+    "src/turbomind/kernels/sampling_topp_kernels.cu",
     "src/turbomind/kernels/ban_bad_words.cu",
     "src/turbomind/kernels/stop_criteria_kernels.cu",
     "src/turbomind/utils/logger.cc",

@@ -431,6 +431,41 @@ REF_API int ref_batch_topk_sampling(void* workspace, size_t* workspace_bytes, co
     return workspace ? finish(st) : 0;
 }
 
+// ---- top-p sampling as TopPSamplingLayer<float>::runSampling drives it (src/turbomind/layers/sampling_layers/
+// ---- TopPSamplingLayer.cu:254-346): invokeTopPInitialize, invokeAddBiasSoftMax (the logits become probabilities in
+// ---- place), invokeBatchTopPSampling, invokeComputeToppDecay.  Scratch is allocated and freed here.
+#include "src/turbomind/kernels/sampling_topp_kernels.h"
+
+REF_API int ref_batch_topp_sampling(float* logits, int* ids, int* sequence_length, bool* finished, void* curand_states, float max_top_p,
+                                    const float* top_ps, int vocab, const int* end_ids, int batch, const bool* skip_decode, cudaStream_t st)
+{
+    int *id_vals = nullptr, *offsets = nullptr, *begin_offsets = nullptr;
+    if (cudaMalloc(&id_vals, sizeof(int) * (size_t)batch * vocab) != cudaSuccess) return -2;
+    if (cudaMalloc(&offsets, sizeof(int) * (batch + 1)) != cudaSuccess) return -2;
+    if (cudaMalloc(&begin_offsets, sizeof(int) * (batch + 1)) != cudaSuccess) return -2;
+    turbomind::invokeTopPInitialize(id_vals, offsets, begin_offsets, (size_t)batch, vocab, st);
+    turbomind::invokeAddBiasSoftMax(logits, (float*)nullptr, end_ids, finished, batch, vocab, vocab, st);
+    size_t ws = 0, cub = 0;
+    turbomind::invokeBatchTopPSampling<float>(nullptr, ws, cub, ids, sequence_length, finished, nullptr, nullptr, logits, id_vals, offsets,
+                                              begin_offsets, (curandState_t*)curand_states, batch, (size_t)vocab, end_ids, max_top_p, top_ps,
+                                              st, nullptr, skip_decode);
+    void* work = nullptr;
+    if (cudaMalloc(&work, ws) != cudaSuccess) return -2;
+    turbomind::invokeBatchTopPSampling<float>(work, ws, cub, ids, sequence_length, finished, nullptr, nullptr, logits, id_vals, offsets,
+                                              begin_offsets, (curandState_t*)curand_states, batch, (size_t)vocab, end_ids, max_top_p, top_ps,
+                                              st, nullptr, skip_decode);
+    const int rc = finish(st);
+    cudaFree(work), cudaFree(id_vals), cudaFree(offsets), cudaFree(begin_offsets);
+    return rc;
+}
+
+REF_API int ref_compute_topp_decay(float* runtime_top_p, const float* initial_top_p, const int* output_ids, const float* decay,
+                                   const float* top_p_min, const int* reset_ids, int batch, cudaStream_t st)
+{
+    turbomind::invokeComputeToppDecay(runtime_top_p, initial_top_p, output_ids, decay, top_p_min, reset_ids, batch, st);
+    return finish(st);
+}
+
 // ---- word lists and stopping: the reference's kernels as DynamicDecodeLayer::forward calls them (beam width 1)
 #include "src/turbomind/kernels/ban_bad_words.h"
 #include "src/turbomind/kernels/stop_criteria_kernels.h"

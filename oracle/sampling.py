@@ -11,6 +11,10 @@ Follows, in the order of ``BaseSamplingLayer<T>::forward``
 * ``topk_stage1`` + ``topk_stage2_sampling`` (src/turbomind/kernels/sampling_topk_kernels.cu:125-312): the k largest
   logits in descending order, ``e_i = exp(l_i - l_max)``, target ``u * top_p * sum(e)``, first i whose running sum
   reaches the target (the last one otherwise).
+* ``addBiasSoftMax`` + ``topp_beam_topk_kernel`` + segmented sort + ``topp_sampling``
+  (src/turbomind/kernels/sampling_topp_kernels.cu:802-1004, 1295-1346) for the sequences without a top-k:
+  probabilities ``exp(l - max) / (sum + 1e-6)``; the most probable token at once when it alone reaches ``top_p``;
+  otherwise the first token, by descending probability, at which the running sum reaches ``u * top_p``.
 
 Pinned on a GPU against those kernels compiled unmodified into ``oracle/_ref`` (tests/test_gpu_sampling.py), where the
 uniform numbers come from the same curand states.  Here the uniform number is an input.
@@ -76,6 +80,46 @@ def sample(logits, top_ks, top_ps, uniforms, finished=None, end_ids=None):
             continue
         ids[b], margins[b] = topk_sample(logits[b], top_ks[b], top_ps[b], uniforms[b])
     return ids, margins
+
+
+def softmax_topp(logits):
+    """addBiasSoftMax for a sequence that is not finished (src/turbomind/kernels/sampling_topp_kernels.cu:1295-1346):
+    exp(l - max) / (sum + 1e-6), float32."""
+    x = np.asarray(logits, dtype=np.float32)
+    e = np.exp((x - x.max()).astype(np.float32)).astype(np.float32)
+    # The kernels add per-thread partial sums and then a tree (blockReduceSum), which stays within an ulp or two of the
+    # exact sum; a sequential float32 loop over 32 000 terms does not (1e-4 off on rows of equal values).  The exact sum
+    # rounded to float stands for the kernels' order; the tests allow a margin for the last ulp.
+    total = np.float32(e.astype(np.float64).sum())
+    return (e / np.float32(total + np.float32(1e-6))).astype(np.float32)
+
+
+def topp_sample(logits, top_p, u):
+    """One row of invokeBatchTopPSampling (sampling_topp_kernels.cu:802-858, 878-1004).  Returns (token id, margin):
+    margin is how far the decision was from flipping (distance of u * top_p from the chosen interval's ends, or of the
+    largest probability from top_p), so that a test can leave out draws that float rounding decides."""
+    p = softmax_topp(logits)
+    order = np.lexsort((np.arange(p.shape[0]), -p.astype(np.float64)))      # descending, equal values in token order
+    top = float(p[order[0]])
+    if top >= np.float32(top_p):                                            # topp_beam_topk_kernel: no sort, no walk
+        return int(order[0]), abs(top - float(np.float32(top_p)))
+    gate = abs(top - float(np.float32(top_p)))
+    r = float(np.float32(np.float32(u) * np.float32(top_p)))
+    # The running sum is kept in double here.  The reference's block scan rounds it in float, in an order no loop
+    # reproduces (an error of a few 1e-6 after thousands of terms): the margin is what a test must leave for that.
+    run = 0.0
+    for i in order:
+        lo, run = run, run + float(p[i])
+        if r <= run:
+            return int(i), min(gate, abs(r - lo), abs(run - r))
+    return int(order[0]), min(gate, abs(r - run))                           # the row sums to less than the target
+
+
+def top_p_decay(top_p, initial, ids, decay, top_p_min, reset_ids):
+    """invokeComputeToppDecay (sampling_topp_kernels.cu:1381-1426)."""
+    top_p, initial = np.asarray(top_p, np.float32), np.asarray(initial, np.float32)
+    stepped = np.maximum((top_p * np.asarray(decay, np.float32)).astype(np.float32), np.asarray(top_p_min, np.float32))
+    return np.where(np.asarray(ids) == np.asarray(reset_ids), initial, stepped).astype(np.float32)
 
 
 def _items(words):

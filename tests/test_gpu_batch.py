@@ -116,3 +116,26 @@ def test_sampling_depends_on_the_seed_only():
     alone, _ = _run(model, 1, [(9, prompt, 12)], llama)
     assert alone[9][0] == out[4]
     model.close()
+
+
+def test_requests_with_only_a_top_p_are_drawn_over_the_whole_vocabulary():
+    """A batch that mixes the reference's two sampling layers: top-k requests, top-p-only requests, a greedy one.  Every
+    kind depends on its own seed only, the greedy neighbour is untouched, and a tiny top_p is greedy."""
+    from lmdeploy_b200 import llama
+    model, _, _ = build(False)
+    _, prompt, _ = _requests()[2]
+    b = llama.Batch(model, 4)          # six requests for four slots: two wait for a free slot
+    assert b.submit(1, prompt, 10, top_p=0.95, temperature=2.0, random_seed=5, ignore_eos=True) == 0
+    assert b.submit(2, prompt, 10, top_p=0.95, temperature=2.0, random_seed=5, ignore_eos=True) == 0
+    assert b.submit(3, prompt, 10, top_p=0.95, temperature=2.0, random_seed=6, ignore_eos=True) == 0
+    assert b.submit(4, prompt, 10, top_k=30, temperature=2.0, random_seed=5, ignore_eos=True) == 0
+    assert b.submit(5, prompt, 10, top_p=1e-4, random_seed=9, ignore_eos=True) == 0      # the top token alone reaches it
+    assert b.submit(6, prompt, 10, ignore_eos=True) == 0
+    b.run(max_rounds=100)
+    out = {sid: b.output(sid)[0] for sid in range(1, 7)}
+    b.close()
+    assert out[1] == out[2] and out[1] != out[3]
+    assert out[5] == out[6]
+    alone, _ = _run(model, 1, [(9, prompt, 10)], llama)
+    assert alone[9][0] == out[6]
+    model.close()

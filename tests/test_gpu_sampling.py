@@ -1,4 +1,4 @@
-"""GPU: token sampling (tm_sample_topk) and the lm-head kernel (tm_lm_head_f16).
+"""GPU: token sampling (tm_sample_topk, tm_sample_topp) and the lm-head kernel (tm_lm_head_f16).
 
 Sampling is checked two ways: against oracle/sampling.py with caller-supplied uniform numbers (draws that sit on an
 interval boundary are left out), and step by step against the reference's own penalty and top-k sampling kernels
@@ -140,6 +140,135 @@ def test_sampling_matches_reference_kernels_over_steps():
         assert torch.equal(fin_a.bool(), fin_b) and torch.equal(len_a, len_b)
         was_finished = fin_b.clone()
     assert bool(fin_b[3])     # the forced end id was taken
+
+
+@pytest.mark.parametrize("B,V,ld", [(9, 32000, 32000), (4, 1000, 1024), (64, 32000, 32000), (2, 50001, 50008)])
+def test_topp_sampling_matches_oracle(B, V, ld):
+    """tm_sample_topp against oracle/sampling.py with caller-supplied uniform numbers: rows that stop at the most probable
+    token, rows that walk, a row of few distinct values (equal probabilities are passed in token order), a finished row,
+    a skipped row."""
+    from lmdeploy_b200 import lib as l
+    rng = np.random.default_rng(B * 77 + V)
+    h = l.default_handle(torch.cuda.current_device())
+    x = (rng.standard_normal((B, ld)) * 3).astype(np.float32)
+    x[1, :V] = rng.integers(0, 4, V).astype(np.float32)          # four distinct probabilities, thousands of equals
+    step, max_in = 10, 5
+    out_ids = rng.integers(0, V, size=(step, B)).astype(np.int32)
+    in_len = rng.integers(1, max_in + 1, size=B).astype(np.int32)
+    temps = rng.uniform(0.5, 1.5, B).astype(np.float32)
+    reps = rng.uniform(1.0, 1.2, B).astype(np.float32)
+    temps[1], reps[1] = 1.0, 1.0
+    end_ids = rng.integers(0, V, B).astype(np.int32)
+    top_ps = rng.uniform(0.02, 1.0, B).astype(np.float32)
+    top_ps[0], top_ps[1] = 1e-3, 0.9                             # row 0 certainly stops at its most probable token
+    us = rng.uniform(1e-3, 1.0, B).astype(np.float32)
+    finished = np.zeros(B, np.uint8)
+    skip = np.zeros(B, np.uint8)
+    if B > 2:
+        finished[B // 2] = 1
+        skip[B - 1] = 1
+    d = {k: torch.from_numpy(v).cuda() for k, v in dict(x=x, out_ids=out_ids, in_len=in_len, temps=temps, reps=reps, end_ids=end_ids,
+                                                         top_ps=top_ps, us=us, finished=finished, skip=skip).items()}
+    ids = torch.full((B,), -7, dtype=torch.int32, device="cuda")
+    p = _params(l, d["x"], ids, vocab=V, output_ids=d["out_ids"], step=step, input_lengths=d["in_len"], max_input_length=max_in,
+                temperatures=d["temps"], repetition_penalties=d["reps"], end_ids=d["end_ids"], top_ps=d["top_ps"], uniforms=d["us"],
+                finished=d["finished"], skip_decode=d["skip"])
+    assert l.lib.tm_sample_topp(h.ptr, C.byref(p), _stream()) == l.TM_OK
+    torch.cuda.synchronize()
+    want_x = osamp.apply_penalties(x[:, :V], temps, reps, out_ids, in_len, max_in)
+    got_x, got = d["x"].cpu().numpy(), ids.cpu().numpy()
+    live = (finished == 0) & (skip == 0)
+    np.testing.assert_allclose(got_x[live][:, :V], want_x[live], rtol=2e-6, atol=0)
+    np.testing.assert_array_equal(got_x[~live], x[~live])
+    assert (got[skip == 1] == -7).all() and (got[finished == 1] == end_ids[finished == 1]).all()
+    n_sure, n_top, n_walk = 0, 0, 0
+    for b in np.nonzero(live)[0]:
+        want, margin = osamp.topp_sample(got_x[b, :V], top_ps[b], us[b])      # from the logits the kernel left behind
+        top = float(osamp.softmax_topp(got_x[b, :V]).max())
+        n_top += top >= top_ps[b]
+        n_walk += top < top_ps[b]
+        if margin > 2e-6:
+            n_sure += 1
+            assert got[b] == want, f"row {b}: {got[b]} vs {want} (margin {margin:.2e}, top_p {top_ps[b]:.3f}, u {us[b]:.3f})"
+    assert n_sure >= live.sum() - 1 and n_top >= 1 and n_walk >= 1
+
+
+def test_topp_sampling_matches_reference_kernels_over_steps():
+    """tm_sample_topp step by step against the reference's penalty kernels, softmax, segmented sort and topp_sampling
+    (compiled unmodified into oracle/_ref), both sides drawing from curand states seeded alike; odd rows belong to the
+    top-k layer and are skipped by both.  Then the top_p decay."""
+    from lmdeploy_b200 import lib as l
+    if not os.path.exists(_REF):
+        pytest.skip("oracle/_ref/libtm_ref.so not built")
+    ref = C.CDLL(_REF)
+    if not hasattr(ref, "ref_batch_topp_sampling"):
+        pytest.skip("oracle/_ref/libtm_ref.so predates the top-p entry layer")
+    B, V, steps, max_in = 16, 32000, 6, 4
+    h = l.default_handle(torch.cuda.current_device())
+    g = torch.Generator(device="cuda").manual_seed(23)
+    seeds = torch.arange(500, 500 + B, dtype=torch.int64, device="cuda")
+    nbytes = int(l.lib.tm_sampling_rng_state_bytes())
+    st_a = torch.zeros(B * nbytes, dtype=torch.uint8, device="cuda")
+    st_b = torch.zeros_like(st_a)
+    vp = C.c_void_p
+    assert l.lib.tm_sampling_rng_init(st_a.data_ptr(), B, seeds.data_ptr(), 0, _stream()) == l.TM_OK
+    assert ref.ref_curand_batch_init(vp(st_b.data_ptr()), B, vp(seeds.data_ptr()), _stream()) == 0
+    temps = (torch.rand(B, device="cuda", generator=g) + 0.5).float()
+    reps = (torch.rand(B, device="cuda", generator=g) * 0.2 + 1.0).float()
+    top_ps = (torch.rand(B, device="cuda", generator=g) * 0.9 + 0.1).float()
+    top_ps[0] = 0.01                                   # stops at the most probable token every step
+    top_ps_b = top_ps.clone()
+    initial = top_ps.clone()
+    decay = torch.full((B,), 0.9, device="cuda")
+    p_min = torch.full((B,), 0.2, device="cuda")
+    reset = torch.full((B,), -1, dtype=torch.int32, device="cuda")
+    skip = torch.zeros(B, dtype=torch.uint8, device="cuda")
+    skip[1::2] = 1
+    end_ids = torch.full((B,), 2, dtype=torch.int32, device="cuda")
+    min_len = torch.full((B,), 3, dtype=torch.int32, device="cuda")
+    in_len = torch.randint(1, max_in + 1, (B,), device="cuda", generator=g, dtype=torch.int32)
+    hist = torch.randint(3, V, (max_in + steps, B), device="cuda", generator=g, dtype=torch.int32)
+    hist_b = hist.clone()
+    fin_a = torch.zeros(B, dtype=torch.uint8, device="cuda")
+    fin_b = torch.zeros(B, dtype=torch.bool, device="cuda")
+    len_a = torch.full((B,), max_in - 1, dtype=torch.int32, device="cuda")
+    len_b = len_a.clone()
+    ref.ref_batch_topp_sampling.argtypes = [vp, vp, vp, vp, vp, C.c_float, vp, C.c_int, vp, C.c_int, vp, vp]
+    ref.ref_compute_topp_decay.argtypes = [vp, vp, vp, vp, vp, vp, C.c_int, vp]
+    for s in range(steps):
+        step = max_in + s
+        logits = torch.randn(B, V, device="cuda", generator=g) * 4
+        if s in (3, 4):
+            logits[4, 2] = 100.0                       # sequence 4 draws its end id once the minimum length allows it
+        if s == 1:
+            reset[6] = -1
+        xa, xb = logits.clone(), logits.clone()
+        p = _params(l, xa, hist[step], output_ids=hist, step=step, input_lengths=in_len, max_input_length=max_in, temperatures=temps,
+                    repetition_penalties=reps, min_lengths=min_len, sequence_lengths=len_a, end_ids=end_ids, top_ps=top_ps,
+                    rng_states=st_a, finished=fin_a, sequence_lengths_out=len_a, skip_decode=skip)
+        assert l.lib.tm_sample_topp(h.ptr, C.byref(p), _stream()) == l.TM_OK
+        assert ref.ref_sampling_penalties(vp(xb.data_ptr()), B, V, vp(temps.data_ptr()), vp(reps.data_ptr()), vp(hist_b.data_ptr()),
+                                          vp(in_len.data_ptr()), max_in, step, vp(min_len.data_ptr()), vp(end_ids.data_ptr()),
+                                          vp(len_b.data_ptr()), _stream()) == 0
+        assert ref.ref_batch_topp_sampling(xb.data_ptr(), hist_b[step].data_ptr(), len_b.data_ptr(), fin_b.data_ptr(), st_b.data_ptr(),
+                                           float(top_ps_b.max()), top_ps_b.data_ptr(), V, end_ids.data_ptr(), B,
+                                           skip.view(torch.bool).data_ptr(), _stream().value) == 0
+        torch.cuda.synchronize()
+        mine = skip == 0
+        assert torch.equal(hist[step][mine], hist_b[step][mine]), f"step {s}: {hist[step].tolist()} vs {hist_b[step].tolist()}"
+        assert torch.equal(fin_a.bool()[mine], fin_b[mine]) and torch.equal(len_a[mine], len_b[mine])
+        # the layer's decay after the draw (reset id of sequence 6 = what it just drew, once)
+        if s == 2:
+            reset[6] = hist[step][6]
+        assert l.lib.tm_top_p_decay(top_ps.data_ptr(), initial.data_ptr(), hist[step].data_ptr(), decay.data_ptr(), p_min.data_ptr(),
+                                    reset.data_ptr(), B, _stream()) == l.TM_OK
+        assert ref.ref_compute_topp_decay(top_ps_b.data_ptr(), initial.data_ptr(), hist_b[step].data_ptr(), decay.data_ptr(),
+                                          p_min.data_ptr(), reset.data_ptr(), B, _stream().value) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(top_ps[mine], top_ps_b[mine])
+        if s == 2:
+            assert float(top_ps[6]) == float(initial[6])
+    assert bool(fin_b[4]) and float(top_ps[0]) == float(np.float32(0.2))
 
 
 @pytest.mark.parametrize("T,V,H,ld", [(1, 32000, 4096, 32000), (64, 32000, 4096, 32000), (5, 1000, 128, 1008), (128, 4000, 8192, 4000),

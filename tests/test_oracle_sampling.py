@@ -54,3 +54,25 @@ def test_word_lists_known_answers():
     assert list(f) == [True, True]                           # 5 ; 9, 9, 4
     f, n = osamp.length_criterion([False, True, False], [5, 9, 3], 4)
     assert list(f) == [False, True, True] and n == 2
+
+
+def test_topp_sample_known_answers():
+    # probabilities 0.5, 0.25, 0.125, 0.125 (up to the 1e-6 in the denominator): logits = log2 scaled
+    x = (np.log(np.array([0.125, 0.5, 0.125, 0.25])) + 3.0).astype(np.float32)
+    assert osamp.topp_sample(x, 0.4, 0.9)[0] == 1               # the top token alone reaches top_p: no walk
+    assert osamp.topp_sample(x, 0.5 - 1e-3, 0.01)[0] == 1
+    # walk: target = u * top_p against the running sums 0.5, 0.75, 0.875, 1.0 in the order 1, 3, 0, 2
+    assert osamp.topp_sample(x, 0.8, 0.5)[0] == 1               # 0.40
+    assert osamp.topp_sample(x, 0.8, 0.8)[0] == 3               # 0.64
+    assert osamp.topp_sample(x, 1.0, 0.8)[0] == 0               # 0.80: equal probabilities in token order
+    assert osamp.topp_sample(x, 1.0, 0.9)[0] == 2               # 0.90
+    assert osamp.topp_sample(x, 1.0, 1.0)[0] == 1               # the row sums to just under 1: falls back to the top token
+    tok, margin = osamp.topp_sample(x, 0.8, 0.8)
+    assert abs(margin - 0.11) < 1e-3                            # 0.64 is 0.14 above 0.5 and 0.11 below 0.75
+    p = osamp.softmax_topp(x)
+    assert abs(float(p.sum()) - 1.0) < 1e-5 and p.dtype == np.float32
+
+
+def test_top_p_decay_known_answers():
+    out = osamp.top_p_decay([0.8, 0.8, 0.05], [0.9, 0.9, 0.9], [7, 3, 1], [0.5, 0.5, 0.5], [0.1, 0.1, 0.1], [3, 3, -1])
+    np.testing.assert_allclose(out, [0.4, 0.9, 0.1], rtol=1e-6)
