@@ -27,6 +27,6 @@ Pin status
   Not pinned: ``oracle.decoder`` (the sequencing of the pinned parts).
 * ``oracle.cache_manager`` is pinned against the reference's own ``LlamaCacheManager.cc`` compiled into
   ``oracle/_ref`` (side by side on a GPU, and through the committed trace ``tests/golden/ref_cache_manager_trace.npz``
-  on the CPU); ``oracle.sampling`` against the reference's penalty and top-k sampling kernels in the same library
+  on the CPU); ``oracle.sampling`` against the reference's penalty, top-k and top-p sampling kernels in the same library
   (``tests/test_gpu_sampling.py``), with known answers on the CPU (``tests/test_oracle_sampling.py``).
 """
