@@ -616,7 +616,9 @@ typedef struct tm_request {
     unsigned long long random_seed;
     int                ignore_eos;
     const int*         stop_ids;           /* host memory, copied: drawing one of these tokens ends the request too (the   */
-    int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:514-515) */
+    int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:512-513) */
+    const int*         bad_ids;            /* host memory, copied: tokens the request never draws (single-token bad words,    */
+    int                bad_count;          /* at most 32; their logits are set to -inf before every draw)                     */
 } tm_request;
 enum { TM_REQUEST_QUEUED = 0, TM_REQUEST_RUNNING = 1, TM_REQUEST_FINISHED = 2, TM_REQUEST_FAILED = 3 };
 TM_API int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager* cache, int max_batch_size, int session_len,

@@ -24,9 +24,12 @@
 namespace tmb {
 namespace {
 
+constexpr int kMaxBadWords = 32;  // banned tokens per request (LlamaBatch.h:132 keeps 32 ints per list)
+
 struct Slot {
     tm_request        req{};
     std::vector<int>  stop_ids;      // tokens that end the request besides the end id
+    std::vector<int>  bad_ids;       // tokens the request must never draw
     tm_cache_sequence seq{};
     std::vector<int>  tokens;        // everything the sequence holds: cached history, prompt, generated
     int               prompt_end = 0;  // tokens.size() when generation started
@@ -59,6 +62,7 @@ struct tm_batch {
     std::deque<tm_request>                       pending;
     std::deque<std::vector<int>>                 pending_ids;  // the prompt of pending[i]
     std::deque<std::vector<int>>                 pending_stop; // its stop tokens
+    std::deque<std::vector<int>>                 pending_bad;  // its banned tokens
     std::vector<tmb::Slot>                       slots;        // [0, active) are live
     int                                          active = 0;
     std::unordered_map<uint64_t, tmb::Result>    results;
@@ -69,6 +73,7 @@ struct tm_batch {
     int *  d_topk = nullptr, *d_hist_len = nullptr;
     float *d_logits = nullptr, *d_topp = nullptr, *d_temp = nullptr, *d_rep = nullptr;
     void*  d_rng = nullptr;
+    int*                d_bad  = nullptr;  // [max batch][2][kMaxBadWords]: the live requests' banned tokens as word lists
     unsigned char*      d_skip = nullptr;  // [2][max batch]: rows the top-k draw leaves alone | rows the top-p draw leaves alone
     unsigned long long* d_seed = nullptr;
     // prefill staging (grown on demand)
@@ -96,7 +101,7 @@ void batch_free(tm_batch* b)
 {
     void* ptrs[] = {b->d_k,    b->d_v,    b->d_len,  b->d_forced, b->d_out,    b->d_step,  b->d_ids,   b->d_hist, b->d_topk, b->d_hist_len,
                     b->d_logits, b->d_topp, b->d_temp, b->d_rep,    b->d_rng,    b->d_seed,  b->d_pf_ids, b->d_pf_cu, b->d_pf_hist, b->d_pf_ctx,
-                    b->d_pf_k, b->d_pf_v, b->d_skip};
+                    b->d_pf_k, b->d_pf_v, b->d_skip, b->d_bad};
     for (void* p : ptrs) {
         if (p) cudaFree(p);
     }
@@ -130,7 +135,7 @@ extern "C" int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager
               && dev_alloc(&b->d_hist, B * session_len) && dev_alloc(&b->d_topk, B) && dev_alloc(&b->d_hist_len, B)
               && dev_alloc(&b->d_logits, B * b->vocab) && dev_alloc(&b->d_topp, B) && dev_alloc(&b->d_temp, B) && dev_alloc(&b->d_rep, B)
               && dev_alloc(&b->d_seed, B) && dev_alloc(&b->d_pf_cu, B + 1) && dev_alloc(&b->d_pf_hist, B) && dev_alloc(&b->d_pf_ctx, B)
-              && dev_alloc(&b->d_pf_k, B) && dev_alloc(&b->d_pf_v, B) && dev_alloc(&b->d_skip, 2 * B);
+              && dev_alloc(&b->d_pf_k, B) && dev_alloc(&b->d_pf_v, B) && dev_alloc(&b->d_skip, 2 * B) && dev_alloc(&b->d_bad, B * 2 * kMaxBadWords);
     ok = ok && cudaMalloc(&b->d_rng, B * tm_sampling_rng_state_bytes()) == cudaSuccess;
     ok = ok && cudaMallocHost((void**)&b->h_ids, B * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(b->d_hist, 0, B * session_len * sizeof(int)) == cudaSuccess;
@@ -155,6 +160,7 @@ extern "C" int tm_batch_submit(tm_batch* b, const tm_request* r)
     if (!b || !r || r->input_length < 0 || (r->input_length > 0 && !r->input_ids) || r->request_output_len < 0) return TM_ERR_INVALID_ARG;
     if (r->top_k < 0 || r->top_k > 1024 || r->top_p < 0.f || r->top_p > 1.f) return TM_ERR_INVALID_ARG;
     if (r->stop_count < 0 || (r->stop_count > 0 && !r->stop_ids)) return TM_ERR_INVALID_ARG;
+    if (r->bad_count < 0 || r->bad_count > tmb::kMaxBadWords || (r->bad_count > 0 && !r->bad_ids)) return TM_ERR_INVALID_ARG;
     for (int i = 0; i < r->input_length; ++i) {
         if (r->input_ids[i] < 0 || r->input_ids[i] >= b->vocab) return TM_ERR_INVALID_ARG;
     }
@@ -166,8 +172,10 @@ extern "C" int tm_batch_submit(tm_batch* b, const tm_request* r)
     b->pending.push_back(*r);
     b->pending_ids.emplace_back(r->input_ids, r->input_ids + r->input_length);
     b->pending_stop.emplace_back(r->stop_ids, r->stop_ids + r->stop_count);
+    b->pending_bad.emplace_back(r->bad_ids, r->bad_ids + r->bad_count);
     b->pending.back().input_ids = nullptr;
     b->pending.back().stop_ids  = nullptr;
+    b->pending.back().bad_ids   = nullptr;
     b->results[r->id]           = Result{};
     return TM_OK;
 }
@@ -312,9 +320,11 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
         std::vector<int> ids = std::move(b->pending_ids.front());
         Slot sl{};
         sl.stop_ids = std::move(b->pending_stop.front());
+        sl.bad_ids  = std::move(b->pending_bad.front());
         b->pending.pop_front();
         b->pending_ids.pop_front();
         b->pending_stop.pop_front();
+        b->pending_bad.pop_front();
         sl.req = r;
         rc     = r.start_flag ? tm_cache_create(b->cache, r.id, s, &sl.seq) : tm_cache_fetch(b->cache, r.id, s, &sl.seq);
         if (rc != TM_OK) {
@@ -437,6 +447,23 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
     st.step             = b->d_step;
     st.logits_out       = b->d_logits;
     if ((rc = tm_llama_decode(b->model, &st, 1, use_graph, s)) != TM_OK) return rc;
+
+    // bad_words_list of the requests (DynamicDecodeLayer.cc:214-236): single tokens, as the reference's scheduler takes
+    // them, banned through the word-list kernel (an item of one token is banned whatever came before it)
+    size_t n_bad = 0;
+    for (int i = 0; i < B; ++i) n_bad = std::max(n_bad, b->slots[i].bad_ids.size());
+    if (n_bad > 0) {
+        std::vector<int> words((size_t)B * 2 * n_bad, -1);
+        for (int i = 0; i < B; ++i) {
+            const auto& bad = b->slots[i].bad_ids;
+            for (size_t k = 0; k < n_bad; ++k) {
+                words[((size_t)i * 2 + 0) * n_bad + k] = k < bad.size() ? bad[k] : 0;
+                words[((size_t)i * 2 + 1) * n_bad + k] = k < bad.size() ? (int)k + 1 : -1;
+            }
+        }
+        if (!up(b->d_bad, words.data(), words.size() * sizeof(int))) return TM_ERR_CUDA;
+        if ((rc = tm_ban_bad_words(b->d_logits, b->vocab, b->vocab, B, nullptr, 0, b->d_bad, (int)n_bad, 0, 0, s)) != TM_OK) return rc;
+    }
 
     tm_sampling_params sp{};
     sp.logits       = b->d_logits;

@@ -92,7 +92,8 @@ class TmRequest(C.Structure):
     _fields_ = [("id", C.c_uint64), ("start_flag", C.c_int), ("end_flag", C.c_int), ("input_ids", C.POINTER(C.c_int)),
                 ("input_length", C.c_int), ("request_output_len", C.c_int), ("top_k", C.c_int), ("top_p", C.c_float),
                 ("temperature", C.c_float), ("repetition_penalty", C.c_float), ("random_seed", C.c_ulonglong),
-                ("ignore_eos", C.c_int), ("stop_ids", C.POINTER(C.c_int)), ("stop_count", C.c_int)]
+                ("ignore_eos", C.c_int), ("stop_ids", C.POINTER(C.c_int)), ("stop_count", C.c_int),
+                ("bad_ids", C.POINTER(C.c_int)), ("bad_count", C.c_int)]
 
 
 class TmContextAttentionParams(C.Structure):

@@ -139,3 +139,24 @@ def test_requests_with_only_a_top_p_are_drawn_over_the_whole_vocabulary():
     alone, _ = _run(model, 1, [(9, prompt, 10)], llama)
     assert alone[9][0] == out[6]
     model.close()
+
+
+def test_banned_tokens_are_never_drawn():
+    """bad_words_list of a request (single tokens, as the reference's scheduler takes them): the greedy answer changes at
+    the first banned token and holds none of them; the neighbour without a list is untouched."""
+    from lmdeploy_b200 import llama
+    model, _, _ = build(False)
+    sid, prompt, _ = _requests()[1]
+    free, _ = _run(model, 2, [(sid, prompt, 8)], llama)
+    toks = free[sid][0]
+    banned = [toks[0], toks[3]]
+    b = llama.Batch(model, 3)
+    assert b.submit(1, prompt, 8, ignore_eos=True, bad_ids=banned) == 0
+    assert b.submit(2, prompt, 8, ignore_eos=True) == 0
+    assert b.submit(3, prompt, 8, ignore_eos=True, bad_ids=list(range(1, 40))) != 0      # more than 32 tokens
+    b.run(max_rounds=50)
+    got, other = b.output(1)[0], b.output(2)[0]
+    b.close()
+    assert other == toks
+    assert len(got) == 8 and got[0] != toks[0] and not set(got) & set(banned)
+    model.close()
