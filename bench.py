@@ -322,7 +322,7 @@ def run_gemm_workload(args, rank, world, device):
                    "l2": "inputs larger than L2: weights replicated beyond 2x L2, next replica each launch",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "kernel": ("reference gemm_s4_f16_nn" if reflib is not None else
-                                                "gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_small_kernel") + " (gate_up)",
+                                                "gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_cols_kernel" if T <= 8 else "gemm_s4_f16_small_kernel") + " (gate_up)",
                      "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
                      "algorithmic_bytes": dom["bytes"],
@@ -892,7 +892,8 @@ def run_decode_workload(args, rank, world, device, name):
                           "frac_of_hbm_peak": round(total_b / (ms_step * 1e-3) * 1e-9 / peaks["hbm_gbs"], 4)},
         "per_kernel_m1": {k: dict(v, frac=round(v["gbs"] / peaks["hbm_gbs"], 4), us_chained=m1c[k]["us"], gbs_chained=m1c[k]["gbs"],
                                   frac_chained=round(m1c[k]["gbs"] / peaks["hbm_gbs"], 4)) for k, v in m1.items()},
-        "per_kernel_m1_note": "gemm_s4_f16_small_kernel at 1 token on this model's weights (per-rank shapes); us / gbs / frac: launches "
+        "per_kernel_m1_note": "the 1-token GEMM on this model's weights (per-rank shapes; gemm_s4_f16_cols_kernel where the weight has a "
+                              "64-column strip per SM: qkv and gate_up, gemm_s4_f16_small_kernel otherwise); us / gbs / frac: launches "
                               "back to back, each waiting for the one before it; *_chained: with programmatic dependent launch, as "
                               "inside the decode step",
         "per_kernel_m1_large": None if m1_large is None else {

@@ -90,6 +90,7 @@ extern "C" int tm_create(tm_handle** out, int device)
     h->p2p_allreduce = env_int("TM_B200_P2P_ALLREDUCE", 1);
     h->lm_head_cublas = env_int("TM_B200_LM_HEAD_CUBLAS", 0);
     h->fold_norm      = env_int("TM_B200_FOLD_NORM", 1);
+    h->gemv_cols      = env_int("TM_B200_GEMV_COLS", 1);
     h->gemm_tc_min_n = env_int("TM_B200_GEMM_TC_MIN", 17);
     h->mmha_chunk  = env_int("TM_B200_MMHA_CHUNK", 0);
     h->mmha_warps  = env_int("TM_B200_MMHA_WARPS", 0);
@@ -159,6 +160,9 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     }
     else if (n == "fold_norm" && (value == 0 || value == 1)) {
         h->fold_norm = value;
+    }
+    else if (n == "gemv_cols" && (value == 0 || value == 1)) {
+        h->gemv_cols = value;
     }
     else if (n == "lm_head_cublas" && (value == 0 || value == 1)) {
         h->lm_head_cublas = value;
@@ -287,7 +291,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     const size_t n_out = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;
     int          n_launch = n;
     for (;;) {
-        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem);
+        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem, h->gemv_cols != 0);
         const size_t  c_b  = ((pl.counter_ints * sizeof(int) + 255) / 256) * 256;
         const size_t  need = pl.workspace_floats * sizeof(float) + c_b;
         const bool    fits = workspace ? workspace_bytes >= need :
@@ -300,7 +304,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
 
     for (int t0 = 0; t0 < n; t0 += n_launch) {
         const int     nt = n - t0 < n_launch ? n - t0 : n_launch;
-        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem);
+        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem, h->gemv_cols != 0);
         float*        ws_f;
         int*          ws_c;
         if (workspace) {

@@ -59,11 +59,20 @@ def test_noalloc_largest_llama_shape_fits_up_to_eight_tokens():
     for t in (1, 8):
         x = torch.randn(t, k, device="cuda", generator=g).half()
         ref = torch.empty(t, n // 2, dtype=torch.float16, device="cuda")
+        cols = torch.empty(t, n // 2, dtype=torch.float16, device="cuda")
         out = torch.full((t, n // 2), 123.0, dtype=torch.float16, device="cuda")
-        assert l.lib.tm_gemm_s4_f16(h.ptr, ref.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, None, 0, st) == l.TM_OK
+        # the handle entry picks the column-owner kernel for this shape; the allocation-free entry always runs the
+        # split-K kernel: bit-identical with the handle entry told to do the same, within the tolerance otherwise
+        assert l.lib.tm_gemm_s4_f16(h.ptr, cols.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, None, 0, st) == l.TM_OK
+        h.set_option("gemv_cols", 0)
+        try:
+            assert l.lib.tm_gemm_s4_f16(h.ptr, ref.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, None, 0, st) == l.TM_OK
+        finally:
+            h.set_option("gemv_cols", 1)
         assert l.lib.tm_gemm_s4_f16_noalloc(out.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, t, k, 128, 1, st) == l.TM_OK
         torch.cuda.synchronize()
         assert torch.equal(out, ref), "same kernel, same plan: bit-identical"
+        assert_close(cols.cpu().numpy(), ref.cpu().numpy(), f"column-owner kernel vs split-K kernel, {t} tokens", rel_slack=2.0 ** -9)
     x = torch.randn(16, k, device="cuda", generator=g).half()
     out = torch.empty(16, n // 2, dtype=torch.float16, device="cuda")
     assert l.lib.tm_gemm_s4_f16_noalloc(out.data_ptr(), A.data_ptr(), x.data_ptr(), Q.data_ptr(), n, 16, k, 128, 1, st) == l.TM_ERR_WORKSPACE
