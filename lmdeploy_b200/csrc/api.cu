@@ -161,7 +161,7 @@ extern "C" int tm_set_option(tm_handle* h, const char* name, int value)
     else if (n == "fold_norm" && (value == 0 || value == 1)) {
         h->fold_norm = value;
     }
-    else if (n == "gemv_cols" && (value == 0 || value == 1)) {
+    else if (n == "gemv_cols" && value >= 0 && value <= 2) {
         h->gemv_cols = value;
     }
     else if (n == "lm_head_cublas" && (value == 0 || value == 1)) {
@@ -291,7 +291,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
     const size_t n_out = type == TM_GEMM_FUSED_SILU_FFN ? (size_t)m / 2 : (size_t)m;
     int          n_launch = n;
     for (;;) {
-        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem, h->gemv_cols != 0);
+        GemmSmallPlan pl   = gemm_small_plan(m, n_launch, k, h->sm_count, h->max_smem, h->gemv_cols);
         const size_t  c_b  = ((pl.counter_ints * sizeof(int) + 255) / 256) * 256;
         const size_t  need = pl.workspace_floats * sizeof(float) + c_b;
         const bool    fits = workspace ? workspace_bytes >= need :
@@ -304,7 +304,7 @@ extern "C" int tm_gemm_s4_f16(tm_handle*  h,
 
     for (int t0 = 0; t0 < n; t0 += n_launch) {
         const int     nt = n - t0 < n_launch ? n - t0 : n_launch;
-        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem, h->gemv_cols != 0);
+        GemmSmallPlan pl = gemm_small_plan(m, nt, k, h->sm_count, h->max_smem, h->gemv_cols);
         float*        ws_f;
         int*          ws_c;
         if (workspace) {

@@ -32,14 +32,15 @@ struct GemmSmallPlan {
     int    ctas;
     int    slots_per_chunk;  // split-K scratch slots per token chunk (= ctas + n_col_tiles)
     int    stages;
-    bool   cols_mode;      // the column-owner kernel runs instead (up to 8 tokens, at least one 64-column strip per SM)
+    int    cols_tiles;     // 1 or 2: the column-owner kernel runs instead, on strips of that many 32-column tiles (up to 8 tokens,
+                           // at least one strip per SM); 0: the split-K kernel
     size_t smem_bytes;
     size_t workspace_floats;
     size_t counter_ints;
 };
 
 size_t        gemm_small_smem_bytes(int nt);
-GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, bool allow_cols = true);
+GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int cols_variant = 1);
 cudaError_t   gemm_small_prepare(int max_smem);
 cudaError_t   gemm_small_launch(const GemmSmallPlan& plan, GemmSmallParams p, cudaStream_t st, bool pdl = false);
 

@@ -497,19 +497,38 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm_for(NT)) gemm_s4_f16_sma
 }
 
 // ---- column-owner variant for up to 8 tokens --------------------------------------------------------------------
-// Where the weight has at least as many 64-column strips as the device has SMs (the qkv and gate/up projections),
-// nothing needs to be split between CTAs: a CTA owns one strip (two packed tiles, 1 KB contiguous per 32-row slab)
-// over the whole K range, its eight warps take the 128-row quantisation groups round robin (warp w: groups w, w + 8,
-// ...), each through a private cp.async ring of whole groups (4 KB of weight + the 256 B of {zero, scale}), and the
-// eight partial sums meet once in shared memory, in a fixed order.  No scratch, no tickets, no fence, no CTA that
-// reduces for others.  The activations (a few KB, the same for every CTA) come as B fragments straight from L1 / L2.
-// The arithmetic per group is that of the kernel above.
-constexpr int kCoStage  = 4 * 2 * kTileBytes + 256;  // one group of one strip: four slabs of two tiles + {zero, scale}
-constexpr int kCoStages = 3;
-constexpr int kCoSmem   = kWarps * kCoStages * kCoStage;
-
-__global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmallParams p)
+// Where the weight has at least as many column strips as the device has SMs (the qkv and gate/up projections),
+// nothing needs to be split between CTAs: a CTA owns one strip of TILES packed tiles (32 or 64 columns: 512 B or 1 KB
+// contiguous per 32-row slab) over the whole K range, its eight warps take the 128-row quantisation groups round
+// robin (warp w: groups w, w + 8, ...), each through a private cp.async ring of whole groups (2 KB of weight per tile
+// + its {zero, scale}), and the eight partial sums meet once in shared memory, in a fixed order.  No scratch, no
+// tickets, no fence, no CTA that reduces for others.  The ring is as deep as the plan says: with 32-column strips and
+// K = 4096 every byte the CTA will read is requested before the first one is used.  The activations (a few KB, the
+// same for every CTA) come as B fragments straight from L1 / L2.  The arithmetic per group is that of the kernel
+// above.
+// kOne: a single token.  The group sums of the activations then come from plain adds (every lane takes four of the
+// group's 128 values, a butterfly over the warp sums them) instead of two more MMAs per slab.
+__device__ __forceinline__ void cp_async_wait_pending(int n)
 {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<5>(); break;
+        case 6: cp_async_wait<6>(); break;
+        default: cp_async_wait<7>(); break;  // more may be pending than asked for: waiting for fewer is always right
+    }
+}
+
+__host__ __device__ constexpr int co_stage_bytes(int tiles) { return tiles * (4 * kTileBytes + 128); }  // four slabs + {zero, scale} per tile
+
+template<int TILES, bool kOne>
+__global__ void __launch_bounds__(kThreads, TILES == 1 ? 3 : 2) gemm_s4_f16_cols_kernel(GemmSmallParams p)
+{
+    constexpr int kStage = co_stage_bytes(TILES);
+    constexpr int kSlab  = TILES * kTileBytes;  // one 32-row slab of the strip
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t smem_s = smem_u32(smem_raw);
     const int      tid    = threadIdx.x;
@@ -517,52 +536,50 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
     const int      lane   = tid & 31;
     const int      r      = lane >> 2;
     const int      c      = lane & 3;
+    const int      ST     = p.stages;  // ring slots per warp
 
     const int    n_tiles32   = p.N / kColsPerTile;
     const int    G           = p.K / 128;
-    const int    tile0       = blockIdx.x * 2;
-    const int    step        = tile0 + 1 < n_tiles32 ? kTileBytes : 0;  // a strip at the edge of N holds one tile: it is read twice
+    const int    tile0       = blockIdx.x * TILES;
+    const int    step        = (TILES == 2 && tile0 + 1 < n_tiles32) ? kTileBytes : 0;  // a strip at the edge of N: one tile, read twice
     const size_t slab_stride = (size_t)n_tiles32 * kTileBytes;
     const int    n_groups    = warp < G ? (G - 1 - warp) / kWarps + 1 : 0;
 
-    const uint32_t       ring_s = smem_s + warp * (kCoStages * kCoStage);
+    const uint32_t       ring_s = smem_s + warp * (ST * kStage);
     const unsigned char* i_w    = p.A + ((size_t)(4 * warp) * n_tiles32 + tile0) * kTileBytes + lane * 16;
-    const unsigned char* i_q    = p.Q + ((size_t)warp * p.N + (size_t)tile0 * kColsPerTile) * 4 + (lane & 15) * 16;
-    const bool           i_qok  = lane < 16 && tile0 * kColsPerTile + lane * 4 < p.N;
-    auto issue_group = [&](int stage) {
-        const uint32_t dst = ring_s + stage * kCoStage;
+    const unsigned char* i_q    = p.Q + ((size_t)warp * p.N + (size_t)tile0 * kColsPerTile) * 4 + lane * 16;
+    const bool           i_qok  = lane < 8 * TILES && tile0 * kColsPerTile + lane * 4 < p.N;
+    auto issue_group = [&](int slot) {
+        const uint32_t dst = ring_s + slot * kStage;
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-            cp_async16(dst + h * (2 * kTileBytes) + lane * 16, i_w + h * slab_stride);
-            cp_async16(dst + h * (2 * kTileBytes) + kTileBytes + lane * 16, i_w + h * slab_stride + step);
+            cp_async16(dst + h * kSlab + lane * 16, i_w + h * slab_stride);
+            if (TILES == 2) cp_async16(dst + h * kSlab + kTileBytes + lane * 16, i_w + h * slab_stride + step);
         }
-        if (i_qok) cp_async16(dst + 4 * 2 * kTileBytes + lane * 16, i_q);
+        if (i_qok) cp_async16(dst + 4 * kSlab + lane * 16, i_q);
+        cp_async_commit();
         i_w += (size_t)(4 * kWarps) * slab_stride;  // this warp's next group: eight groups further down
         i_q += (size_t)kWarps * p.N * 4;
     };
     // the packed weight is written by no kernel: its first copies start ahead of the wait for the kernel before
-#pragma unroll
-    for (int sidx = 0; sidx < kCoStages - 1; ++sidx) {
-        if (sidx < n_groups) issue_group(sidx);
-        cp_async_commit();
-    }
+    int issued = 0;
+    for (; issued < ST && issued < n_groups; ++issued) issue_group(issued);
     pdl_wait();
     pdl_launch_dependents();
 
     // B fragments: token = fragment row (tokens beyond T repeat the last one: their columns are never stored)
     const uint32_t* x_row = reinterpret_cast<const uint32_t*>(p.X + (size_t)min(r, p.T - 1) * p.K * 2) + c;
 
-    float tot[kTilesPerWarp][2][4];
+    float tot[TILES][2][4];
 #pragma unroll
-    for (int w = 0; w < kTilesPerWarp; ++w)
+    for (int w = 0; w < TILES; ++w)
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
             for (int i = 0; i < 4; ++i) tot[w][a][i] = 0.f;
     const uint32_t ones[4] = {0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u};
 
-    int s = 0, s_fill = kCoStages - 1;
-    int to_issue = n_groups - (kCoStages - 1);
+    int slot = 0;  // ring slot of group `it`
     for (int it = 0; it < n_groups; ++it) {
         const int g = warp + it * kWarps;
         // the group's activations: k = 128 g + 32 h + 8 i + 2 c, + 1
@@ -571,17 +588,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
         for (int h = 0; h < 4; ++h)
 #pragma unroll
             for (int i = 0; i < 4; ++i) bf[h][i] = __ldg(x_row + g * 64 + h * 16 + i * 4);
-        cp_async_wait<kCoStages - 2>();
+        uint2 xs = make_uint2(0u, 0u);
+        if (kOne) xs = __ldg(reinterpret_cast<const uint2*>(p.X) + g * 32 + lane);  // this lane's four values of the group
+        // copies complete in the order they were committed: group `it` has landed once at most issued - it - 1 are pending
+        cp_async_wait_pending(issued - it - 1);
         __syncwarp();  // every lane's copies of this group have landed, and every lane is done with the group before
-        if (to_issue > 0) issue_group(s_fill);
-        --to_issue;
-        cp_async_commit();
+        if (it >= 1 && issued < n_groups) {
+            issue_group(slot == 0 ? ST - 1 : slot - 1);  // the slot of the group before: free now
+            ++issued;
+        }
 
-        const unsigned char* sb = smem_raw + warp * (kCoStages * kCoStage) + s * kCoStage;
-        const __half2*       qs = reinterpret_cast<const __half2*>(sb + 4 * 2 * kTileBytes);
-        float zl[kTilesPerWarp][2], zh[kTilesPerWarp][2], sl[kTilesPerWarp][2], sh[kTilesPerWarp][2];
+        const unsigned char* sb = smem_raw + warp * (ST * kStage) + slot * kStage;
+        const __half2*       qs = reinterpret_cast<const __half2*>(sb + 4 * kSlab);
+        float zl[TILES][2], zh[TILES][2], sl[TILES][2], sh[TILES][2];
 #pragma unroll
-        for (int w = 0; w < kTilesPerWarp; ++w) {
+        for (int w = 0; w < TILES; ++w) {
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
                 const float2 q_lo = __half22float2(qs[w * 32 + a * 16 + r]);      // {64 + z, s} of row r
@@ -592,22 +613,31 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
                 sh[w][a] = q_hi.y * 0.0625f;
             }
         }
-        float acc[kTilesPerWarp][2][4];
+        float acc[TILES][2][4];
         float sx[4];
+        if (kOne) {
+            float part = (__half2float(__ushort_as_half((unsigned short)(xs.x & 0xffffu))) + __half2float(__ushort_as_half((unsigned short)(xs.x >> 16))))
+                         + (__half2float(__ushort_as_half((unsigned short)(xs.y & 0xffffu))) + __half2float(__ushort_as_half((unsigned short)(xs.y >> 16))));
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            sx[0] = sx[1] = sx[2] = sx[3] = part;  // every column is the one token
+        }
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
-            // group sum of the activations, in the accumulator layout (every row alike)
-            if (h == 0) {
-                mma_m16n8k16_init(sx, ones, bf[h][0], bf[h][1]);
+            if (!kOne) {
+                // group sum of the activations, in the accumulator layout (every row alike)
+                if (h == 0) {
+                    mma_m16n8k16_init(sx, ones, bf[h][0], bf[h][1]);
+                }
+                else {
+                    mma_m16n8k16(sx, ones, bf[h][0], bf[h][1]);
+                }
+                mma_m16n8k16(sx, ones, bf[h][2], bf[h][3]);
             }
-            else {
-                mma_m16n8k16(sx, ones, bf[h][0], bf[h][1]);
-            }
-            mma_m16n8k16(sx, ones, bf[h][2], bf[h][3]);
-            uint32_t af[kTilesPerWarp][4][4];
+            uint32_t af[TILES][4][4];
 #pragma unroll
-            for (int w = 0; w < kTilesPerWarp; ++w) {
-                const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * (2 * kTileBytes) + w * kTileBytes + lane * 16);
+            for (int w = 0; w < TILES; ++w) {
+                const uint4    wq    = *reinterpret_cast<const uint4*>(sb + h * kSlab + w * kTileBytes + lane * 16);
                 const uint32_t wv[4] = {wq.x, wq.y, wq.z, wq.w};
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) unpack_s4_biased(wv[wi], af[w][wi]);
@@ -615,7 +645,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
 #pragma unroll
             for (int k16 = 0; k16 < 2; ++k16) {
 #pragma unroll
-                for (int w = 0; w < kTilesPerWarp; ++w) {
+                for (int w = 0; w < TILES; ++w) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
                         if (h == 0 && k16 == 0) {
@@ -630,7 +660,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
         }
         // end of the group: remove offsets and zero point, apply the scale
 #pragma unroll
-        for (int w = 0; w < kTilesPerWarp; ++w)
+        for (int w = 0; w < TILES; ++w)
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
                 tot[w][a][0] = fmaf(sl[w][a], fmaf(-zl[w][a], sx[0], acc[w][a][0]), tot[w][a][0]);
@@ -638,23 +668,23 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_s4_f16_cols_kernel(GemmSmall
                 tot[w][a][2] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[0], acc[w][a][2]), tot[w][a][2]);
                 tot[w][a][3] = fmaf(sh[w][a], fmaf(-zh[w][a], sx[1], acc[w][a][3]), tot[w][a][3]);
             }
-        s      = (s == kCoStages - 1) ? 0 : s + 1;
-        s_fill = (s_fill == kCoStages - 1) ? 0 : s_fill + 1;
+        slot = (slot == ST - 1) ? 0 : slot + 1;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();  // the rings are free: they now hold the eight warps' partial sums, [warp][16 values][lane]
-    float* red = reinterpret_cast<float*>(smem_raw);
+    __syncthreads();  // the rings are free: they now hold the eight warps' partial sums, [warp][TILES x 8 values][lane]
+    constexpr int kVals = TILES * 8;
+    float*        red   = reinterpret_cast<float*>(smem_raw);
 #pragma unroll
-    for (int w = 0; w < kTilesPerWarp; ++w)
+    for (int w = 0; w < TILES; ++w)
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) red[(warp * 16 + (w * 2 + a) * 4 + i) * 32 + lane] = tot[w][a][i];
+            for (int i = 0; i < 4; ++i) red[(warp * kVals + (w * 2 + a) * 4 + i) * 32 + lane] = tot[w][a][i];
     __syncthreads();
-    for (int e = warp; e < 16; e += kWarps) {
+    for (int e = warp; e < kVals; e += kWarps) {
         float v = 0.f;
 #pragma unroll
-        for (int wp = 0; wp < kWarps; ++wp) v += red[(wp * 16 + e) * 32 + lane];  // fixed order
+        for (int wp = 0; wp < kWarps; ++wp) v += red[(wp * kVals + e) * 32 + lane];  // fixed order
         const int  w     = e >> 3, a = (e >> 2) & 1, i = e & 3;
         const int  n     = (tile0 + w) * kColsPerTile + a * 16 + r + (i >> 1) * 8;
         const int  t     = 2 * c + (i & 1);
@@ -682,7 +712,7 @@ size_t gemm_small_smem_bytes(int nt)
     return (size_t)st * (kWarps * kWarpStage + 2 * nt * 512) + 16;
 }
 
-GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, bool allow_cols)
+GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, int cols_variant)
 {
     (void)max_smem;
     GemmSmallPlan pl{};
@@ -702,13 +732,23 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, b
     pl.smem_bytes       = gemm_small_smem_bytes(pl.nt);
     pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * tp * kUnitCols;
     pl.counter_ints     = (size_t)pl.t_chunks * pl.n_col_tiles;
-    // Enough 64-column strips to give every SM one: the column-owner kernel, which splits nothing between CTAs.  The
+    // Enough column strips to give every SM one: the column-owner kernel, which splits nothing between CTAs.  The
     // scratch sizes above stay (unused) so that a caller's workspace is judged the same way for both kernels.
-    const int strips = (N / kColsPerTile + 1) / 2;
-    pl.cols_mode     = allow_cols && T <= 8 && strips >= sm_count;
-    if (pl.cols_mode) {
+    // Variant 1: 32-column strips, three CTAs per SM, a ring of up to four groups per warp (the whole K range of a
+    // 4096-row weight is requested at once); variant 2: 64-column strips, two CTAs per SM, three groups.
+    const int tiles  = cols_variant == 2 ? 2 : 1;
+    const int strips = (N / kColsPerTile + tiles - 1) / tiles;
+    // Measured on the 7B shapes: with all strips resident at once (qkv: 384 strips for 444 slots) it wins at every
+    // token count up to 8; with more strips than slots (gate/up: 688) it wins at one token, ties up to four and loses at
+    // eight, where every CTA re-reads 64 KB of activations.
+    const int  slots      = sm_count * (tiles == 2 ? 2 : 3);
+    const bool worthwhile = strips >= sm_count && (strips <= slots || T == 1);
+    pl.cols_tiles         = (cols_variant != 0 && T <= 8 && worthwhile) ? tiles : 0;
+    if (pl.cols_tiles) {
+        const int per_warp = (K / 128 + kWarps - 1) / kWarps;  // groups of the busiest warp
         pl.ctas       = strips;
-        pl.smem_bytes = kCoSmem;
+        pl.stages     = tiles == 2 ? 3 : (per_warp < 2 ? 2 : (per_warp > 4 ? 4 : per_warp));
+        pl.smem_bytes = (size_t)kWarps * pl.stages * co_stage_bytes(tiles);
     }
     return pl;
 }
@@ -720,7 +760,14 @@ cudaError_t gemm_small_prepare(int max_smem)
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(gemm_s4_f16_small_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(gemm_s4_f16_cols_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCoSmem);
+    constexpr int kCoSmemMax = kWarps * 4 * co_stage_bytes(2);
+    e = cudaFuncSetAttribute(gemm_s4_f16_cols_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCoSmemMax);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(gemm_s4_f16_cols_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCoSmemMax);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(gemm_s4_f16_cols_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCoSmemMax);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(gemm_s4_f16_cols_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCoSmemMax);
     if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(gemm_s4_f16_small_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
@@ -734,7 +781,14 @@ cudaError_t gemm_small_launch(const GemmSmallPlan& pl, GemmSmallParams p, cudaSt
     p.stages          = pl.stages;
     dim3 grid(pl.ctas, pl.t_chunks);
     dim3 block(kThreads);
-    if (pl.cols_mode) return launch_kernel(gemm_s4_f16_cols_kernel, grid, block, pl.smem_bytes, st, pdl, p);
+    if (pl.cols_tiles == 1) {
+        return p.T == 1 ? launch_kernel(gemm_s4_f16_cols_kernel<1, true>, grid, block, pl.smem_bytes, st, pdl, p) :
+                          launch_kernel(gemm_s4_f16_cols_kernel<1, false>, grid, block, pl.smem_bytes, st, pdl, p);
+    }
+    if (pl.cols_tiles == 2) {
+        return p.T == 1 ? launch_kernel(gemm_s4_f16_cols_kernel<2, true>, grid, block, pl.smem_bytes, st, pdl, p) :
+                          launch_kernel(gemm_s4_f16_cols_kernel<2, false>, grid, block, pl.smem_bytes, st, pdl, p);
+    }
     switch (pl.nt) {
         case 1: return launch_kernel(gemm_s4_f16_small_kernel<1>, grid, block, pl.smem_bytes, st, pdl, p);
         case 2: return launch_kernel(gemm_s4_f16_small_kernel<2>, grid, block, pl.smem_bytes, st, pdl, p);
@@ -816,7 +870,7 @@ extern "C" int tm_gemm_s4_f16_noalloc(
         d = s;
     }
 
-    const GemmSmallPlan pl = gemm_small_plan(m, n, k, d.sm_count, d.max_smem, false);
+    const GemmSmallPlan pl = gemm_small_plan(m, n, k, d.sm_count, d.max_smem, 0);
     if (pl.counter_ints * sizeof(int) > kStaticControlBytes - 8
         || pl.workspace_floats * sizeof(float) > kStaticScratchBytes - kStaticControlBytes) {
         return TM_ERR_WORKSPACE;  // problem too large for the 8 MB built into the library

@@ -29,7 +29,8 @@ struct tm_handle {
     int                p2p_allreduce   = 1;  // TM_B200_P2P_ALLREDUCE / option "p2p_allreduce": peer-memory all-reduce + norm in the decode step
     int                fold_norm       = 1;  // TM_B200_FOLD_NORM=0 / option "fold_norm": the decode step keeps residual add + RMSNorm as kernels of their own
     int                lm_head_cublas  = 0;  // TM_B200_LM_HEAD_CUBLAS=1 / option "lm_head_cublas": the decode step's lm-head through cuBLAS (comparison only)
-    int                gemv_cols       = 1;  // TM_B200_GEMV_COLS=0 / option "gemv_cols": the small-token GEMM never uses its column-owner kernel
+    int                gemv_cols       = 1;  // TM_B200_GEMV_COLS / option "gemv_cols": 0 = the small-token GEMM never uses its column-owner kernel,
+                                             // 1 = 32-column strips, 2 = 64-column strips
     int                pdl             = 1;  // TM_B200_PDL=0: the decode driver launches its kernels without programmatic dependent launch
 };
 
