@@ -741,8 +741,8 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, i
     // Measured on the 7B shapes: with all strips resident at once (qkv: 384 strips for 444 slots) it wins at every
     // token count up to 8; with more strips than slots (gate/up: 688) it wins at one token, ties up to four and loses at
     // eight, where every CTA re-reads 64 KB of activations.
-    const int  slots      = sm_count * (tiles == 2 ? 2 : 3);
-    const bool worthwhile = strips >= sm_count && (strips <= slots || T == 1);
+    const int  co_slots   = sm_count * (tiles == 2 ? 2 : 3);
+    const bool worthwhile = strips >= sm_count && (strips <= co_slots || T == 1);
     pl.cols_tiles         = (cols_variant != 0 && T <= 8 && worthwhile) ? tiles : 0;
     if (pl.cols_tiles) {
         const int per_warp = (K / 128 + kWarps - 1) / kWarps;  // groups of the busiest warp
