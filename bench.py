@@ -867,7 +867,7 @@ def run_decode_workload(args, rank, world, device, name):
     dom = max(((k, v) for k, v in per.items() if not k.startswith("gemm ")), key=lambda kv: kv[1]["us_per_step"])
     # DRAM bytes per launch of the dominant kernel: ratio measured once with ncu on the same shapes
     # (dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes; profiles/), applied to this launch
-    traffic_ratio = {"gemm_s4_f16_tc_kernel": 1.03, "gemm_s4_f16_small_kernel": 1.0, "mmha_decode_kernel": 1.02}
+    traffic_ratio = {"gemm_s4_f16_tc_kernel": 1.03, "gemm_s4_f16_small_kernel": 1.0, "gemm_s4_f16_cols_kernel": 1.0, "mmha_decode_kernel": 1.02}
     ratio = next((r for k, r in traffic_ratio.items() if dom[0].startswith(k)), None)
     out = {
         "metric": "decode tokens/s Llama-2 W4A16", "value": round(B * 1e3 / ms_step, 1), "unit": "tokens/s",

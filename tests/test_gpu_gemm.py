@@ -56,7 +56,7 @@ def test_small_shapes_all_token_counts(n, k, t):
     assert_close(y, ogemm.gemm_s4_f16(x, lin["w_kn"]), f"gemm n={n} k={k} t={t}")
 
 
-@pytest.mark.parametrize("n,k", [(64, 128), (192, 512), (22016, 4096)])
+@pytest.mark.parametrize("n,k", [(64, 128), (192, 512), (22016, 4096), (7168, 2048)])   # the last: one strip per CTA slot, fused, at every token count
 @pytest.mark.parametrize("t", [1, 2, 8, 16, 40])
 def test_fused_silu(n, k, t):
     lin = _linear(n, k, 11)
