@@ -71,6 +71,8 @@ TM_API unsigned long long tm_launch_count(const tm_handle* h);
  * them into the tensor-core GEMMs on either side),
  * "lm_head_cublas" (1: the decode driver computes the lm-head with cuBLAS, as the reference does, instead of this
  * library's kernel; for comparison),
+ * "gemv_cols" (the GEMM for 1..8 tokens: 0 = always the stream-K kernel, 1 = the column-owner kernel on 32-column strips
+ * where the weight has a strip for every SM, 2 = on 64-column strips),
  * "mmha_chunk" (cached tokens per KV split, 0 = automatic), "mmha_warps" (warps per attention CTA: 1, 2,
  * 4 or 0 = automatic), "pdl" (1 = tm_llama_decode launches with programmatic dependent launch).
  * Returns TM_ERR_INVALID_ARG for an unknown name or value. */
