@@ -798,7 +798,9 @@ def run_decode_workload(args, rank, world, device, name):
         # prompts (not timed): tm_llama_prefill, a few sequences per call to bound the activation buffers
         group = max(1, min(B, 16384 // max(pmax, 1)))
         for b0 in range(0, B, group):
-            model.prefill(st, [prompts[b][:-1].tolist() if b0 <= b < b0 + group else [] for b in range(B)])
+            part = [prompts[b][:-1].tolist() if b0 <= b < b0 + group else [] for b in range(B)]
+            if any(part):                                     # one-token prompts have nothing to prefill
+                model.prefill(st, part)
         assert bool((st.lengths.cpu().numpy() == prompt_len - 1).all())
         model.decode(st, lead, use_graph=True)            # untimed decode steps up to the window (>= warm-up)
         h.check_device_status(stream.cuda_stream)
@@ -1031,7 +1033,7 @@ def time_decode_kernels(model, st, cfg, B, tp, stream, tm, session_len):
         gemm_us += us
         gemm_b += nb
         per[nm] = dict(us=round(us, 2), gbs=round(nb / us * 1e-3, 1), us_per_step=round(us * cfg.num_layer, 1), bytes=int(nb))
-    kname = "gemm_s4_f16_tc_kernel" if B > 16 else "gemm_s4_f16_small_kernel"
+    kname = "gemm_s4_f16_tc_kernel" if B > 16 else "gemm_s4_f16_small_kernel" if B > 8 else "gemm_s4_f16_cols_kernel + gemm_s4_f16_small_kernel"
     per[f"{kname} (4 projections of a layer)"] = dict(us=round(gemm_us / 4, 2), gbs=round(gemm_b / gemm_us * 1e-3, 1),
                                                       us_per_step=round(gemm_us * cfg.num_layer, 1), bytes=int(gemm_b / 4))
     # attention over the caches as they stand (layer l of every sequence)
