@@ -733,7 +733,7 @@ GemmSmallPlan gemm_small_plan(int N, int T, int K, int sm_count, int max_smem, i
     pl.workspace_floats = (size_t)pl.t_chunks * pl.slots_per_chunk * tp * kUnitCols;
     pl.counter_ints     = (size_t)pl.t_chunks * pl.n_col_tiles;
     // Enough column strips to give every SM one: the column-owner kernel, which splits nothing between CTAs.  The
-    // scratch sizes above stay (unused) so that a caller's workspace is judged the same way for both kernels.
+    // scratch sizes above stay (unused) so that a caller's workspace is sized the same way for both kernels.
     // Variant 1: 32-column strips, three CTAs per SM, a ring of up to four groups per warp (the whole K range of a
     // 4096-row weight is requested at once); variant 2: 64-column strips, two CTAs per SM, three groups.
     const int tiles  = cols_variant == 2 ? 2 : 1;

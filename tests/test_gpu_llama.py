@@ -3,7 +3,7 @@ numpy oracle, teacher-forced: the oracle free-runs, the GPU path is fed the orac
 and the normed hidden state and logits are compared step by step (max-abs 2e-2, mean-rel 1e-3 would
 be the single-kernel bar; through several layers the bound used is max-abs 3e-2 and mean-rel 5e-3).
 After every step the rows appended to the KV cache are compared (one LSB for int8) and the oracle
-continues from the GPU's cache, so that each step is judged on identical history."""
+continues from the GPU's cache, so that each step is compared on identical history."""
 import numpy as np
 import pytest
 import torch
