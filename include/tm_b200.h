@@ -618,7 +618,7 @@ typedef struct tm_request {
     unsigned long long random_seed;
     int                ignore_eos;
     const int*         stop_ids;           /* host memory, copied: drawing one of these tokens ends the request too (the   */
-    int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:512-513) */
+    int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:513-514) */
     const int*         bad_ids;            /* host memory, copied: tokens the request never draws (single-token bad words,    */
     int                bad_count;          /* at most 32; their logits are set to -inf before every draw)                     */
 } tm_request;
