@@ -621,6 +621,8 @@ typedef struct tm_request {
     int                stop_count;         /* single-token stop words, the only kind LlamaBatch takes: LlamaBatch.cc:513-514) */
     const int*         bad_ids;            /* host memory, copied: tokens the request never draws (single-token bad words,    */
     int                bad_count;          /* at most 32; their logits are set to -inf before every draw)                     */
+    int                rewind;             /* 1: a continued session first goes back to its first `step` tokens (the "step"   */
+    int                step;               /* input of the reference's requests, LlamaBatch.cc:587-596); 0: history kept     */
 } tm_request;
 enum { TM_REQUEST_QUEUED = 0, TM_REQUEST_RUNNING = 1, TM_REQUEST_FINISHED = 2, TM_REQUEST_FAILED = 3 };
 TM_API int tm_batch_create(tm_batch** out, tm_llama* model, tm_cache_manager* cache, int max_batch_size, int session_len,

@@ -335,7 +335,13 @@ extern "C" int tm_batch_step(tm_batch* b, void* stream, int use_graph)
         size_t got = 0;
         if (sl.seq.token_count) tm_cache_tokens(b->cache, r.id, sl.tokens.data(), sl.tokens.size(), &got);
         sl.tokens.resize(got);
-        const int cached = (int)std::min(sl.seq.cache_len, sl.tokens.size());  // a swapped-out slab comes back with 0
+        int cached = (int)std::min(sl.seq.cache_len, sl.tokens.size());  // a swapped-out slab comes back with 0
+        if (r.rewind && !r.start_flag && r.step >= 0 && r.step <= (int)sl.tokens.size()) {
+            // the session goes back to its first `step` tokens (LlamaBatch.cc:587-596; a step beyond the history is
+            // ignored there with a warning, here silently); rows of the slab beyond them are overwritten as needed
+            sl.tokens.resize(r.step);
+            cached = std::min(cached, r.step);
+        }
         sl.tokens.insert(sl.tokens.end(), ids.begin(), ids.end());
         if (sl.tokens.empty()) sl.tokens.push_back(b->start_id);  // LlamaBatch.cc:599-604
         const int context_len = (int)sl.tokens.size();

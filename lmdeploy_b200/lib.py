@@ -93,7 +93,7 @@ class TmRequest(C.Structure):
                 ("input_length", C.c_int), ("request_output_len", C.c_int), ("top_k", C.c_int), ("top_p", C.c_float),
                 ("temperature", C.c_float), ("repetition_penalty", C.c_float), ("random_seed", C.c_ulonglong),
                 ("ignore_eos", C.c_int), ("stop_ids", C.POINTER(C.c_int)), ("stop_count", C.c_int),
-                ("bad_ids", C.POINTER(C.c_int)), ("bad_count", C.c_int)]
+                ("bad_ids", C.POINTER(C.c_int)), ("bad_count", C.c_int), ("rewind", C.c_int), ("step", C.c_int)]
 
 
 class TmContextAttentionParams(C.Structure):

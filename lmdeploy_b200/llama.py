@@ -311,12 +311,13 @@ class Batch:
 
     def submit(self, session_id: int, input_ids, request_output_len: int, start: bool = True, end: bool = True, top_k: int = 0,
                top_p: float = 0.0, temperature: float = 0.0, repetition_penalty: float = 0.0, random_seed: int = 0,
-               ignore_eos: bool = False, stop_ids=(), bad_ids=()) -> int:
+               ignore_eos: bool = False, stop_ids=(), bad_ids=(), step=None) -> int:
         ids = (C.c_int * max(1, len(input_ids)))(*[int(t) for t in input_ids])
         stops = (C.c_int * max(1, len(stop_ids)))(*[int(t) for t in stop_ids])
         bads = (C.c_int * max(1, len(bad_ids)))(*[int(t) for t in bad_ids])
         r = _l.TmRequest(session_id, int(start), int(end), ids, len(input_ids), request_output_len, top_k, top_p, temperature,
-                         repetition_penalty, random_seed, int(ignore_eos), stops, len(stop_ids), bads, len(bad_ids))
+                         repetition_penalty, random_seed, int(ignore_eos), stops, len(stop_ids), bads, len(bad_ids),
+                         0 if step is None else 1, 0 if step is None else int(step))
         return _l.lib.tm_batch_submit(self._b, C.byref(r))
 
     def step(self, use_graph: bool = False, stream=None) -> None:

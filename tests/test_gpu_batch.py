@@ -101,6 +101,25 @@ def test_session_continues_from_its_cached_tokens():
     model.close()
 
 
+def test_session_rewound_to_a_step_equals_the_truncated_conversation():
+    """The `step` input of a continued request: the session keeps its first `step` tokens only."""
+    from lmdeploy_b200 import llama
+    model, _, _ = build(False)
+    rng = np.random.default_rng(4)
+    p1, p2 = [int(t) for t in rng.integers(3, CFG["vocab_size"], size=6)], [int(t) for t in rng.integers(3, CFG["vocab_size"], size=3)]
+    b = llama.Batch(model, 2)
+    assert b.submit(1, p1, 5, end=False, ignore_eos=True) == 0
+    b.run(max_rounds=50)
+    g1 = b.output(1)[0]
+    assert b.submit(1, p2, 4, start=False, end=True, ignore_eos=True, step=8) == 0      # 6 prompt tokens + the first 2 generated
+    b.run(max_rounds=50)
+    g2 = b.output(1)[0]
+    b.close()
+    res, _ = _run(model, 1, [(2, (p1 + g1)[:8] + p2, 4)], llama)
+    assert res[2][0] == g2, (res[2][0], g2)
+    model.close()
+
+
 def test_sampling_depends_on_the_seed_only():
     from lmdeploy_b200 import llama
     model, _, _ = build(False)
