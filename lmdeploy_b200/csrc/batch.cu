@@ -188,7 +188,7 @@ extern "C" int tm_batch_output(const tm_batch* b, uint64_t id, int* tokens, size
     const auto& g = it->second.generated;
     if (count) *count = g.size();
     if (state) *state = it->second.state;
-    if (tokens) std::memcpy(tokens, g.data(), std::min(capacity, g.size()) * sizeof(int));
+    if (tokens && !g.empty()) std::memcpy(tokens, g.data(), std::min(capacity, g.size()) * sizeof(int));
     return TM_OK;
 }
 

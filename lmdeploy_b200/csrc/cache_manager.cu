@@ -219,7 +219,7 @@ extern "C" int tm_cache_tokens(const tm_cache_manager* m, uint64_t id, int* toke
     *token_count = it->second.token_ids.size();
     if (token_ids) {
         if (capacity < *token_count) return TM_ERR_WORKSPACE;
-        std::memcpy(token_ids, it->second.token_ids.data(), *token_count * sizeof(int));
+        if (*token_count) std::memcpy(token_ids, it->second.token_ids.data(), *token_count * sizeof(int));  // an empty vector's data() may be null
     }
     return TM_OK;
 }
