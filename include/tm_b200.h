@@ -590,7 +590,8 @@ TM_API unsigned long long tm_llama_last_launches(const tm_llama* m);
 TM_API int tm_llama_check_status(tm_llama* m, void* stream, unsigned* word);
 
 /* ------------------------------------------------------------------------------------------
- * Persistent-batch scheduler over tm_cache_*, tm_llama_prefill, tm_llama_decode and tm_sample_topk: the part of
+ * Persistent-batch scheduler over tm_cache_*, tm_llama_prefill, tm_llama_decode, tm_sample_topk / tm_sample_topp and
+ * tm_ban_bad_words: the part of
  * LlamaBatch<T> (src/turbomind/models/llama/LlamaBatch.cc: initialize :562-763, contextDecode :765-877, generate
  * :471-559, finish / finishRequest :930-970, 1056-1118) that decides who runs.  Requests wait in a queue; every
  * tm_batch_step admits as many as there are free slots (their session's cached tokens come back from the cache
@@ -600,7 +601,9 @@ TM_API int tm_llama_check_status(tm_llama* m, void* stream, unsigned* word);
  * length go back to the cache manager (tm_cache_update), or the slab is released when end_flag was set.
  * Live sequences are kept dense in the batch; nothing is padded.  Not thread-safe: one host thread per scheduler.
  * Sampling fields of a request: top_k 0 and top_p 0 mean greedy, top_p 0 means 1, temperature / repetition_penalty 0
- * mean 1 (TopKSamplingLayer<T>::setup, src/turbomind/layers/sampling_layers/TopKSamplingLayer.cu:60-112).
+ * mean 1 (TopKSamplingLayer<T>::setup, src/turbomind/layers/sampling_layers/TopKSamplingLayer.cu:60-112); a request
+ * with a top_p and no top_k is drawn over the whole vocabulary by tm_sample_topp, the others by tm_sample_topk, as the
+ * reference's two layers share a batch (src/turbomind/layers/DynamicDecodeLayer.cc:305-312).
  * With tensor parallelism every rank runs its own scheduler on the same requests and seeds and draws the same tokens.
  */
 typedef struct tm_batch tm_batch;
