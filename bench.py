@@ -322,7 +322,7 @@ def run_gemm_workload(args, rank, world, device):
                    "l2": "inputs larger than L2: weights replicated beyond 2x L2, next replica each launch",
                    "parallelism": "replicas only" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "kernel": ("reference gemm_s4_f16_nn" if reflib is not None else
-                                                "gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_cols_kernel" if T <= 8 else "gemm_s4_f16_small_kernel") + " (gate_up)",
+                                                "gemm_s4_f16_tc_kernel" if T > 16 else "gemm_s4_f16_cols_kernel" if T == 1 else "gemm_s4_f16_small_kernel") + " (gate_up)",
                      "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(dom["gbs"] / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
                      "algorithmic_bytes": dom["bytes"],
